@@ -1,0 +1,335 @@
+// Host side of the C ABI declared in include/cute_mma_b200.h: argument validation, TMA descriptor
+// construction, launch of the sm_100a kernels, the per-device workspace (status record, staging
+// buffers of the host-buffer entry point).  Takes over the role of the reference's host launchers
+// oft_tn (cute_oft_coop_pc.cu:505-577) and gemm_tn / gemm_nt / gemm (gemm_sm80_tc.cu:95-228, 393-418),
+// with the checks the reference leaves out (shape, alignment, shared-memory opt-in).
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+#include <mutex>
+#include <string>
+
+#include <cuda.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+
+#include "../../include/cute_mma_b200.h"
+#include "gemm_config.hpp"   // resolved through -I<config dir>
+#include "oft_config.hpp"
+#include "gemm_kernel.cuh"
+#include "oft_kernel.cuh"
+
+namespace {
+
+using namespace b200;
+
+thread_local std::string g_err;
+
+int fail(int code, const char* fmt, ...) {
+  char buf[512];
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(buf, sizeof buf, fmt, ap);
+  va_end(ap);
+  g_err = buf;
+  return code;
+}
+
+#define CUDA_TRY(call)                                                                       \
+  do {                                                                                       \
+    cudaError_t e_ = (call);                                                                 \
+    if (e_ != cudaSuccess) return fail(B200_ECUDA, "%s failed: %s", #call, cudaGetErrorString(e_)); \
+  } while (0)
+
+// ---- per-device state ------------------------------------------------------------------------------
+constexpr int kMaxDevices = 64;
+struct DeviceState {
+  bool ready = false;
+  int sm_count = 0;
+  int* status = nullptr;            // 4 ints, zeroed; kernels record a timed-out wait here
+  void* stage[4] = {nullptr, nullptr, nullptr, nullptr};  // staging of the host-buffer entry point
+  size_t stage_bytes[4] = {0, 0, 0, 0};
+  cudaStream_t host_stream = nullptr;
+};
+DeviceState g_dev[kMaxDevices];
+std::mutex g_mu;        // guards g_dev initialisation
+std::mutex g_host_mu;   // serialises the host-buffer entry point (it owns the staging buffers)
+
+using EncodeFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                              const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                              CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+EncodeFn g_encode = nullptr;
+
+int device_state(DeviceState** out) {
+  int dev = 0;
+  CUDA_TRY(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= kMaxDevices) return fail(B200_EINVAL, "device ordinal %d out of range", dev);
+  std::lock_guard<std::mutex> lock(g_mu);
+  DeviceState& st = g_dev[dev];
+  if (!st.ready) {
+    cudaDeviceProp prop;
+    CUDA_TRY(cudaGetDeviceProperties(&prop, dev));
+    if (prop.major != 10)
+      return fail(B200_EUNSUPPORTED, "device %d is sm_%d%d; this library contains sm_100a code only", dev, prop.major, prop.minor);
+    st.sm_count = prop.multiProcessorCount;
+    CUDA_TRY(cudaMalloc(&st.status, 4 * sizeof(int)));
+    CUDA_TRY(cudaMemset(st.status, 0, 4 * sizeof(int)));
+    if (!g_encode) {
+      void* fn = nullptr;
+      cudaDriverEntryPointQueryResult q;
+      CUDA_TRY(cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &q));
+      if (q != cudaDriverEntryPointSuccess || !fn) return fail(B200_ECUDA, "cuTensorMapEncodeTiled not available from the driver");
+      g_encode = reinterpret_cast<EncodeFn>(fn);
+    }
+    st.ready = true;
+  }
+  *out = &st;
+  return B200_OK;
+}
+
+// 2-D tensor map over a matrix whose contiguous dimension has `inner` elements and whose other
+// dimension has `outer` rows `ld` elements apart; boxes of box_inner x box_outer, 128-byte swizzle.
+int make_map(CUtensorMap* map, const void* base, int elem_bytes, long long inner, long long outer, long long ld,
+             int box_inner, int box_outer, const char* what, bool atom32 = false) {
+  if (reinterpret_cast<uintptr_t>(base) & 15) return fail(B200_EINVAL, "%s: base pointer must be 16-byte aligned", what);
+  if ((ld * elem_bytes) % 16 != 0) return fail(B200_EINVAL, "%s: leading dimension %lld x %d bytes must be a multiple of 16 bytes", what, ld, elem_bytes);
+  if (ld < inner) return fail(B200_EINVAL, "%s: leading dimension %lld smaller than the contiguous extent %lld", what, ld, inner);
+  cuuint64_t dims[2] = {static_cast<cuuint64_t>(inner), static_cast<cuuint64_t>(outer)};
+  cuuint64_t strides[1] = {static_cast<cuuint64_t>(ld) * elem_bytes};
+  cuuint32_t box[2] = {static_cast<cuuint32_t>(box_inner), static_cast<cuuint32_t>(box_outer)};
+  cuuint32_t estr[2] = {1, 1};
+  const CUtensorMapDataType dt = elem_bytes == 2 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32;
+  CUresult r = g_encode(map, dt, 2, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                        atom32 ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B : CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return fail(B200_ECUDA, "%s: cuTensorMapEncodeTiled failed with CUresult %d", what, static_cast<int>(r));
+  return B200_OK;
+}
+
+template <class Kernel>
+int opt_in_smem(Kernel kernel, int bytes) {
+  // The reference never raises the dynamic shared-memory limit and so cannot launch any tile
+  // configuration above 48 KB; every kernel here needs the opt-in.
+  CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes));
+  return B200_OK;
+}
+
+int common_dims(int m, int n, int k, const void* A, const void* B, void* C) {
+  if (m < 0 || n < 0 || k < 0) return fail(B200_EINVAL, "negative dimension (m=%d n=%d k=%d)", m, n, k);
+  if (m > 0 && n > 0 && !C) return fail(B200_EINVAL, "C is null");
+  if (m > 0 && n > 0 && k > 0 && (!A || !B)) return fail(B200_EINVAL, "A or B is null");
+  return B200_OK;
+}
+
+// ---- plain GEMM --------------------------------------------------------------------------------------
+template <typename TIn, typename TOut, bool kNT, class P>
+int launch_gemm(int m, int n, int k, const void* A, int ldA, const void* B, int ldB, void* C, int ldC, void* stream_v) {
+  using T = GemmTraits<TIn, TOut, kNT, kNT, P::bN, P::bP>;
+  static_assert(P::bM == T::kBM && P::bK == T::kBK, "gemm_config.hpp: bM must be 128 and bK one 128-byte row");
+  g_err.clear();
+  if (int rc = common_dims(m, n, k, A, B, C)) return rc;
+  if (ldC < m) return fail(B200_EINVAL, "ldC=%d smaller than m=%d (C is column-major)", ldC, m);
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
+  if (m == 0 || n == 0) return B200_OK;
+  if (k == 0) {
+    CUDA_TRY(cudaMemset2DAsync(C, static_cast<size_t>(ldC) * sizeof(TOut), 0, static_cast<size_t>(m) * sizeof(TOut), n, stream));
+    return B200_OK;
+  }
+  DeviceState* st;
+  if (int rc = device_state(&st)) return rc;
+  CUtensorMap ma, mb;
+  if (!kNT) {  // K contiguous
+    if (int rc = make_map(&ma, A, sizeof(TIn), k, m, ldA, T::kBK, T::kBM, "A")) return rc;
+    if (int rc = make_map(&mb, B, sizeof(TIn), k, n, ldB, T::kBK, T::kBN, "B")) return rc;
+  } else {     // M / N contiguous, one 128-byte column chunk per copy
+    if (int rc = make_map(&ma, A, sizeof(TIn), m, k, ldA, T::kChunk, T::kBK, "A", T::kA32Atom)) return rc;
+    if (int rc = make_map(&mb, B, sizeof(TIn), n, k, ldB, T::kChunk, T::kBK, "B", T::kB32Atom)) return rc;
+  }
+  auto kernel = gemm_kernel<T>;
+  if (int rc = opt_in_smem(kernel, T::kSmemBytes)) return rc;
+  const long long tiles = static_cast<long long>((m + T::kBM - 1) / T::kBM) * ((n + T::kBN - 1) / T::kBN);
+  const int grid = static_cast<int>(tiles < st->sm_count ? tiles : st->sm_count);
+  GemmArgs args{m, n, k, C, ldC, st->status};
+  kernel<<<grid, T::kThreads, T::kSmemBytes, stream>>>(ma, mb, args);
+  CUDA_TRY(cudaGetLastError());
+  return B200_OK;
+}
+
+// ---- fused OFT ---------------------------------------------------------------------------------------
+template <int kB>
+int launch_oft(int m, int n, int k, int group_size, const void* A, int ldA, const void* B, int ldB, const void* R, int ldR,
+               void* C, int ldC, cudaStream_t stream, DeviceState* st) {
+  using T = OftTraits<kB, CurrCompParams::bN, CurrCompParams::bP1, CurrCompParams::bP2>;
+  static_assert(CurrCompParams::bM == T::kBM && CurrCompParams::bK == T::kBK, "oft_config.hpp: bM must be 128 and bK 64");
+  if (group_size != n && group_size % T::kBN != 0)
+    return fail(B200_EUNSUPPORTED, "group_size=%d must equal n or be a multiple of the N tile %d", group_size, T::kBN);
+  const int n_groups = n / group_size;
+  CUtensorMap ma, mr, mb;
+  if (int rc = make_map(&ma, A, 2, k, m, ldA, T::kBK, T::kBM, "A")) return rc;
+  if (int rc = make_map(&mr, R, 2, k, static_cast<long long>(n_groups) * kB, ldR, T::kBK, kB, "R")) return rc;
+  if (int rc = make_map(&mb, B, 2, k, n, ldB, T::kBK, T::kBN, "B")) return rc;
+  auto kernel = oft_kernel<T>;
+  if (int rc = opt_in_smem(kernel, T::kSmemBytes)) return rc;
+  const long long tiles = static_cast<long long>((m + T::kBM - 1) / T::kBM) * ((n + T::kBN - 1) / T::kBN);
+  const int grid = static_cast<int>(tiles < st->sm_count ? tiles : st->sm_count);
+  OftArgs args{m, n, k, group_size, static_cast<__half*>(C), ldC, st->status};
+  kernel<<<grid, T::kThreads, T::kSmemBytes, stream>>>(ma, mr, mb, args);
+  CUDA_TRY(cudaGetLastError());
+  return B200_OK;
+}
+
+int oft_dispatch(int m, int n, int k, int group_size, int b, const void* A, int ldA, const void* B, int ldB, const void* R, int ldR,
+                 void* C, int ldC, cudaStream_t stream) {
+  g_err.clear();
+  if (int rc = common_dims(m, n, k, A, B, C)) return rc;
+  if (b <= 0 || group_size <= 0) return fail(B200_EINVAL, "group_size=%d and reconn_sz=%d must be positive", group_size, b);
+  if (k % b != 0) return fail(B200_EINVAL, "k=%d is not a multiple of reconn_sz=%d", k, b);
+  if (n % group_size != 0) return fail(B200_EINVAL, "n=%d is not a multiple of group_size=%d", n, group_size);
+  if (ldC < n) return fail(B200_EINVAL, "ldC=%d smaller than n=%d (C is row-major)", ldC, n);
+  if (m > 0 && n > 0 && k > 0 && !R) return fail(B200_EINVAL, "R is null");
+  if (m == 0 || n == 0) return B200_OK;
+  if (k == 0) {  // cpu_oft_tn zero-fills C and has no K block to add (cpu_oft.hpp:31,101-102)
+    CUDA_TRY(cudaMemset2DAsync(C, static_cast<size_t>(ldC) * 2, 0, static_cast<size_t>(n) * 2, m, stream));
+    return B200_OK;
+  }
+  DeviceState* st;
+  if (int rc = device_state(&st)) return rc;
+  switch (b) {
+    case 16: return launch_oft<16>(m, n, k, group_size, A, ldA, B, ldB, R, ldR, C, ldC, stream, st);
+    case 32: return launch_oft<32>(m, n, k, group_size, A, ldA, B, ldB, R, ldR, C, ldC, stream, st);
+    case 64: return launch_oft<64>(m, n, k, group_size, A, ldA, B, ldB, R, ldR, C, ldC, stream, st);
+    case 128: return launch_oft<128>(m, n, k, group_size, A, ldA, B, ldB, R, ldR, C, ldC, stream, st);
+    default: return fail(B200_EUNSUPPORTED, "reconn_sz=%d not compiled in (16, 32, 64, 128)", b);
+  }
+}
+
+int stage_reserve(DeviceState* st, int slot, size_t bytes) {
+  if (st->stage_bytes[slot] >= bytes) return B200_OK;
+  if (st->stage[slot]) CUDA_TRY(cudaFree(st->stage[slot]));
+  st->stage[slot] = nullptr;
+  st->stage_bytes[slot] = 0;
+  CUDA_TRY(cudaMalloc(&st->stage[slot], bytes));
+  st->stage_bytes[slot] = bytes;
+  return B200_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+int b200_oft_tn_f16(int m, int n, int k, int group_size, int reconn_sz, const void* A, int ldA, const void* B, int ldB,
+                    const void* R, int ldR, void* C, int ldC, void* stream) {
+  return oft_dispatch(m, n, k, group_size, reconn_sz, A, ldA, B, ldB, R, ldR, C, ldC, static_cast<cudaStream_t>(stream));
+}
+
+int b200_oft_tn_f16_host(int m, int n, int k, int group_size, int reconn_sz, const void* A, int ldA, const void* B, int ldB,
+                         const void* R, int ldR, void* C, int ldC) {
+  g_err.clear();
+  if (int rc = common_dims(m, n, k, A, B, C)) return rc;
+  if (reconn_sz <= 0 || group_size <= 0 || n % group_size != 0) return fail(B200_EINVAL, "bad group_size / reconn_sz");
+  if (ldA < k || ldB < k || ldR < k || ldC < n) return fail(B200_EINVAL, "leading dimension smaller than the row length");
+  if (m == 0 || n == 0) return B200_OK;
+  DeviceState* st;
+  if (int rc = device_state(&st)) return rc;
+  std::lock_guard<std::mutex> lock(g_host_mu);
+  if (!st->host_stream) CUDA_TRY(cudaStreamCreateWithFlags(&st->host_stream, cudaStreamNonBlocking));
+  cudaStream_t s = st->host_stream;
+  const int r_rows = (n / group_size) * reconn_sz;
+  const int kp = (k + 7) & ~7, np = (n + 7) & ~7;  // device copies are packed with 16-byte aligned rows
+  if (int rc = stage_reserve(st, 0, static_cast<size_t>(m) * kp * 2 + 16)) return rc;
+  if (int rc = stage_reserve(st, 1, static_cast<size_t>(n) * kp * 2 + 16)) return rc;
+  if (int rc = stage_reserve(st, 2, static_cast<size_t>(r_rows) * kp * 2 + 16)) return rc;
+  if (int rc = stage_reserve(st, 3, static_cast<size_t>(m) * np * 2 + 16)) return rc;
+  if (k > 0) {
+    CUDA_TRY(cudaMemcpy2DAsync(st->stage[0], kp * 2, A, static_cast<size_t>(ldA) * 2, static_cast<size_t>(k) * 2, m, cudaMemcpyHostToDevice, s));
+    CUDA_TRY(cudaMemcpy2DAsync(st->stage[1], kp * 2, B, static_cast<size_t>(ldB) * 2, static_cast<size_t>(k) * 2, n, cudaMemcpyHostToDevice, s));
+    CUDA_TRY(cudaMemcpy2DAsync(st->stage[2], kp * 2, R, static_cast<size_t>(ldR) * 2, static_cast<size_t>(k) * 2, r_rows, cudaMemcpyHostToDevice, s));
+  }
+  if (int rc = oft_dispatch(m, n, k, group_size, reconn_sz, st->stage[0], kp, st->stage[1], kp, st->stage[2], kp, st->stage[3], np, s)) return rc;
+  CUDA_TRY(cudaMemcpy2DAsync(C, static_cast<size_t>(ldC) * 2, st->stage[3], np * 2, static_cast<size_t>(n) * 2, m, cudaMemcpyDeviceToHost, s));
+  CUDA_TRY(cudaStreamSynchronize(s));
+  return B200_OK;
+}
+
+int b200_gemm_tn_f16(int m, int n, int k, const void* A, int ldA, const void* B, int ldB, void* C, int ldC, void* stream) {
+  return launch_gemm<__half, __half, false, Params<half, half, MMA_T, MMA_N>>(m, n, k, A, ldA, B, ldB, C, ldC, stream);
+}
+int b200_gemm_nt_f16(int m, int n, int k, const void* A, int ldA, const void* B, int ldB, void* C, int ldC, void* stream) {
+  return launch_gemm<__half, __half, true, Params<half, half, MMA_N, MMA_T>>(m, n, k, A, ldA, B, ldB, C, ldC, stream);
+}
+int b200_gemm_tn_tf32(int m, int n, int k, const void* A, int ldA, const void* B, int ldB, void* C, int ldC, void* stream) {
+  return launch_gemm<float, float, false, Params<float, float, MMA_T, MMA_N>>(m, n, k, A, ldA, B, ldB, C, ldC, stream);
+}
+int b200_gemm_nt_tf32(int m, int n, int k, const void* A, int ldA, const void* B, int ldB, void* C, int ldC, void* stream) {
+  return launch_gemm<float, float, true, Params<float, float, MMA_N, MMA_T>>(m, n, k, A, ldA, B, ldB, C, ldC, stream);
+}
+
+int b200_gemm(char transA, char transB, int is_float, int m, int n, int k, const void* A, int ldA, const void* B, int ldB,
+              void* C, int ldC, void* stream) {
+  const bool tn = (transA == 'T' || transA == 't') && (transB == 'N' || transB == 'n');
+  const bool nt = (transA == 'N' || transA == 'n') && (transB == 'T' || transB == 't');
+  if (tn) return is_float ? b200_gemm_tn_tf32(m, n, k, A, ldA, B, ldB, C, ldC, stream) : b200_gemm_tn_f16(m, n, k, A, ldA, B, ldB, C, ldC, stream);
+  if (nt) return is_float ? b200_gemm_nt_tf32(m, n, k, A, ldA, B, ldB, C, ldC, stream) : b200_gemm_nt_f16(m, n, k, A, ldA, B, ldB, C, ldC, stream);
+  return fail(B200_EUNSUPPORTED, "gemm('%c','%c'): only ('T','N') and ('N','T') exist, as in the reference", transA, transB);
+}
+
+int b200_tile_coord(unsigned tiles_m, unsigned tiles_n, unsigned idx, unsigned* tile_m, unsigned* tile_n) {
+  g_err.clear();
+  if (!tile_m || !tile_n || tiles_m == 0 || tiles_n == 0 || idx >= tiles_m * tiles_n) return fail(B200_EINVAL, "tile index out of range");
+  b200::tile_coord(tiles_m, tiles_n, idx, *tile_m, *tile_n);
+  return B200_OK;
+}
+
+int b200_device_status(int out[4]) {
+  g_err.clear();
+  DeviceState* st;
+  if (int rc = device_state(&st)) return rc;
+  CUDA_TRY(cudaDeviceSynchronize());
+  int host[4] = {0, 0, 0, 0};
+  CUDA_TRY(cudaMemcpy(host, st->status, sizeof host, cudaMemcpyDeviceToHost));
+  if (out) std::memcpy(out, host, sizeof host);
+  if (host[0] != 0) {
+    CUDA_TRY(cudaMemset(st->status, 0, sizeof host));
+    return fail(B200_EDEVICE, "a bounded wait ran out in CTA %d at wait site %d (parity %d)", host[1], host[2], host[3]);
+  }
+  return B200_OK;
+}
+
+const char* b200_kernel_info(void) {
+  static char buf[768];
+  using PH = Params<half, half, MMA_T, MMA_N>;
+  using PF = Params<float, float, MMA_N, MMA_T>;
+  using O64 = OftTraits<64, CurrCompParams::bN, CurrCompParams::bP1, CurrCompParams::bP2>;
+  using O128 = OftTraits<128, CurrCompParams::bN, CurrCompParams::bP1, CurrCompParams::bP2>;
+  snprintf(buf, sizeof buf,
+           "{\"arch\": \"sm_100a\", \"gemm_half_tn\": {\"bM\": %d, \"bN\": %d, \"bK\": %d, \"bP\": %d}, "
+           "\"gemm_float_nt\": {\"bM\": %d, \"bN\": %d, \"bK\": %d, \"bP\": %d}, "
+           "\"oft\": {\"bM\": %d, \"bN\": %d, \"bK\": %d, \"bP1\": %d, \"bP2\": %d, \"threads\": %d, "
+           "\"b64\": {\"smem\": %d, \"tmem_cols\": %d, \"xr_acc_bufs\": %d, \"xr_h_bufs\": %d}, "
+           "\"b128\": {\"smem\": %d, \"tmem_cols\": %d, \"xr_acc_bufs\": %d, \"xr_h_bufs\": %d}}}",
+           PH::bM, PH::bN, PH::bK, PH::bP, PF::bM, PF::bN, PF::bK, PF::bP, (int)CurrCompParams::bM, (int)CurrCompParams::bN,
+           (int)CurrCompParams::bK, (int)CurrCompParams::bP1, (int)CurrCompParams::bP2, O64::kThreads, O64::kSmemBytes,
+           O64::kTmemUsed, O64::kXrAccBufs, O64::kXrHBufs, O128::kSmemBytes, O128::kTmemUsed, O128::kXrAccBufs, O128::kXrHBufs);
+  return buf;
+}
+
+const char* b200_last_error(void) { return g_err.c_str(); }
+
+int b200_shutdown(void) {
+  g_err.clear();
+  std::lock_guard<std::mutex> lock(g_mu);
+  int cur = 0;
+  cudaGetDevice(&cur);
+  for (int d = 0; d < kMaxDevices; ++d) {
+    DeviceState& st = g_dev[d];
+    if (!st.ready) continue;
+    cudaSetDevice(d);
+    cudaFree(st.status);
+    for (int i = 0; i < 4; ++i) cudaFree(st.stage[i]);
+    if (st.host_stream) cudaStreamDestroy(st.host_stream);
+    st = DeviceState{};
+  }
+  cudaSetDevice(cur);
+  return B200_OK;
+}
+
+}  // extern "C"

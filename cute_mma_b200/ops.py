@@ -1,0 +1,151 @@
+"""Host-side mirror of the reference operator surface over the C ABI (ctypes).
+
+Names and argument order follow the reference launchers:
+  oft_tn(m, n, k, A, ldA, B, ldB, R, ldR, C, ldC, stream)        cute_oft_coop_pc.hpp:17-23
+  gemm_tn / gemm_nt(m, n, k, A, ldA, B, ldB, C, ldC, stream)     gemm_sm80_tc.cu:163-168 / 95-100
+  gemm(transA, transB, m, n, k, ...)                             gemm_sm80_tc.cu:393-398
+with the reference's compile-time KernelParams (group_size, reconn_sz) as keyword arguments.
+Matrix arguments are device pointers: anything with ``data_ptr()`` (a torch tensor) or an int.
+Where the reference throws std::runtime_error from GEMM_CHECK_CUDA (common.hpp:8-14), these raise
+``Error`` carrying the library's status code and message.  There is no CPU fallback: if the CUDA
+library is missing, importing works but the first call raises.
+"""
+from __future__ import annotations
+
+import ctypes
+import json
+import os
+
+_PKG = os.path.dirname(os.path.abspath(__file__))
+_LIB_ENV = "CUTE_MMA_B200_LIB"
+
+OK, EINVAL, EUNSUPPORTED, ECUDA, EDEVICE = 0, 1, 2, 3, 4
+
+# every symbol include/cute_mma_b200.h declares
+SYMBOLS = (
+    "b200_oft_tn_f16", "b200_oft_tn_f16_host", "b200_gemm_tn_f16", "b200_gemm_nt_f16", "b200_gemm_tn_tf32",
+    "b200_gemm_nt_tf32", "b200_gemm", "b200_tile_coord", "b200_device_status", "b200_kernel_info",
+    "b200_last_error", "b200_shutdown",
+)
+
+
+class Error(RuntimeError):
+    def __init__(self, code: int, message: str):
+        super().__init__(f"cute_mma_b200 status {code}: {message}")
+        self.code = code
+        self.message = message
+
+
+_lib = None
+
+
+def library_path() -> str:
+    return os.environ.get(_LIB_ENV) or os.path.join(_PKG, "libcute_mma_b200.so")
+
+
+def load_library(path: str | None = None):
+    """Loads the CUDA library (built by ``python -m cute_mma_b200.build``).  Fails loudly if absent."""
+    global _lib
+    if _lib is not None and path is None:
+        return _lib
+    p = path or library_path()
+    if not os.path.exists(p):
+        raise FileNotFoundError(f"{p} not found: build it with `python -m cute_mma_b200.build` (no CPU fallback exists)")
+    lib = ctypes.CDLL(p)
+    i, vp, c = ctypes.c_int, ctypes.c_void_p, ctypes.c_char
+    lib.b200_oft_tn_f16.argtypes = [i, i, i, i, i, vp, i, vp, i, vp, i, vp, i, vp]
+    lib.b200_oft_tn_f16_host.argtypes = [i, i, i, i, i, vp, i, vp, i, vp, i, vp, i]
+    for name in ("b200_gemm_tn_f16", "b200_gemm_nt_f16", "b200_gemm_tn_tf32", "b200_gemm_nt_tf32"):
+        getattr(lib, name).argtypes = [i, i, i, vp, i, vp, i, vp, i, vp]
+    lib.b200_gemm.argtypes = [c, c, i, i, i, i, vp, i, vp, i, vp, i, vp]
+    lib.b200_tile_coord.argtypes = [ctypes.c_uint, ctypes.c_uint, ctypes.c_uint, ctypes.POINTER(ctypes.c_uint), ctypes.POINTER(ctypes.c_uint)]
+    lib.b200_device_status.argtypes = [ctypes.POINTER(ctypes.c_int)]
+    lib.b200_kernel_info.restype = ctypes.c_char_p
+    lib.b200_last_error.restype = ctypes.c_char_p
+    for name in SYMBOLS:
+        if name not in ("b200_kernel_info", "b200_last_error"):
+            getattr(lib, name).restype = ctypes.c_int
+    if path is None:
+        _lib = lib
+    return lib
+
+
+def _ptr(x) -> int:
+    if x is None:
+        return 0
+    if hasattr(x, "data_ptr"):
+        return int(x.data_ptr())
+    if hasattr(x, "ctypes"):  # numpy array: host memory, only valid for the *_host entry point
+        return int(x.ctypes.data)
+    return int(x)
+
+
+def _stream(s) -> int:
+    if s is None:
+        return 0
+    if hasattr(s, "cuda_stream"):
+        return int(s.cuda_stream)
+    return int(s)
+
+
+def _check(lib, rc: int) -> None:
+    if rc != OK:
+        raise Error(rc, lib.b200_last_error().decode())
+
+
+def oft_tn(m, n, k, A, ldA, B, ldB, R, ldR, C, ldC, stream=None, *, group_size=None, reconn_sz=8, lib=None) -> None:
+    """C[m,n] = (A[m,k] . R) . B^T on the current CUDA device, asynchronous on ``stream``.
+    group_size defaults to n (one block-diagonal R for all of N)."""
+    lib = lib or load_library()
+    gs = n if group_size is None else group_size
+    _check(lib, lib.b200_oft_tn_f16(m, n, k, gs, reconn_sz, _ptr(A), ldA, _ptr(B), ldB, _ptr(R), ldR, _ptr(C), ldC, _stream(stream)))
+
+
+def oft_tn_host(m, n, k, A, ldA, B, ldB, R, ldR, C, ldC, *, group_size=None, reconn_sz=8, lib=None) -> None:
+    """Same product on HOST buffers (numpy arrays or host addresses); synchronous."""
+    lib = lib or load_library()
+    gs = n if group_size is None else group_size
+    _check(lib, lib.b200_oft_tn_f16_host(m, n, k, gs, reconn_sz, _ptr(A), ldA, _ptr(B), ldB, _ptr(R), ldR, _ptr(C), ldC))
+
+
+def _gemm(fn_name, m, n, k, A, ldA, B, ldB, C, ldC, stream, lib):
+    lib = lib or load_library()
+    _check(lib, getattr(lib, fn_name)(m, n, k, _ptr(A), ldA, _ptr(B), ldB, _ptr(C), ldC, _stream(stream)))
+
+
+def gemm_tn(m, n, k, A, ldA, B, ldB, C, ldC, stream=None, *, dtype="half", lib=None) -> None:
+    """C(i,j) = sum_l A[i*ldA+l] B[j*ldB+l], C column-major.  dtype 'half' or 'float' (TF32)."""
+    _gemm("b200_gemm_tn_f16" if dtype == "half" else "b200_gemm_tn_tf32", m, n, k, A, ldA, B, ldB, C, ldC, stream, lib)
+
+
+def gemm_nt(m, n, k, A, ldA, B, ldB, C, ldC, stream=None, *, dtype="half", lib=None) -> None:
+    """C(i,j) = sum_l A[i+l*ldA] B[j+l*ldB], C column-major."""
+    _gemm("b200_gemm_nt_f16" if dtype == "half" else "b200_gemm_nt_tf32", m, n, k, A, ldA, B, ldB, C, ldC, stream, lib)
+
+
+def gemm(transA, transB, m, n, k, A, ldA, B, ldB, C, ldC, stream=None, *, dtype="half", lib=None) -> None:
+    lib = lib or load_library()
+    _check(lib, lib.b200_gemm(transA.encode(), transB.encode(), 0 if dtype == "half" else 1, m, n, k, _ptr(A), ldA,
+                              _ptr(B), ldB, _ptr(C), ldC, _stream(stream)))
+
+
+def tile_coord(tiles_m: int, tiles_n: int, idx: int, lib=None):
+    lib = lib or load_library()
+    tm, tn = ctypes.c_uint(0), ctypes.c_uint(0)
+    _check(lib, lib.b200_tile_coord(tiles_m, tiles_n, idx, ctypes.byref(tm), ctypes.byref(tn)))
+    return tm.value, tn.value
+
+
+def device_status(lib=None, raise_on_error: bool = True):
+    """Synchronises the device and returns the kernels' status record [code, cta, site, parity]."""
+    lib = lib or load_library()
+    out = (ctypes.c_int * 4)()
+    rc = lib.b200_device_status(out)
+    if rc != OK and raise_on_error:
+        raise Error(rc, lib.b200_last_error().decode())
+    return list(out)
+
+
+def kernel_info(lib=None) -> dict:
+    lib = lib or load_library()
+    return json.loads(lib.b200_kernel_info().decode())

@@ -1,0 +1,84 @@
+/*
+ * C ABI of the B200 (sm_100a) GEMM / OFT library.  Plain pointers and sizes only.
+ *
+ * Every entry point returns 0 on success or one of the B200_E* codes; b200_last_error() then
+ * describes the failure of the calling thread's last call.  Unless stated otherwise all matrix
+ * pointers are caller-owned DEVICE memory, calls are asynchronous on `stream` (a cudaStream_t passed
+ * as void*, NULL = default stream) and the library keeps no reference to the buffers after return.
+ * Requirements common to all compute calls: base pointers of A, B, R aligned to 16 bytes and
+ * leading dimensions whose byte size is a multiple of 16 (they are read through TMA descriptors);
+ * C needs only natural alignment.  M, N, K need not be multiples of the tile.
+ */
+#ifndef CUTE_MMA_B200_H_
+#define CUTE_MMA_B200_H_
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+enum {
+  B200_OK = 0,
+  B200_EINVAL = 1,        /* bad pointer, size, alignment or leading dimension */
+  B200_EUNSUPPORTED = 2,  /* shape class not compiled into this build (e.g. block edge) */
+  B200_ECUDA = 3,         /* a CUDA runtime / driver call failed */
+  B200_EDEVICE = 4        /* a kernel reported a bounded wait that ran out (see b200_device_status) */
+};
+
+/* Fused OFT product  C[m,n] = (A[m,k] . R) . B^T  with block-diagonal R.
+ * Replaces oft_tn<KernelParams> (cute_oft_coop_pc.hpp:17-23, cute_oft_coop_pc.cu:505-577); the
+ * reference's compile-time KernelParams::group_size / reconn_sz are the run-time arguments
+ * group_size / reconn_sz here (the C++ shim cute_mma_b200/shim/cute_oft_coop_pc.hpp restores the template form).
+ *   A [m][k] ldA, B [n][k] ldB (= W^T), R [(n/group_size)*reconn_sz][k] ldR, C [m][n] ldC, all fp16,
+ *   all row-major; stored R block (g,kb) = rows g*b.., cols kb*b.. holds the TRANSPOSE of the
+ *   mathematical rotation.  fp32 accumulation, X.R rounded to fp16 (RNE) before the main product.
+ * reconn_sz in {16, 32, 64, 128}; k % reconn_sz == 0; n % group_size == 0; group_size == n or a
+ * multiple of the kernel's N tile. */
+int b200_oft_tn_f16(int m, int n, int k, int group_size, int reconn_sz,
+                    const void* A, int ldA, const void* B, int ldB, const void* R, int ldR,
+                    void* C, int ldC, void* stream);
+
+/* Same product with HOST buffers: copies A, B, R to the device, runs the kernel, copies C back and
+ * synchronises before returning.  Device staging buffers are owned and reused by the library.
+ * This is the call the end-to-end figure of bench.py times. */
+int b200_oft_tn_f16_host(int m, int n, int k, int group_size, int reconn_sz,
+                         const void* A, int ldA, const void* B, int ldB, const void* R, int ldR,
+                         void* C, int ldC);
+
+/* Plain GEMM  C(i,j) = sum_l A(i,l) B(j,l),  C column-major: C(i,j) at C[i + j*ldC].
+ * Replace gemm_tn / gemm_nt<TO,TR> (gemm_sm80_tc.cu:163-228 / 95-160).
+ *   tn: A(i,l) at A[i*ldA + l], B(j,l) at B[j*ldB + l]   (both K-contiguous)
+ *   nt: A(i,l) at A[i + l*ldA], B(j,l) at B[j + l*ldB]   (M- / N-contiguous)
+ * f16: fp16 in, fp32 accumulate, fp16 out.  tf32: fp32 in consumed as TF32 by the tensor cores
+ * (low 13 mantissa bits ignored), fp32 accumulate and out. */
+int b200_gemm_tn_f16(int m, int n, int k, const void* A, int ldA, const void* B, int ldB, void* C, int ldC, void* stream);
+int b200_gemm_nt_f16(int m, int n, int k, const void* A, int ldA, const void* B, int ldB, void* C, int ldC, void* stream);
+int b200_gemm_tn_tf32(int m, int n, int k, const void* A, int ldA, const void* B, int ldB, void* C, int ldC, void* stream);
+int b200_gemm_nt_tf32(int m, int n, int k, const void* A, int ldA, const void* B, int ldB, void* C, int ldC, void* stream);
+
+/* Dispatcher of gemm(char transA, char transB, ...) (gemm_sm80_tc.cu:393-418): ('T','N') -> tn,
+ * ('N','T') -> nt; lower-case letters select the same kernels (the reference's *_test variants are
+ * an alternative shared-memory path of the same operator).  is_float: 0 = half/half, 1 = float/float. */
+int b200_gemm(char transA, char transB, int is_float, int m, int n, int k,
+              const void* A, int ldA, const void* B, int ldB, void* C, int ldC, void* stream);
+
+/* Tile visiting order of the persistent kernels; same order as z_curve(grid, idx) (z_curve.hpp:28-49). */
+int b200_tile_coord(unsigned tiles_m, unsigned tiles_n, unsigned idx, unsigned* tile_m, unsigned* tile_n);
+
+/* Synchronises the current device and reads the kernels' status record:
+ * out[0] = 0 ok / 1 a bounded wait ran out, out[1] = CTA, out[2] = wait site, out[3] = parity.
+ * Clears the record.  Returns B200_EDEVICE when out[0] != 0. */
+int b200_device_status(int out[4]);
+
+/* Compile-time configuration of this build as a short JSON string (tile sizes, ring depths). */
+const char* b200_kernel_info(void);
+
+/* Text of the calling thread's last error ("" if none). */
+const char* b200_last_error(void);
+
+/* Frees the per-device workspaces and staging buffers. */
+int b200_shutdown(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* CUTE_MMA_B200_H_ */

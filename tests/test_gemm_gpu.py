@@ -1,0 +1,158 @@
+"""GPU parity of gemm_tn / gemm_nt (half and float/TF32) against the fp64 truth, through the C ABI."""
+import numpy as np
+import pytest
+
+from _util import TF32_TOL, oft_ok, tf32_ok
+from cute_mma_b200 import inputs, ops
+from oracle import oracle
+
+pytestmark = pytest.mark.gpu
+
+
+def run_gemm(lib, cuda, layout, dtype, m, n, k, A, B, ldA, ldB, ldC):
+    import torch
+
+    tdt = torch.float16 if dtype == "half" else torch.float32
+    dA = torch.from_numpy(A).to(cuda)
+    dB = torch.from_numpy(B).to(cuda)
+    dC = torch.full((n + 1, ldC), -7.0, dtype=tdt, device=cuda)  # column-major: n columns of ldC elements
+    fn = ops.gemm_tn if layout == "TN" else ops.gemm_nt
+    fn(m, n, k, dA, ldA, dB, ldB, dC, ldC, dtype=dtype, lib=lib)
+    assert ops.device_status(lib)[0] == 0
+    out = dC.cpu().numpy()
+    assert np.all(out[n, :] == -7.0), "column past the end of C was written"
+    if ldC > m:
+        assert np.all(out[:n, m:] == -7.0), "padding rows of C were written"
+    return out[:n, :m].T.copy()  # -> [m, n]
+
+
+def make_operands(layout, dtype, m, n, k, seed, ldA=None, ldB=None, dist="uniform"):
+    npdt = np.float16 if dtype == "half" else np.float32
+    gen = (lambda shape, s: inputs.uniform_pm1(shape, s, npdt)) if dist == "uniform" else (lambda shape, s: inputs.normal(shape, s, 1.0, npdt))
+    if layout == "TN":   # A [m][ldA>=k], B [n][ldB>=k]
+        ldA, ldB = ldA or k, ldB or k
+        A = np.zeros((m, ldA), npdt); A[:, :k] = gen((m, k), seed)
+        B = np.zeros((n, ldB), npdt); B[:, :k] = gen((n, k), seed + 1)
+        a_rows, b_cols = A[:, :k], B[:, :k]
+    else:                # A [k][ldA>=m], B [k][ldB>=n]
+        ldA, ldB = ldA or m, ldB or n
+        A = np.zeros((k, ldA), npdt); A[:, :m] = gen((k, m), seed)
+        B = np.zeros((k, ldB), npdt); B[:, :n] = gen((k, n), seed + 1)
+        a_rows, b_cols = A[:, :m].T, B[:, :n].T
+    return A, B, ldA, ldB, a_rows, b_cols
+
+
+def truth(layout, m, n, k, A, ldA, B, ldB, rows, cols, tf32_mode=0):
+    ta, tb = ("T", "N") if layout == "TN" else ("N", "T")
+    return oracle.gemm_f64_sampled(ta, tb, m, n, k, A, ldA, B, ldB, rows, cols, tf32_mode=tf32_mode)
+
+
+SHAPES = [(128, 256, 64), (128, 256, 512), (384, 512, 256), (200, 328, 136), (72, 40, 64), (640, 1280, 1024)]
+
+
+@pytest.mark.parametrize("layout", ["TN", "NT"])
+@pytest.mark.parametrize("m,n,k", SHAPES)
+def test_gemm_half(lib, cuda, layout, m, n, k):
+    A, B, ldA, ldB, _, _ = make_operands(layout, "half", m, n, k, seed=1)
+    got = run_gemm(lib, cuda, layout, "half", m, n, k, A, B, ldA, ldB, ldC=m)
+    ref = truth(layout, m, n, k, A, ldA, B, ldB, np.arange(m), np.arange(n))
+    bad, worst = oft_ok(got, ref)  # fp16 in / fp32 accumulate / fp16 out: |c-ref| <= 1e-2 (|ref|+1)
+    assert bad == 0, (bad, worst)
+    # fp32 accumulation leaves only the final fp16 rounding: much tighter than the stated bound
+    assert worst < 2e-3, worst
+
+
+@pytest.mark.parametrize("layout", ["TN", "NT"])
+@pytest.mark.parametrize("m,n,k", SHAPES)
+def test_gemm_float_tf32(lib, cuda, layout, m, n, k):
+    A, B, ldA, ldB, a_rows, b_cols = make_operands(layout, "float", m, n, k, seed=2, dist="normal")
+    got = run_gemm(lib, cuda, layout, "float", m, n, k, A, B, ldA, ldB, ldC=m)
+    ref = truth(layout, m, n, k, A, ldA, B, ldB, np.arange(m), np.arange(n))
+    bad, worst = tf32_ok(got, ref, a_rows, b_cols, k)
+    assert bad == 0, (bad, worst)
+    # against operands truncated to TF32 the result must be far closer (fp32 accumulation only)
+    ref_t = truth(layout, m, n, k, A, ldA, B, ldB, np.arange(m), np.arange(n), tf32_mode=1)
+    bad_t, worst_t = tf32_ok(got, ref_t, a_rows, b_cols, k, tol=2e-4)
+    assert bad_t == 0, (bad_t, worst_t)
+
+
+@pytest.mark.parametrize("layout,dtype", [("TN", "half"), ("NT", "half"), ("TN", "float"), ("NT", "float")])
+def test_gemm_padded_leading_dimensions(lib, cuda, layout, dtype):
+    m, n, k = 200, 328, 136
+    pad = 8 if dtype == "half" else 4
+    base = (k, k) if layout == "TN" else (m, n)
+    A, B, ldA, ldB, a_rows, b_cols = make_operands(layout, dtype, m, n, k, seed=3, ldA=base[0] + pad, ldB=base[1] + 2 * pad)
+    got = run_gemm(lib, cuda, layout, dtype, m, n, k, A, B, ldA, ldB, ldC=m + 5)
+    ref = truth(layout, m, n, k, A, ldA, B, ldB, np.arange(m), np.arange(n))
+    if dtype == "half":
+        bad, worst = oft_ok(got, ref)
+    else:
+        bad, worst = tf32_ok(got, ref, a_rows, b_cols, k)
+    assert bad == 0, (bad, worst)
+
+
+def test_gemm_dispatcher_and_errors(lib, cuda):
+    import torch
+
+    m, n, k = 128, 256, 64
+    A, B, ldA, ldB, _, _ = make_operands("TN", "half", m, n, k, seed=4)
+    dA, dB = torch.from_numpy(A).to(cuda), torch.from_numpy(B).to(cuda)
+    c1 = torch.empty((n, m), dtype=torch.float16, device=cuda)
+    c2 = torch.empty((n, m), dtype=torch.float16, device=cuda)
+    ops.gemm("T", "N", m, n, k, dA, ldA, dB, ldB, c1, m, lib=lib)
+    ops.gemm("t", "n", m, n, k, dA, ldA, dB, ldB, c2, m, lib=lib)
+    ops.gemm_tn(m, n, k, dA, ldA, dB, ldB, c2, m, lib=lib)
+    assert ops.device_status(lib)[0] == 0
+    assert torch.equal(c1, c2)
+    with pytest.raises(ops.Error) as e:
+        ops.gemm("N", "N", m, n, k, dA, ldA, dB, ldB, c1, m, lib=lib)
+    assert e.value.code == ops.EUNSUPPORTED
+    with pytest.raises(ops.Error) as e:  # misaligned base pointer
+        ops.gemm_tn(m, n, k, dA.data_ptr() + 2, ldA, dB, ldB, c1, m, lib=lib)
+    assert e.value.code == ops.EINVAL
+
+
+def _sampled(lib, cuda, layout, dtype, m, n, k, seed, dist):
+    import torch
+
+    g = torch.Generator(device=cuda).manual_seed(seed)
+    tdt = torch.float16 if dtype == "half" else torch.float32
+    shapeA, shapeB = ((m, k), (n, k)) if layout == "TN" else ((k, m), (k, n))
+    if dist == "uniform":
+        dA = (torch.rand(shapeA, generator=g, device=cuda) * 2 - 1).to(tdt)
+        dB = (torch.rand(shapeB, generator=g, device=cuda) * 2 - 1).to(tdt)
+    else:
+        dA = torch.randn(shapeA, generator=g, device=cuda).to(tdt)
+        dB = torch.randn(shapeB, generator=g, device=cuda).to(tdt)
+    dC = torch.empty((n, m), dtype=tdt, device=cuda)
+    fn = ops.gemm_tn if layout == "TN" else ops.gemm_nt
+    fn(m, n, k, dA, shapeA[1], dB, shapeB[1], dC, m, dtype=dtype, lib=lib)
+    assert ops.device_status(lib)[0] == 0
+    rng = np.random.default_rng(seed)
+    rows = np.unique(np.concatenate([[0, 127, 128, m - 1], rng.integers(0, m, 60)]))
+    cols = np.unique(np.concatenate([[0, 255, 256, n - 1], rng.integers(0, n, 60)]))
+    A, B = dA.cpu().numpy(), dB.cpu().numpy()
+    ref = truth(layout, m, n, k, A, shapeA[1], B, shapeB[1], rows, cols)
+    got = dC.cpu().numpy().T[np.ix_(rows, cols)]
+    if dtype == "half":
+        bad, worst = oft_ok(got, ref)
+    else:
+        a_rows = A[rows] if layout == "TN" else A[:, rows].T
+        b_cols = B[cols] if layout == "TN" else B[:, cols].T
+        bad, worst = tf32_ok(got, ref, a_rows, b_cols, k)
+    assert bad == 0, (bad, worst)
+    # size-independent property: a second launch is bitwise identical
+    dC2 = torch.empty_like(dC)
+    fn(m, n, k, dA, shapeA[1], dB, shapeB[1], dC2, m, dtype=dtype, lib=lib)
+    assert ops.device_status(lib)[0] == 0
+    assert torch.equal(dC, dC2)
+
+
+def test_gemm_half_tn_8192_sampled(lib, cuda):
+    """gemm_half TN, M=N=K=8192, U(-1,1): full size on the GPU, fp64 truth on sampled rows x columns."""
+    _sampled(lib, cuda, "TN", "half", 8192, 8192, 8192, 21, "uniform")
+
+
+def test_gemm_float_nt_4096_sampled(lib, cuda):
+    """gemm_float NT on TF32 tensor cores, M=N=K=4096, N(0,1)."""
+    _sampled(lib, cuda, "NT", "float", 4096, 4096, 4096, 22, "normal")

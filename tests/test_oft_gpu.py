@@ -1,0 +1,185 @@
+"""GPU parity of the fused OFT kernel against the CPU oracle, through the C ABI."""
+import numpy as np
+import pytest
+
+from _util import make_oft_case, oft_ok, truth_ok
+from cute_mma_b200 import ops
+from oracle import oracle
+
+pytestmark = pytest.mark.gpu
+
+
+def run_oft(lib, cuda, A, R, B, m, n, k, b, group_size=None, ldA=None, ldB=None, ldR=None, ldC=None, canary=True):
+    """Uploads the operands (optionally with padded leading dimensions), runs b200_oft_tn_f16 and
+    returns C[m,n] as numpy.  The padding of C is filled with a canary and must come back untouched."""
+    import torch
+
+    ldA, ldB, ldR, ldC = ldA or k, ldB or k, ldR or k, ldC or n
+
+    def up(x, ld):
+        rows = x.shape[0]
+        buf = torch.full((rows, ld), float("nan"), dtype=torch.float16, device=cuda)
+        buf[:, : x.shape[1]] = torch.from_numpy(x).to(cuda)
+        return buf
+
+    dA, dB, dR = up(A, ldA), up(B, ldB), up(R, ldR)
+    dC = torch.full((m + 1, ldC), -7.0, dtype=torch.float16, device=cuda)  # one canary row + canary columns
+    ops.oft_tn(m, n, k, dA, ldA, dB, ldB, dR, ldR, dC, ldC, group_size=group_size, reconn_sz=b, lib=lib)
+    st = ops.device_status(lib)
+    assert st[0] == 0, st
+    out = dC.cpu().numpy()
+    if canary:
+        assert np.all(out[m, :] == np.float16(-7.0)), "row past the end of C was written"
+        if ldC > n:
+            assert np.all(out[:m, n:] == np.float16(-7.0)), "padding columns of C were written"
+    return out[:m, :n].copy()
+
+
+def oracle_full(A, R, B, m, n, k, b, group_size=None):
+    gs = n if group_size is None else group_size
+    return oracle.cpu_oft_tn(A, R, B, m, gs, n // gs, k, b, threads=oracle.num_threads())
+
+
+CASES = [
+    # m, n, k, b, group_size
+    (128, 256, 64, 64, None),      # one tile, one unit
+    (128, 256, 256, 64, None),     # one tile, several units
+    (384, 512, 512, 64, None),     # several tiles per CTA order
+    (384, 512, 512, 32, None),
+    (384, 512, 512, 16, None),
+    (256, 512, 512, 128, None),
+    (512, 1024, 1024, 32, None),   # the CPU-oracle configuration: 32 blocks of 32x32
+    (200, 328, 192, 64, None),     # ragged M and N
+    (136, 264, 96, 32, None),      # K not a multiple of the 64-wide stage
+    (72, 40, 128, 16, None),       # smaller than one tile
+    (256, 512, 256, 32, 256),      # two N-groups, each with its own R
+    (128, 768, 128, 16, 256),      # three groups
+]
+
+
+@pytest.mark.parametrize("m,n,k,b,gs", CASES)
+def test_oft_matches_oracle(lib, cuda, m, n, k, b, gs):
+    A, R, B = make_oft_case(m, n, k, b, gs, seed=0, kind="qr")
+    ref = oracle_full(A, R, B, m, n, k, b, gs)
+    got = run_oft(lib, cuda, A, R, B, m, n, k, b, gs)
+    truth = oracle.oft_f64(A, R, B, m, n if gs is None else gs, 1 if gs is None else n // gs, k, b, round_xr=True)
+    bad, worst = oft_ok(got, ref, truth=truth)
+    assert bad == 0, f"{bad} elements outside 1e-2*(|ref|+1) + oracle drift; worst normalised error {worst:.3e}"
+    bad_t, worst_t = truth_ok(got, truth)
+    assert bad_t == 0, f"{bad_t} elements further than 2e-3*(|y|+1) from exact arithmetic; worst {worst_t:.3e}"
+    if k // b <= 8:  # few re-roundings in the oracle: the stated tolerance holds without any allowance
+        assert oft_ok(got, ref)[0] == 0
+
+
+def test_oft_padded_leading_dimensions(lib, cuda):
+    m, n, k, b = 200, 328, 192, 64
+    A, R, B = make_oft_case(m, n, k, b, seed=3)
+    ref = oracle_full(A, R, B, m, n, k, b)
+    got = run_oft(lib, cuda, A, R, B, m, n, k, b, ldA=k + 8, ldB=k + 16, ldR=k + 24, ldC=n + 8)
+    bad, worst = oft_ok(got, ref)
+    assert bad == 0, (bad, worst)
+    # ldC not a multiple of 8 elements: the epilogue must take its scalar path
+    got2 = run_oft(lib, cuda, A, R, B, m, n, k, b, ldC=n + 3)
+    assert np.array_equal(got.view(np.uint16), got2.view(np.uint16))
+
+
+def test_oft_permutation_blocks_reference_check(lib, cuda):
+    """The reference's own correctness protocol (cute_oft_pc.cu:195-236, 334-350): positive inputs,
+    permutation blocks, count of elements above 5e-3 relative error must be zero."""
+    m, n, k, b = 256, 512, 512, 32
+    A, R, B = make_oft_case(m, n, k, b, seed=5, kind="perm", xdist="u01")
+    ref = oracle_full(A, R, B, m, n, k, b)
+    got = run_oft(lib, cuda, A, R, B, m, n, k, b)
+    errors, worst = oracle.check_result(got, ref, 5e-3)
+    assert errors == 0, (errors, worst)
+
+
+def test_oft_zero_one_init_is_bit_exact(lib, cuda):
+    """--01init (cute_oft_pc.cu:202-216): every partial sum is a small integer, exact in fp16 and
+    fp32, so the kernel must agree with the oracle bit for bit (K <= 2048 keeps sums <= 2048)."""
+    m, n, k, b = 256, 512, 256, 64
+    A, R, B = make_oft_case(m, n, k, b, seed=7, kind="perm", xdist="01")
+    ref = oracle_full(A, R, B, m, n, k, b)
+    got = run_oft(lib, cuda, A, R, B, m, n, k, b)
+    assert np.array_equal(got.view(np.uint16), ref.view(np.uint16))
+
+
+def test_oft_structured_block_known_answer(lib, cuda):
+    """Known-answer block (idea of playgrounds/bd_construct.cu:117-159): with R_math = I + e0 1^T,
+    (x R)[q] = x[q] + x[0] per block, so Y = X' W with X' computed in closed form.  A transposed-R
+    bug would instead add the block's row sum to column 0."""
+    m, n, k, b = 128, 256, 128, 32
+    A, R, B = make_oft_case(m, n, k, b, seed=9, kind="structured", xdist="01")
+    Xp = A.astype(np.float64).reshape(m, k // b, b).copy()
+    Xp += Xp[:, :, :1]
+    expect = Xp.reshape(m, k) @ B.astype(np.float64).T
+    got = run_oft(lib, cuda, A, R, B, m, n, k, b)
+    assert np.array_equal(got.astype(np.float64), expect)  # integers below 2048: exact
+
+
+def test_oft_is_deterministic(lib, cuda):
+    m, n, k, b = 384, 512, 512, 64
+    A, R, B = make_oft_case(m, n, k, b, seed=11)
+    a = run_oft(lib, cuda, A, R, B, m, n, k, b)
+    c = run_oft(lib, cuda, A, R, B, m, n, k, b)
+    assert np.array_equal(a.view(np.uint16), c.view(np.uint16))
+
+
+def test_oft_k_zero_and_empty(lib, cuda):
+    import torch
+
+    dC = torch.full((8, 16), 3.0, dtype=torch.float16, device=cuda)
+    d = torch.zeros(16, dtype=torch.float16, device=cuda)
+    ops.oft_tn(8, 16, 0, d, 8, d, 8, d, 8, dC, 16, reconn_sz=16, lib=lib)   # K = 0: C = 0 like cpu_oft_tn
+    assert torch.all(dC == 0)
+    ops.oft_tn(0, 16, 64, d, 64, d, 64, d, 64, dC, 16, reconn_sz=16, lib=lib)  # M = 0: nothing to do
+    assert ops.device_status(lib)[0] == 0
+
+
+def _sampled_parity(lib, cuda, m, n, k, b, kind, wsigma, n_rows, seed):
+    """Full-size run on the GPU from device-generated operands; the oracle recomputes sampled rows
+    (an output row depends only on its own row of X, all of R and all of W)."""
+    import torch
+    from cute_mma_b200 import inputs
+
+    g = torch.Generator(device=cuda).manual_seed(seed)
+    dA = torch.randn((m, k), generator=g, device=cuda, dtype=torch.float32).to(torch.float16)
+    dB = (torch.randn((n, k), generator=g, device=cuda, dtype=torch.float32) * wsigma).to(torch.float16)
+    blocks = inputs.blocks_cayley(1, k // b, b, seed) if kind == "cayley" else inputs.blocks_qr(1, k // b, b, seed)
+    R = inputs.pack_r(blocks)
+    dR = torch.from_numpy(R).to(cuda)
+    dC = torch.empty((m, n), dtype=torch.float16, device=cuda)
+    ops.oft_tn(m, n, k, dA, k, dB, k, dR, k, dC, n, reconn_sz=b, lib=lib)
+    assert ops.device_status(lib)[0] == 0
+    rows = np.unique(np.concatenate([[0, 127, 128, m - 1], np.random.default_rng(seed).integers(0, m, n_rows)]))
+    idx = torch.from_numpy(rows).to(cuda)
+    A_s = dA[idx].cpu().numpy()
+    got = dC[idx].cpu().numpy()
+    ref = oracle.cpu_oft_tn(A_s, R, dB.cpu().numpy(), len(rows), n, 1, k, b, threads=oracle.num_threads())
+    bad, worst = oft_ok(got, ref)
+    assert bad == 0, (bad, worst)
+    truth = oracle.oft_f64(A_s, R, dB.cpu().numpy(), len(rows), n, 1, k, b, round_xr=True)
+    bad_t, worst_t = truth_ok(got, truth)
+    assert bad_t == 0, (bad_t, worst_t)
+    # size-independent property over the whole output: linearity in X.  Scaling by 2 commutes with
+    # every rounding except for fp16 subnormals (|XR| or |Y| below 2^-14), so all but a sliver of the
+    # elements must match bit for bit and the rest within one fp16 ulp.
+    dC2 = torch.empty_like(dC)
+    dA2 = dA * 2
+    ops.oft_tn(m, n, k, dA2, k, dB, k, dR, k, dC2, n, reconn_sz=b, lib=lib)
+    assert ops.device_status(lib)[0] == 0
+    twice = dC.float() * 2
+    diff = (dC2.float() - twice).abs()
+    assert bool((diff <= twice.abs() * 2.0 ** -10 + 2.0 ** -13).all())
+    assert float((diff != 0).float().mean()) < 1e-3
+
+
+def test_oft_projection_shape_sampled(lib, cuda):
+    """M=16384, K=N=4096, b=64, Cayley blocks, X~N(0,1), W~N(0,0.02): the headline configuration."""
+    _sampled_parity(lib, cuda, 16384, 4096, 4096, 64, "cayley", 0.02, 40, seed=4)
+
+
+def test_oft_large_slab_sampled(lib, cuda):
+    """One GPU's slab of the N-sharded large configuration at 8 GPUs (N = 28672/8 = 3584), K = 8192,
+    b = 128, QR blocks; M reduced to 8192 rows to keep the run short (rows are independent)."""
+    _sampled_parity(lib, cuda, 8192, 3584, 8192, 128, "qr", 0.02, 12, seed=5)
