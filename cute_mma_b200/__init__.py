@@ -13,5 +13,7 @@ from .ops import (  # noqa: F401
     load_library,
     oft_tn,
     oft_tn_host,
+    shard_range,
+    tile_coord,
     kernel_info,
 )

@@ -60,6 +60,38 @@ def build(config_dir: str = DEFAULT_CONFIG, out: str = DEFAULT_OUT, verbose: boo
     return out
 
 
+CLI_DIR = os.path.join(PKG, "cli")
+BIN_DIR = os.path.join(PKG, "bin")
+# executable -> (source, extra defines); names follow the reference's targets (README.md:18-21, CMakeLists.txt:69-80)
+CLI_TARGETS = {
+    "cute_oft_pc": ("cute_oft_pc.cu", []),
+    "gemm_half_half": ("gemm_bench.cu", []),
+    "gemm_float_float": ("gemm_bench.cu", ["-DGEMM_FLOAT"]),
+}
+
+
+def build_cli(lib: str = DEFAULT_OUT, defines: list[str] | None = None, out_dir: str = BIN_DIR, force: bool = False) -> list[str]:
+    """Builds the C++ benchmark drivers against the library (found at run time through an rpath)."""
+    os.makedirs(out_dir, exist_ok=True)
+    outs = []
+    lib_dir, lib_name = os.path.dirname(os.path.abspath(lib)), os.path.basename(lib)
+    for exe, (src, defs) in CLI_TARGETS.items():
+        out = os.path.join(out_dir, exe)
+        src_path = os.path.join(CLI_DIR, src)
+        deps = [src_path, os.path.join(CLI_DIR, "flags.hpp"), lib] + [os.path.join(PKG, "shim", f) for f in os.listdir(os.path.join(PKG, "shim"))]
+        if not force and os.path.exists(out) and all(os.path.getmtime(d) <= os.path.getmtime(out) for d in deps):
+            outs.append(out)
+            continue
+        cmd = [nvcc_path(), "-gencode", "arch=compute_100a,code=sm_100a", "-std=c++17", "-O3", "-lineinfo", *defs, *(defines or []),
+               src_path, "-o", out, f"-L{lib_dir}", f"-l:{lib_name}", "-Xlinker", f"-rpath={lib_dir}", "-lcudart"]
+        res = subprocess.run(cmd, capture_output=True, text=True)
+        if res.returncode != 0:
+            sys.stderr.write(res.stdout + res.stderr)
+            raise RuntimeError("nvcc failed: " + " ".join(cmd))
+        outs.append(out)
+    return outs
+
+
 if __name__ == "__main__":
     ap = argparse.ArgumentParser()
     ap.add_argument("--config-dir", default=DEFAULT_CONFIG)

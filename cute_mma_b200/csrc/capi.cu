@@ -272,6 +272,25 @@ int b200_gemm(char transA, char transB, int is_float, int m, int n, int k, const
   return fail(B200_EUNSUPPORTED, "gemm('%c','%c'): only ('T','N') and ('N','T') exist, as in the reference", transA, transB);
 }
 
+int b200_shard_range(int n, int group_size, int world, int rank, int* n_begin, int* n_end) {
+  g_err.clear();
+  if (n < 0 || group_size <= 0 || world <= 0 || rank < 0 || rank >= world || !n_begin || !n_end)
+    return fail(B200_EINVAL, "bad shard arguments (n=%d group_size=%d world=%d rank=%d)", n, group_size, world, rank);
+  // Slabs are cut on multiples of `unit` columns: whole N-groups when R differs per group, otherwise
+  // whole 256-column tiles so that every rank keeps full tiles; the remainder goes to the low ranks.
+  const int unit = (group_size < n) ? group_size : 256;
+  const int units = (n + unit - 1) / unit;
+  const int base = units / world, extra = units % world;
+  const long long u0 = static_cast<long long>(rank) * base + (rank < extra ? rank : extra);
+  const long long u1 = u0 + base + (rank < extra ? 1 : 0);
+  long long b0 = u0 * unit, b1 = u1 * unit;
+  if (b0 > n) b0 = n;
+  if (b1 > n) b1 = n;
+  *n_begin = static_cast<int>(b0);
+  *n_end = static_cast<int>(b1);
+  return B200_OK;
+}
+
 int b200_tile_coord(unsigned tiles_m, unsigned tiles_n, unsigned idx, unsigned* tile_m, unsigned* tile_n) {
   g_err.clear();
   if (!tile_m || !tile_n || tiles_m == 0 || tiles_n == 0 || idx >= tiles_m * tiles_n) return fail(B200_EINVAL, "tile index out of range");

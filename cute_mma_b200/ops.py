@@ -24,7 +24,7 @@ OK, EINVAL, EUNSUPPORTED, ECUDA, EDEVICE = 0, 1, 2, 3, 4
 # every symbol include/cute_mma_b200.h declares
 SYMBOLS = (
     "b200_oft_tn_f16", "b200_oft_tn_f16_host", "b200_gemm_tn_f16", "b200_gemm_nt_f16", "b200_gemm_tn_tf32",
-    "b200_gemm_nt_tf32", "b200_gemm", "b200_tile_coord", "b200_device_status", "b200_kernel_info",
+    "b200_gemm_nt_tf32", "b200_gemm", "b200_shard_range", "b200_tile_coord", "b200_device_status", "b200_kernel_info",
     "b200_last_error", "b200_shutdown",
 )
 
@@ -58,6 +58,7 @@ def load_library(path: str | None = None):
     for name in ("b200_gemm_tn_f16", "b200_gemm_nt_f16", "b200_gemm_tn_tf32", "b200_gemm_nt_tf32"):
         getattr(lib, name).argtypes = [i, i, i, vp, i, vp, i, vp, i, vp]
     lib.b200_gemm.argtypes = [c, c, i, i, i, i, vp, i, vp, i, vp, i, vp]
+    lib.b200_shard_range.argtypes = [i, i, i, i, ctypes.POINTER(i), ctypes.POINTER(i)]
     lib.b200_tile_coord.argtypes = [ctypes.c_uint, ctypes.c_uint, ctypes.c_uint, ctypes.POINTER(ctypes.c_uint), ctypes.POINTER(ctypes.c_uint)]
     lib.b200_device_status.argtypes = [ctypes.POINTER(ctypes.c_int)]
     lib.b200_kernel_info.restype = ctypes.c_char_p
@@ -127,6 +128,14 @@ def gemm(transA, transB, m, n, k, A, ldA, B, ldB, C, ldC, stream=None, *, dtype=
     lib = lib or load_library()
     _check(lib, lib.b200_gemm(transA.encode(), transB.encode(), 0 if dtype == "half" else 1, m, n, k, _ptr(A), ldA,
                               _ptr(B), ldB, _ptr(C), ldC, _stream(stream)))
+
+
+def shard_range(n: int, group_size: int, world: int, rank: int, lib=None):
+    """[n_begin, n_end) of the N columns owned by ``rank`` (whole groups / whole 256-column tiles)."""
+    lib = lib or load_library()
+    a, b = ctypes.c_int(0), ctypes.c_int(0)
+    _check(lib, lib.b200_shard_range(n, group_size, world, rank, ctypes.byref(a), ctypes.byref(b)))
+    return a.value, b.value
 
 
 def tile_coord(tiles_m: int, tiles_n: int, idx: int, lib=None):

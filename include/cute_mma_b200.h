@@ -61,6 +61,13 @@ int b200_gemm_nt_tf32(int m, int n, int k, const void* A, int ldA, const void* B
 int b200_gemm(char transA, char transB, int is_float, int m, int n, int k,
               const void* A, int ldA, const void* B, int ldB, void* C, int ldC, void* stream);
 
+/* Column range [n_begin, n_end) of B (rows of the stored [n][k] matrix) and of C owned by `rank` when
+ * the product is sharded along N over `world` GPUs, A and R replicated.  The reference has no
+ * multi-GPU path; the partition follows its group structure (cpu_oft.hpp:52-93: columns of one
+ * N-group share an R, so slabs never split a group; with a single group they are cut on 256-column
+ * tiles).  Pure host arithmetic, no CUDA call. */
+int b200_shard_range(int n, int group_size, int world, int rank, int* n_begin, int* n_end);
+
 /* Tile visiting order of the persistent kernels; same order as z_curve(grid, idx) (z_curve.hpp:28-49). */
 int b200_tile_coord(unsigned tiles_m, unsigned tiles_n, unsigned idx, unsigned* tile_m, unsigned* tile_n);
 
