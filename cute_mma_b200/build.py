@@ -45,10 +45,11 @@ def _stale(out: str, config_dir: str) -> bool:
     return any(os.path.getmtime(d) > t for d in deps if os.path.exists(d))
 
 
-def build(config_dir: str = DEFAULT_CONFIG, out: str = DEFAULT_OUT, verbose: bool = False, force: bool = False) -> str:
+def build(config_dir: str = DEFAULT_CONFIG, out: str = DEFAULT_OUT, verbose: bool = False, force: bool = False,
+          defines: list[str] | None = None) -> str:
     if not force and not _stale(out, config_dir):
         return out
-    cmd = [nvcc_path(), *NVCC_FLAGS, f"-I{config_dir}", f"-I{CSRC}"]
+    cmd = [nvcc_path(), *NVCC_FLAGS, f"-I{config_dir}", f"-I{CSRC}", *(defines or [])]
     if verbose:
         cmd += ["-Xptxas", "-v"]
     cmd += sources() + ["-o", out, "-lcudart"]
@@ -98,5 +99,6 @@ if __name__ == "__main__":
     ap.add_argument("--out", default=DEFAULT_OUT)
     ap.add_argument("--verbose", action="store_true")
     ap.add_argument("--force", action="store_true")
+    ap.add_argument("-D", dest="defines", action="append", default=[], help="extra macro, e.g. -D B200_PROFILE_WAITS")
     a = ap.parse_args()
-    print(build(a.config_dir, a.out, a.verbose, a.force))
+    print(build(a.config_dir, a.out, a.verbose, a.force, [f"-D{d}" for d in a.defines]))

@@ -51,6 +51,8 @@ struct DeviceState {
   size_t stage_bytes[4] = {0, 0, 0, 0};
   cudaStream_t host_stream = nullptr;
 };
+// workspace layout: kStatusInts ints of status, then 2 * kWaitSites 64-bit wait-profile counters
+constexpr size_t kWorkspaceBytes = kStatusInts * sizeof(int) + 2 * kWaitSites * sizeof(unsigned long long);
 DeviceState g_dev[kMaxDevices];
 std::mutex g_mu;        // guards g_dev initialisation
 std::mutex g_host_mu;   // serialises the host-buffer entry point (it owns the staging buffers)
@@ -72,8 +74,8 @@ int device_state(DeviceState** out) {
     if (prop.major != 10)
       return fail(B200_EUNSUPPORTED, "device %d is sm_%d%d; this library contains sm_100a code only", dev, prop.major, prop.minor);
     st.sm_count = prop.multiProcessorCount;
-    CUDA_TRY(cudaMalloc(&st.status, 4 * sizeof(int)));
-    CUDA_TRY(cudaMemset(st.status, 0, 4 * sizeof(int)));
+    CUDA_TRY(cudaMalloc(&st.status, kWorkspaceBytes));
+    CUDA_TRY(cudaMemset(st.status, 0, kWorkspaceBytes));
     if (!g_encode) {
       void* fn = nullptr;
       cudaDriverEntryPointQueryResult q;
@@ -313,6 +315,23 @@ int b200_device_status(int out[4]) {
   return B200_OK;
 }
 
+int b200_wait_profile(unsigned long long* out, int n) {
+  g_err.clear();
+#ifdef B200_PROFILE_WAITS
+  DeviceState* st;
+  if (int rc = device_state(&st)) return rc;
+  if (!out || n < 0 || n > 2 * kWaitSites) return fail(B200_EINVAL, "out must hold at most %d counters", 2 * kWaitSites);
+  CUDA_TRY(cudaDeviceSynchronize());
+  CUDA_TRY(cudaMemcpy(out, st->status + kStatusInts, static_cast<size_t>(n) * sizeof(unsigned long long), cudaMemcpyDeviceToHost));
+  CUDA_TRY(cudaMemset(st->status + kStatusInts, 0, 2 * kWaitSites * sizeof(unsigned long long)));
+  return B200_OK;
+#else
+  (void)out;
+  (void)n;
+  return fail(B200_EUNSUPPORTED, "this build has no wait profiling (compile with -DB200_PROFILE_WAITS)");
+#endif
+}
+
 const char* b200_kernel_info(void) {
   static char buf[768];
   using PH = Params<half, half, MMA_T, MMA_N>;
@@ -323,11 +342,11 @@ const char* b200_kernel_info(void) {
            "{\"arch\": \"sm_100a\", \"gemm_half_tn\": {\"bM\": %d, \"bN\": %d, \"bK\": %d, \"bP\": %d}, "
            "\"gemm_float_nt\": {\"bM\": %d, \"bN\": %d, \"bK\": %d, \"bP\": %d}, "
            "\"oft\": {\"bM\": %d, \"bN\": %d, \"bK\": %d, \"bP1\": %d, \"bP2\": %d, \"threads\": %d, "
-           "\"b64\": {\"smem\": %d, \"tmem_cols\": %d, \"xr_acc_bufs\": %d, \"xr_h_bufs\": %d}, "
-           "\"b128\": {\"smem\": %d, \"tmem_cols\": %d, \"xr_acc_bufs\": %d, \"xr_h_bufs\": %d}}}",
+           "\"b64\": {\"smem\": %d, \"tmem_cols\": %d, \"xr_bufs\": %d}, "
+           "\"b128\": {\"smem\": %d, \"tmem_cols\": %d, \"xr_bufs\": %d}}}",
            PH::bM, PH::bN, PH::bK, PH::bP, PF::bM, PF::bN, PF::bK, PF::bP, (int)CurrCompParams::bM, (int)CurrCompParams::bN,
            (int)CurrCompParams::bK, (int)CurrCompParams::bP1, (int)CurrCompParams::bP2, O64::kThreads, O64::kSmemBytes,
-           O64::kTmemUsed, O64::kXrAccBufs, O64::kXrHBufs, O128::kSmemBytes, O128::kTmemUsed, O128::kXrAccBufs, O128::kXrHBufs);
+           O64::kTmemUsed, O64::kXrBufs, O128::kSmemBytes, O128::kTmemUsed, O128::kXrBufs);
   return buf;
 }
 

@@ -64,6 +64,9 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem_gen + T::kStages * T::kStageBytes + T::kNumBars * 8);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
   const WaitCtx ctx{abort_flag, args.status, kWaitLimitNs};
+#ifdef B200_PROFILE_WAITS
+  const long long kernel_c0 = clock64();
+#endif
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const unsigned tiles_m = (args.m + T::kBM - 1) / T::kBM, tiles_n = (args.n + T::kBN - 1) / T::kBN;
@@ -193,6 +196,14 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
   }
 
   // ---------------------------------------------------------------------- teardown
+#ifdef B200_PROFILE_WAITS
+  if (threadIdx.x == 0) {  // site 63: cycles this CTA ran
+    ctx.prof_cycles[7] += static_cast<unsigned long long>(clock64() - kernel_c0);
+    ctx.prof_count[7] += 1u;
+    ctx.prof_site[7] = 63;
+  }
+#endif
+  wait_profile_flush(ctx);
   __syncthreads();
   if (*abort_flag) {
     // Give copies and MMAs that were already issued time to land before shared and tensor memory go away.

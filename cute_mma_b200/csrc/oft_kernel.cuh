@@ -5,15 +5,15 @@
 // The reference hands one b-wide slice of A.R from producer warps to consumer warps through shared
 // memory and named barriers, once per b (= 8) columns of K.  Here the rotated slice never leaves the
 // SM's tensor memory:
-//   MMA1   XRacc[128 x U] (fp32, TMEM)  = A_tile[128 x U] . Rblk^T           (tcgen05.mma, N = b)
-//   cvt    XR16 [128 x U] (fp16, TMEM)  = round-to-nearest-even(XRacc)         (tcgen05.ld / st)
-//   MMA2   acc  [128 x bN] (fp32, TMEM) += XR16 . B_tile[bN x U]^T             (A operand from TMEM)
+//   MMA1   XR[128 x U] (fp32, TMEM)     = A_tile[128 x U] . Rblk^T           (tcgen05.mma, N = b)
+//   cvt    XR[128 x U] (fp16, TMEM)     = round-to-nearest-even(XR), in place  (tcgen05.ld / st)
+//   MMA2   acc[128 x bN] (fp32, TMEM)  += XR . B_tile[bN x U]^T                (A operand from TMEM)
 // with U = max(b, 64) columns of K per "unit".  Warp roles:
 //   warp 0      TMA producer of the {A, R} ring        warp 1      TMA producer of the {B} ring
-//   warp 2      issues both MMAs                       warp 3      allocates / frees tensor memory
+//   warp 2      issues MMA1                            warp 3      owns tensor memory, issues MMA2
 //   warps 4..7  fp32 -> fp16 conversion of XR          warps 8..11 epilogue (TMEM -> fp16 -> C)
-// MMA1 of unit u+L is issued ahead of MMA2 of unit u, so the conversion of unit u+1.. overlaps the
-// main contraction.  All hand-offs are mbarriers with bounded waits.
+// MMA1 runs ahead of MMA2 by as many units as there are XR buffers in tensor memory, so the conversion of
+// the next units overlaps the main contraction.  All hand-offs are mbarriers with bounded waits.
 #pragma once
 #include "ptx.cuh"
 
@@ -33,21 +33,20 @@ struct OftTraits {
   static constexpr int kRBytes = kB * 128;             // R tile: b rows (q) x 64 columns of K
   static constexpr int kS1Bytes = kABytes + kRBytes;
   static constexpr int kS2Bytes = kBN * 128;
-  // tensor-memory budget (512 columns of 32 bits per SM)
-  static constexpr int kXrAccBufs = (kBN + 2 * kUnitK + 2 * (kUnitK / 2) <= 512) ? 2 : 1;
-  static constexpr int kXrHBufs = (kBN + kXrAccBufs * kUnitK + 3 * (kUnitK / 2) <= 512) ? 3 : 2;
-  static constexpr int kLookahead = kXrAccBufs;        // MMA1 runs this many units ahead of MMA2
+  // tensor-memory budget (512 columns of 32 bits per SM): the accumulator plus as many XR buffers
+  // as fit.  One XR buffer holds a unit twice in turn: first the fp32 result of MMA1 (kUnitK columns),
+  // then, converted in place, its fp16 image in the first kUnitK/2 columns, which MMA2 reads as A.
+  static constexpr int kXrBufs = (512 - kBN) / kUnitK;
   static constexpr int kColAcc = 0;
-  static constexpr int kColXrAcc = kBN;
-  static constexpr int kColXrH = kBN + kXrAccBufs * kUnitK;
-  static constexpr int kTmemUsed = kColXrH + kXrHBufs * (kUnitK / 2);
+  static constexpr int kColXr = kBN;
+  static constexpr int kTmemUsed = kBN + kXrBufs * kUnitK;
   static constexpr int kTmemCols = 512;
   static constexpr int kThreads = 384;
-  static constexpr int kNumBars = 2 * kS1 + 2 * kS2 + 2 * kXrAccBufs + 2 * kXrHBufs + 2;
+  static constexpr int kNumBars = 2 * kS1 + 2 * kS2 + 3 * kXrBufs + 2;
   static constexpr int kSmemBytes = kS1 * kS1Bytes + kS2 * kS2Bytes + kNumBars * 8 + 64 + 1024;
   static_assert(kB == 16 || kB == 32 || kB == 64 || kB == 128, "block edge must be 16, 32, 64 or 128");
   static_assert(kBN % 32 == 0 && kBN >= 32 && kBN <= 256, "bN must be a multiple of 32 up to 256");
-  static_assert(kTmemUsed <= kTmemCols, "tensor memory budget exceeded");
+  static_assert(kTmemUsed <= kTmemCols && kXrBufs >= 2, "tensor memory budget exceeded");
   static_assert(kSmemBytes <= 232448, "shared memory rings too large");
   static_assert(kRBytes % 1024 == 0, "R tile must keep the next tile 1024-byte aligned");
 };
@@ -74,15 +73,17 @@ oft_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ C
   const uint32_t empty1 = bars + 8u * bi; bi += T::kS1;        // {A,R} stage read by MMA1 (commit)
   const uint32_t full2 = bars + 8u * bi;  bi += T::kS2;        // {B} stage filled
   const uint32_t empty2 = bars + 8u * bi; bi += T::kS2;        // {B} stage read by MMA2
-  const uint32_t xa_full = bars + 8u * bi;  bi += T::kXrAccBufs;   // XRacc written by MMA1
-  const uint32_t xa_empty = bars + 8u * bi; bi += T::kXrAccBufs;   // XRacc read by the converters
-  const uint32_t xh_full = bars + 8u * bi;  bi += T::kXrHBufs;     // XR16 written by the converters
-  const uint32_t xh_empty = bars + 8u * bi; bi += T::kXrHBufs;     // XR16 read by MMA2
+  const uint32_t x_acc = bars + 8u * bi;   bi += T::kXrBufs;   // XR buffer holds the fp32 result of MMA1 (commit)
+  const uint32_t x_half = bars + 8u * bi;  bi += T::kXrBufs;   // XR buffer holds the fp16 image (converters)
+  const uint32_t x_empty = bars + 8u * bi; bi += T::kXrBufs;   // XR buffer read by MMA2 (commit)
   const uint32_t acc_full = bars + 8u * bi;  bi += 1;
   const uint32_t acc_empty = bars + 8u * bi; bi += 1;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem_gen + (bars - smem_base) + T::kNumBars * 8);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
   const WaitCtx ctx{abort_flag, args.status, kWaitLimitNs};
+#ifdef B200_PROFILE_WAITS
+  const long long kernel_c0 = clock64();
+#endif
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const unsigned tiles_m = (args.m + T::kBM - 1) / T::kBM, tiles_n = (args.n + T::kBN - 1) / T::kBN;
@@ -96,8 +97,7 @@ oft_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ C
     *abort_flag = 0;
     for (int s = 0; s < T::kS1; ++s) { mbar_init(full1 + 8 * s, 1); mbar_init(empty1 + 8 * s, 1); }
     for (int s = 0; s < T::kS2; ++s) { mbar_init(full2 + 8 * s, 1); mbar_init(empty2 + 8 * s, 1); }
-    for (int i = 0; i < T::kXrAccBufs; ++i) { mbar_init(xa_full + 8 * i, 1); mbar_init(xa_empty + 8 * i, 128); }
-    for (int i = 0; i < T::kXrHBufs; ++i) { mbar_init(xh_full + 8 * i, 128); mbar_init(xh_empty + 8 * i, 1); }
+    for (int i = 0; i < T::kXrBufs; ++i) { mbar_init(x_acc + 8 * i, 1); mbar_init(x_half + 8 * i, 128); mbar_init(x_empty + 8 * i, 1); }
     mbar_init(acc_full, 1);
     mbar_init(acc_empty, 128);
     fence_mbar_init();
@@ -115,8 +115,14 @@ oft_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ C
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
+  // The epilogue keeps a whole accumulator row (bN/2 packed registers) per thread; the copy / issue
+  // warps need few registers and the converters a moderate number, so the warpgroups trade registers.
+  // (each role issues its own setmaxnreg at the top of its branch: warps 0..3 give registers up,
+  // warps 4..7 keep a moderate number, warps 8..11 take the rest)
+
   if (warp == 0) {
     // -------------------------------------------------------------- producer of the {A, R} ring
+    setmaxnreg_dec<96>();
     if (lane == 0) {
       uint32_t it = 0;
       bool ok = true;
@@ -138,6 +144,7 @@ oft_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ C
     __syncwarp();
   } else if (warp == 1) {
     // -------------------------------------------------------------- producer of the {B} ring
+    setmaxnreg_dec<96>();
     if (lane == 0) {
       uint32_t it = 0;
       bool ok = true;
@@ -155,93 +162,107 @@ oft_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ C
     }
     __syncwarp();
   } else if (warp == 2) {
-    // -------------------------------------------------------------- MMA issuer
+    // -------------------------------------------------------------- issuer of MMA1: XRacc = A_tile . Rblk^T
+    // The two MMAs have their own issuing threads: one thread cannot issue both at the rate the
+    // tensor pipe retires them, and the mbarriers already carry every ordering between the two.
+    setmaxnreg_dec<96>();
     if (lane == 0) {
       constexpr uint32_t idesc1 = umma_idesc(kFmtF16, 0, 0, T::kBM, T::kB);
-      constexpr uint32_t idesc2 = umma_idesc(kFmtF16, 0, 0, T::kBM, T::kBN);
-      uint32_t it1 = 0, it2 = 0;  // stage counters of the two rings as consumed by MMA1 / MMA2
+      const uint64_t a_desc0 = umma_desc_sw128(ring1, 16, 1024), r_desc0 = umma_desc_sw128(ring1 + T::kABytes, 16, 1024);
+      int s = 0, xb = 0;
+      uint32_t ph_s = 0, ph_xb = 0;
       bool ok = true;
-      // g enumerates this CTA's units over all of its tiles; MMA1 leads MMA2 by kLookahead units.
-      for (unsigned g = 0; ok && g < total_units + T::kLookahead; ++g) {
-        if (g < total_units) {
-          // ---- MMA1(g): XRacc = A_tile . Rblk^T
-          const int xa = g % T::kXrAccBufs;
-          if (!(ok = mbar_wait(xa_empty + 8 * xa, ((g / T::kXrAccBufs) & 1) ^ 1, ctx, 20))) break;
-          const uint32_t d1 = tmem_base + T::kColXrAcc + xa * T::kUnitK;
+      for (unsigned g = 0; ok && g < total_units; ++g) {
+        if (!(ok = mbar_wait(x_empty + 8 * xb, ph_xb ^ 1, ctx, 20))) break;  // MMA2 is done with this buffer
+        tc_fence_after();
+        const uint32_t d1 = tmem_base + T::kColXr + xb * T::kUnitK;
 #pragma unroll
-          for (int su = 0; su < T::kStagesPerUnit; ++su, ++it1) {
-            const int s = it1 % T::kS1;
-            if (!(ok = mbar_wait(full1 + 8 * s, (it1 / T::kS1) & 1, ctx, 21))) break;
-            tc_fence_after();
-            const uint32_t a_src = ring1 + s * T::kS1Bytes;
-            const uint64_t a_desc = umma_desc_sw128(a_src, 16, 1024), r_desc = umma_desc_sw128(a_src + T::kABytes, 16, 1024);
-#pragma unroll
-            for (int kk = 0; kk < T::kBK / 16; ++kk) {
-              // b < 64: the stage holds 64/b diagonal blocks; slice kk belongs to block (kk*16)/b and
-              // lands in XRacc columns [blk*b, blk*b+b).  b >= 64: one block, accumulated over the unit.
-              const int blk = (T::kB < 64) ? (kk * 16) / T::kB : 0;
-              const uint32_t accum = (T::kB < 64) ? (((kk * 16) % T::kB) != 0) : ((su > 0 || kk > 0) ? 1u : 0u);
-              umma_f16_ss(d1 + blk * T::kB, umma_desc_advance(a_desc, kk * 32), umma_desc_advance(r_desc, kk * 32), idesc1, accum);
-            }
-            umma_commit(empty1 + 8 * s);
-          }
-          if (!ok) break;
-          umma_commit(xa_full + 8 * xa);
-        }
-        if (g >= static_cast<unsigned>(T::kLookahead)) {
-          // ---- MMA2(u): acc += XR16 . B_tile^T
-          const unsigned u = g - T::kLookahead;
-          const int ku = u % units;  // unit index inside its tile
-          const int xh = u % T::kXrHBufs;
-          if (ku == 0) {
-            const unsigned t = u / units;
-            if (!(ok = mbar_wait(acc_empty, (t & 1) ^ 1, ctx, 22))) break;
-          }
-          if (!(ok = mbar_wait(xh_full + 8 * xh, (u / T::kXrHBufs) & 1, ctx, 23))) break;
+        for (int su = 0; su < T::kStagesPerUnit; ++su) {
+          if (!(ok = mbar_wait(full1 + 8 * s, ph_s, ctx, 21))) break;
           tc_fence_after();
-          const uint32_t a_tmem = tmem_base + T::kColXrH + xh * (T::kUnitK / 2);
+          const uint64_t a_desc = a_desc0 + static_cast<uint64_t>(s * (T::kS1Bytes >> 4));
+          const uint64_t r_desc = r_desc0 + static_cast<uint64_t>(s * (T::kS1Bytes >> 4));
 #pragma unroll
-          for (int su = 0; su < T::kStagesPerUnit; ++su, ++it2) {
-            const int s = it2 % T::kS2;
-            if (!(ok = mbar_wait(full2 + 8 * s, (it2 / T::kS2) & 1, ctx, 24))) break;
-            tc_fence_after();
-            const uint64_t b_desc = umma_desc_sw128(ring2 + s * T::kS2Bytes, 16, 1024);
-#pragma unroll
-            for (int kk = 0; kk < T::kBK / 16; ++kk) {
-              const uint32_t accum = (ku > 0 || su > 0 || kk > 0) ? 1u : 0u;
-              umma_f16_ts(tmem_base + T::kColAcc, a_tmem + su * (T::kBK / 2) + kk * 8, umma_desc_advance(b_desc, kk * 32), idesc2, accum);
-            }
-            umma_commit(empty2 + 8 * s);
+          for (int kk = 0; kk < T::kBK / 16; ++kk) {
+            // b < 64: the stage holds 64/b diagonal blocks; slice kk belongs to block (kk*16)/b and
+            // lands in XRacc columns [blk*b, blk*b+b).  b >= 64: one block, accumulated over the unit.
+            constexpr bool small = T::kB < 64;
+            const int blk = small ? (kk * 16) / T::kB : 0;
+            const uint32_t accum = small ? ((((kk * 16) % T::kB) != 0) ? 1u : 0u) : ((su > 0 || kk > 0) ? 1u : 0u);
+            umma_f16_ss(d1 + blk * T::kB, a_desc + kk * 2, r_desc + kk * 2, idesc1, accum);
           }
-          if (!ok) break;
-          umma_commit(xh_empty + 8 * xh);
-          if (ku == units - 1) umma_commit(acc_full);
+          umma_commit(empty1 + 8 * s);
+          if (++s == T::kS1) { s = 0; ph_s ^= 1; }
+        }
+        if (!ok) break;
+        umma_commit(x_acc + 8 * xb);
+        if (++xb == T::kXrBufs) { xb = 0; ph_xb ^= 1; }
+      }
+    }
+    __syncwarp();
+  } else if (warp == 3) {
+    // -------------------------------------------------------------- issuer of MMA2: acc += XR16 . B_tile^T
+    setmaxnreg_dec<96>();
+    if (lane == 0) {
+      constexpr uint32_t idesc2 = umma_idesc(kFmtF16, 0, 0, T::kBM, T::kBN);
+      const uint64_t b_desc0 = umma_desc_sw128(ring2, 16, 1024);
+      int s = 0, xb = 0, ku = 0;
+      uint32_t ph_s = 0, ph_xb = 0, ph_acc = 0;
+      bool ok = true;
+      for (unsigned u = 0; ok && u < total_units; ++u) {
+        if (ku == 0) {  // first unit of a tile: the epilogue must have drained the accumulator
+          if (!(ok = mbar_wait(acc_empty, ph_acc ^ 1, ctx, 22))) break;
+        }
+        if (!(ok = mbar_wait(x_half + 8 * xb, ph_xb, ctx, 23))) break;
+        tc_fence_after();
+        const uint32_t a_tmem = tmem_base + T::kColXr + xb * T::kUnitK;
+#pragma unroll
+        for (int su = 0; su < T::kStagesPerUnit; ++su) {
+          if (!(ok = mbar_wait(full2 + 8 * s, ph_s, ctx, 24))) break;
+          tc_fence_after();
+          const uint64_t b_desc = b_desc0 + static_cast<uint64_t>(s * (T::kS2Bytes >> 4));
+#pragma unroll
+          for (int kk = 0; kk < T::kBK / 16; ++kk) {
+            const uint32_t accum = (su > 0 || kk > 0) ? 1u : (ku > 0 ? 1u : 0u);
+            umma_f16_ts(tmem_base + T::kColAcc, a_tmem + su * (T::kBK / 2) + kk * 8, b_desc + kk * 2, idesc2, accum);
+          }
+          umma_commit(empty2 + 8 * s);
+          if (++s == T::kS2) { s = 0; ph_s ^= 1; }
+        }
+        if (!ok) break;
+        umma_commit(x_empty + 8 * xb);
+        if (++xb == T::kXrBufs) { xb = 0; ph_xb ^= 1; }
+        if (++ku == units) {
+          umma_commit(acc_full);
+          ku = 0;
+          ph_acc ^= 1;
         }
       }
     }
     __syncwarp();
   } else if (warp >= 4 && warp < 8) {
-    // -------------------------------------------------------------- converters: XRacc (fp32) -> XR16 (fp16)
+    // -------------------------------------------------------------- converters: fp32 -> fp16, in place
+    // Each warp owns its 32 lanes.  Columns are converted in 64-wide groups in ascending order, so the
+    // fp16 words written to columns [32h, 32h+32) only ever land on fp32 columns already in registers.
+    setmaxnreg_dec<152>();
     const int quad = warp & 3;
     const uint32_t lane_off = static_cast<uint32_t>(quad * 32) << 16;
     bool ok = true;
+    int xb = 0;
+    uint32_t ph_xb = 0;
     for (unsigned g = 0; ok && g < total_units; ++g) {
-      const int xa = g % T::kXrAccBufs, xh = g % T::kXrHBufs;
-      if (!(ok = mbar_wait_warp(xa_full + 8 * xa, (g / T::kXrAccBufs) & 1, ctx, 30))) break;
+      if (!(ok = mbar_wait_warp(x_acc + 8 * xb, ph_xb, ctx, 30))) break;
       tc_fence_after();
-      const uint32_t src = tmem_base + lane_off + T::kColXrAcc + xa * T::kUnitK;
-      const uint32_t dst = tmem_base + lane_off + T::kColXrH + xh * (T::kUnitK / 2);
+#ifdef B200_PROFILE_WAITS
+      const long long cv0 = clock64();
+#endif
+      const uint32_t buf = tmem_base + lane_off + T::kColXr + xb * T::kUnitK;
 #pragma unroll
       for (int h = 0; h < T::kUnitK / 64; ++h) {
         uint32_t v0[32], v1[32];
-        tmem_ld_x32(src + h * 64, v0);
-        tmem_ld_x32(src + h * 64 + 32, v1);
+        tmem_ld_x32(buf + h * 64, v0);
+        tmem_ld_x32(buf + h * 64 + 32, v1);
         tmem_wait_ld();
-        if (h == T::kUnitK / 64 - 1) {
-          // XRacc is free again as soon as its last columns sit in registers
-          tc_fence_before();
-          mbar_arrive(xa_empty + 8 * xa);
-        }
         uint32_t p0[16], p1[16];
 #pragma unroll
         for (int j = 0; j < 16; ++j) {
@@ -250,20 +271,20 @@ oft_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ C
           p0[j] = *reinterpret_cast<uint32_t*>(&a);
           p1[j] = *reinterpret_cast<uint32_t*>(&b);
         }
-        if (h == 0) {
-          if (!(ok = mbar_wait_warp(xh_empty + 8 * xh, ((g / T::kXrHBufs) & 1) ^ 1, ctx, 31))) break;
-          tc_fence_after();
-        }
-        tmem_st_x16(dst + h * 32, p0);
-        tmem_st_x16(dst + h * 32 + 16, p1);
+        tmem_st_x16(buf + h * 32, p0);
+        tmem_st_x16(buf + h * 32 + 16, p1);
       }
-      if (!ok) break;
       tmem_wait_st();
       tc_fence_before();
-      mbar_arrive(xh_full + 8 * xh);
+      mbar_arrive(x_half + 8 * xb);
+#ifdef B200_PROFILE_WAITS
+      if (threadIdx.x == 128) { ctx.prof_cycles[3] += clock64() - cv0; ctx.prof_count[3] += 1; ctx.prof_site[3] = 51; }  // unit converted
+#endif
+      if (++xb == T::kXrBufs) { xb = 0; ph_xb ^= 1; }
     }
   } else if (warp >= 8) {
     // -------------------------------------------------------------- epilogue: acc -> fp16 -> row-major C
+    setmaxnreg_inc<248>();
     const int quad = warp & 3;
     const uint32_t t_row = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + T::kColAcc;
     const bool vec_ok = ((reinterpret_cast<uintptr_t>(args.C) & 15) == 0) && ((args.ldC & 7) == 0);
@@ -276,36 +297,54 @@ oft_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ C
       tc_fence_after();
       const int row = tm * T::kBM + quad * 32 + lane;
       __half* c_row = args.C + static_cast<long long>(row) * args.ldC;
-#pragma unroll 1
+      // Drain the whole accumulator row into registers as packed fp16 first and hand the
+      // accumulator back to MMA2 before any global store is issued: the stores (one row per lane,
+      // 16 bytes per instruction) are slow and would otherwise sit on the tile-to-tile critical path.
+      uint32_t p[T::kBN / 2];
+#pragma unroll
       for (int c = 0; c < T::kBN / 32; ++c) {
         uint32_t v[32];
         tmem_ld_x32(t_row + c * 32, v);
         tmem_wait_ld();
-        const int col0 = tn * T::kBN + c * 32;
-        if (row < args.m) {
-          uint32_t p[16];
 #pragma unroll
-          for (int j = 0; j < 16; ++j) {
-            __half2 h2 = __floats2half2_rn(__uint_as_float(v[2 * j]), __uint_as_float(v[2 * j + 1]));
-            p[j] = *reinterpret_cast<uint32_t*>(&h2);
-          }
-          if (vec_ok && col0 + 32 <= args.n) {
-            uint4* dst = reinterpret_cast<uint4*>(c_row + col0);
-#pragma unroll
-            for (int q = 0; q < 4; ++q) dst[q] = make_uint4(p[4 * q], p[4 * q + 1], p[4 * q + 2], p[4 * q + 3]);
-          } else {
-#pragma unroll
-            for (int j = 0; j < 32; ++j)
-              if (col0 + j < args.n) c_row[col0 + j] = reinterpret_cast<const __half*>(p)[j];
-          }
+        for (int j = 0; j < 16; ++j) {
+          __half2 h2 = __floats2half2_rn(__uint_as_float(v[2 * j]), __uint_as_float(v[2 * j + 1]));
+          p[c * 16 + j] = *reinterpret_cast<uint32_t*>(&h2);
         }
       }
       tc_fence_before();
       mbar_arrive(acc_empty);
+      if (row < args.m) {
+#pragma unroll
+        for (int c = 0; c < T::kBN / 32; ++c) {
+          const int col0 = tn * T::kBN + c * 32;
+          if (vec_ok && col0 + 32 <= args.n) {
+            uint4* dst = reinterpret_cast<uint4*>(c_row + col0);
+#pragma unroll
+            for (int q = 0; q < 4; ++q)
+              dst[q] = make_uint4(p[c * 16 + 4 * q], p[c * 16 + 4 * q + 1], p[c * 16 + 4 * q + 2], p[c * 16 + 4 * q + 3]);
+          } else {
+#pragma unroll
+            for (int j = 0; j < 32; ++j)
+              if (col0 + j < args.n) {
+                const uint32_t w = p[c * 16 + j / 2];
+                c_row[col0 + j] = __ushort_as_half(static_cast<unsigned short>((j & 1) ? (w >> 16) : (w & 0xFFFFu)));
+              }
+          }
+        }
+      }
     }
   }
 
   // ---------------------------------------------------------------------- teardown
+#ifdef B200_PROFILE_WAITS
+  if (threadIdx.x == 0) {  // site 63: cycles this CTA ran
+    ctx.prof_cycles[7] += static_cast<unsigned long long>(clock64() - kernel_c0);
+    ctx.prof_count[7] += 1u;
+    ctx.prof_site[7] = 63;
+  }
+#endif
+  wait_profile_flush(ctx);
   __syncthreads();
   if (*abort_flag) {
     for (int i = 0; i < 200; ++i) __nanosleep(1000);

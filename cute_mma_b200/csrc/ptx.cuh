@@ -55,9 +55,18 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
 // Shared by every role of a CTA: where to raise the abort flag and where to record the failure.
 struct WaitCtx {
   volatile int* abort_flag;  // shared memory, one per CTA
-  int* status;               // global memory, 4 ints
+  int* status;               // global memory: 4 status ints, then (16-byte aligned) kWaitSites cycle counters
   unsigned long long limit_ns;
+#ifdef B200_PROFILE_WAITS
+  mutable unsigned long long prof_cycles[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+  mutable unsigned prof_count[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+  mutable int prof_site[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+#endif
 };
+// In-kernel stage timers: when the library is built with -DB200_PROFILE_WAITS every wait that
+// has to spin adds its cycles to a per-site counter (and site+64 counts those waits), read back by b200_wait_profile.
+constexpr int kWaitSites = 64;
+constexpr int kStatusInts = 4;
 
 __device__ __noinline__ void report_timeout(const WaitCtx& ctx, int site, uint32_t parity) {
   *ctx.abort_flag = 1;
@@ -71,7 +80,7 @@ __device__ __noinline__ void report_timeout(const WaitCtx& ctx, int site, uint32
 
 // Bounded wait.  Returns false when this CTA is aborting (this wait or another one ran out); the
 // caller then leaves its role loop and falls through to the common teardown.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, const WaitCtx& ctx, int site) {
+__device__ __forceinline__ bool mbar_wait_impl(uint32_t bar, uint32_t parity, const WaitCtx& ctx, int site) {
   if (mbar_try_wait(bar, parity)) return true;
   const unsigned long long t0 = globaltimer_ns();
   int it = 0;
@@ -87,11 +96,45 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, const W
   }
 }
 
+// Profiling build: every wait adds its cycles to a per-thread slot (site % 8: the sites of one role map to distinct slots), flushed to the
+// global counters once at the end of the kernel by wait_profile_flush().
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, const WaitCtx& ctx, int site) {
+#ifdef B200_PROFILE_WAITS
+  // (try_wait may itself suspend the thread for a while, so every wait is timed, not only the spins)
+  const long long c0 = clock64();
+  const bool ok = mbar_wait_impl(bar, parity, ctx, site);
+  ctx.prof_cycles[site & 7] += static_cast<unsigned long long>(clock64() - c0);
+  ctx.prof_count[site & 7] += 1u;
+  ctx.prof_site[site & 7] = site;
+  return ok;
+#else
+  return mbar_wait_impl(bar, parity, ctx, site);
+#endif
+}
+__device__ __forceinline__ void wait_profile_flush(const WaitCtx& ctx) {
+#ifdef B200_PROFILE_WAITS
+  unsigned long long* prof = reinterpret_cast<unsigned long long*>(ctx.status + kStatusInts);
+  for (int i = 0; i < 8; ++i)
+    if (ctx.prof_count[i]) {
+      atomicAdd(prof + ctx.prof_site[i], ctx.prof_cycles[i]);
+      atomicAdd(prof + kWaitSites + ctx.prof_site[i], static_cast<unsigned long long>(ctx.prof_count[i]));
+    }
+#endif
+}
+
 // Whole-warp form for roles whose next instruction is warp-collective (tcgen05.ld / st / wait):
 // every lane gets the same answer, so the warp stays converged when a wait gives up.
 __device__ __forceinline__ bool mbar_wait_warp(uint32_t bar, uint32_t parity, const WaitCtx& ctx, int site) {
   const bool ok = mbar_wait(bar, parity, ctx, site);
   return __all_sync(0xffffffffu, ok);
+}
+
+// Register re-balancing between warpgroups (all four warps of a warpgroup execute the same one).
+template <int kRegs> __device__ __forceinline__ void setmaxnreg_inc() {
+  asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(kRegs));
+}
+template <int kRegs> __device__ __forceinline__ void setmaxnreg_dec() {
+  asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kRegs));
 }
 
 // ---- TMA ----------------------------------------------------------------------------------------

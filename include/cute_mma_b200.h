@@ -76,6 +76,13 @@ int b200_tile_coord(unsigned tiles_m, unsigned tiles_n, unsigned idx, unsigned* 
  * Clears the record.  Returns B200_EDEVICE when out[0] != 0. */
 int b200_device_status(int out[4]);
 
+/* In-kernel stage timers (the reference has no tracing beyond cudaEvent timing, cute_oft_pc.cu:372-377).
+ * A library built with -DB200_PROFILE_WAITS adds, per wait site of the kernels' mbarrier protocol,
+ * the cycles spent waiting (out[site]) and the number of waits (out[64 + site]); this call
+ * synchronises the device, copies up to n <= 128 counters and clears them.  Ordinary builds return
+ * B200_EUNSUPPORTED. */
+int b200_wait_profile(unsigned long long* out, int n);
+
 /* Compile-time configuration of this build as a short JSON string (tile sizes, ring depths). */
 const char* b200_kernel_info(void);
 
