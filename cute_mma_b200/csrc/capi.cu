@@ -52,7 +52,8 @@ struct DeviceState {
   cudaStream_t host_stream = nullptr;
 };
 // workspace layout: kStatusInts ints of status, then 2 * kWaitSites 64-bit wait-profile counters
-constexpr size_t kWorkspaceBytes = kStatusInts * sizeof(int) + 2 * kWaitSites * sizeof(unsigned long long);
+constexpr int kProfileWords = 2 * kWaitSites + kTraceUnits * kTraceEvents;  // counters, then the unit trace
+constexpr size_t kWorkspaceBytes = kStatusInts * sizeof(int) + kProfileWords * sizeof(unsigned long long);
 DeviceState g_dev[kMaxDevices];
 std::mutex g_mu;        // guards g_dev initialisation
 std::mutex g_host_mu;   // serialises the host-buffer entry point (it owns the staging buffers)
@@ -162,6 +163,9 @@ int launch_oft(int m, int n, int k, int group_size, const void* A, int ldA, cons
                void* C, int ldC, cudaStream_t stream, DeviceState* st) {
   using T = OftTraits<kB, CurrCompParams::bN, CurrCompParams::bP1, CurrCompParams::bP2>;
   static_assert(CurrCompParams::bM == T::kBM && CurrCompParams::bK == T::kBK, "oft_config.hpp: bM must be 128 and bK 64");
+  if constexpr (!T::kFits) {
+    return fail(B200_EUNSUPPORTED, "reconn_sz=%d needs %d bytes of shared memory with this tile configuration (limit 232448)", kB, T::kSmemBytes);
+  } else {
   if (group_size != n && group_size % T::kBN != 0)
     return fail(B200_EUNSUPPORTED, "group_size=%d must equal n or be a multiple of the N tile %d", group_size, T::kBN);
   const int n_groups = n / group_size;
@@ -177,6 +181,7 @@ int launch_oft(int m, int n, int k, int group_size, const void* A, int ldA, cons
   kernel<<<grid, T::kThreads, T::kSmemBytes, stream>>>(ma, mr, mb, args);
   CUDA_TRY(cudaGetLastError());
   return B200_OK;
+  }
 }
 
 int oft_dispatch(int m, int n, int k, int group_size, int b, const void* A, int ldA, const void* B, int ldB, const void* R, int ldR,
@@ -320,10 +325,10 @@ int b200_wait_profile(unsigned long long* out, int n) {
 #ifdef B200_PROFILE_WAITS
   DeviceState* st;
   if (int rc = device_state(&st)) return rc;
-  if (!out || n < 0 || n > 2 * kWaitSites) return fail(B200_EINVAL, "out must hold at most %d counters", 2 * kWaitSites);
+  if (!out || n < 0 || n > kProfileWords) return fail(B200_EINVAL, "out must hold at most %d counters", kProfileWords);
   CUDA_TRY(cudaDeviceSynchronize());
   CUDA_TRY(cudaMemcpy(out, st->status + kStatusInts, static_cast<size_t>(n) * sizeof(unsigned long long), cudaMemcpyDeviceToHost));
-  CUDA_TRY(cudaMemset(st->status + kStatusInts, 0, 2 * kWaitSites * sizeof(unsigned long long)));
+  CUDA_TRY(cudaMemset(st->status + kStatusInts, 0, kProfileWords * sizeof(unsigned long long)));
   return B200_OK;
 #else
   (void)out;

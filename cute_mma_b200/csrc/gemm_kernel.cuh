@@ -131,27 +131,35 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
       // K-major: advance 32 bytes inside the swizzled row per UMMA-K; MN-major: UMMA-K rows of 128 bytes.
       constexpr uint32_t a_adv = T::kAMn ? T::kUmmaK * 128 : 32, b_adv = T::kBMn ? T::kUmmaK * 128 : 32;
       constexpr uint32_t a_lbo = T::kAMn ? T::kBK * 128 : 16, b_lbo = T::kBMn ? T::kBK * 128 : 16;
+      // The tensor pipe queues only a couple of MMAs per issuing thread; to keep it fed, each stage
+      // looks at the next stage's barrier (non-blocking) once its first MMAs are queued, and the
+      // next stage only waits if that look did not find the data landed.
       uint32_t it = 0, tcount = 0;
-      bool ok = true;
+      bool ok = true, have_full = false;
+      const uint64_t a_desc0 = umma_desc_sw128(smem_base, a_lbo, T::kA32Atom ? 512 : 1024, T::kA32Atom ? 1 : 2);
+      const uint64_t b_desc0 = umma_desc_sw128(smem_base + T::kABytes, b_lbo, T::kB32Atom ? 512 : 1024, T::kB32Atom ? 1 : 2);
       for (unsigned tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x, ++tcount) {
         const int a = tcount % T::kAccBufs;
         if (!(ok = mbar_wait(accempty_bar(a), ((tcount / T::kAccBufs) & 1) ^ 1, ctx, 2))) break;
-        tc_fence_after();
         const uint32_t d_tmem = tmem_base + a * T::kBN;
+        const bool last_tile = tile + gridDim.x >= num_tiles;
         for (int ks = 0; ks < k_steps; ++ks, ++it) {
           const int s = it % T::kStages;
-          if (!(ok = mbar_wait(full_bar(s), (it / T::kStages) & 1, ctx, 3))) break;
+          if (!have_full && !(ok = mbar_wait(full_bar(s), (it / T::kStages) & 1, ctx, 3))) break;
           tc_fence_after();
-          const uint32_t a_src = smem_base + s * T::kStageBytes, b_src = a_src + T::kABytes;
-          const uint64_t a_desc = umma_desc_sw128(a_src, a_lbo, T::kA32Atom ? 512 : 1024, T::kA32Atom ? 1 : 2);
-          const uint64_t b_desc = umma_desc_sw128(b_src, b_lbo, T::kB32Atom ? 512 : 1024, T::kB32Atom ? 1 : 2);
+          const uint64_t a_desc = a_desc0 + static_cast<uint64_t>(s * (T::kStageBytes >> 4));
+          const uint64_t b_desc = b_desc0 + static_cast<uint64_t>(s * (T::kStageBytes >> 4));
 #pragma unroll
           for (int kk = 0; kk < T::kBK / T::kUmmaK; ++kk) {
+            if (kk == (T::kBK / T::kUmmaK) / 2) {
+              const bool more = !(last_tile && ks + 1 == k_steps);
+              have_full = more && mbar_test_wait(full_bar((it + 1) % T::kStages), ((it + 1) / T::kStages) & 1);
+            }
             const uint32_t acc = (ks > 0 || kk > 0) ? 1u : 0u;
             if constexpr (T::kFmt == kFmtF16)
-              umma_f16_ss(d_tmem, umma_desc_advance(a_desc, kk * a_adv), umma_desc_advance(b_desc, kk * b_adv), idesc, acc);
+              umma_f16_ss(d_tmem, a_desc + ((kk * a_adv) >> 4), b_desc + ((kk * b_adv) >> 4), idesc, acc);
             else
-              umma_tf32_ss(d_tmem, umma_desc_advance(a_desc, kk * a_adv), umma_desc_advance(b_desc, kk * b_adv), idesc, acc);
+              umma_tf32_ss(d_tmem, a_desc + ((kk * a_adv) >> 4), b_desc + ((kk * b_adv) >> 4), idesc, acc);
           }
           umma_commit(empty_bar(s));  // frees the stage once these MMAs have read it
         }

@@ -47,7 +47,9 @@ struct OftTraits {
   static_assert(kB == 16 || kB == 32 || kB == 64 || kB == 128, "block edge must be 16, 32, 64 or 128");
   static_assert(kBN % 32 == 0 && kBN >= 32 && kBN <= 256, "bN must be a multiple of 32 up to 256");
   static_assert(kTmemUsed <= kTmemCols && kXrBufs >= 2, "tensor memory budget exceeded");
-  static_assert(kSmemBytes <= 232448, "shared memory rings too large");
+  // A tile configuration may fit some block edges and not others (the R tile grows with b); the
+  // launcher reports an unsupported shape for the ones that do not fit instead of failing the build.
+  static constexpr bool kFits = kSmemBytes <= 232448;
   static_assert(kRBytes % 1024 == 0, "R tile must keep the next tile 1024-byte aligned");
 };
 
@@ -134,10 +136,15 @@ oft_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ C
         for (int st = 0; st < units * T::kStagesPerUnit; ++st, ++it) {
           const int s = it % T::kS1;
           if (!(ok = mbar_wait(empty1 + 8 * s, ((it / T::kS1) & 1) ^ 1, ctx, 10))) break;
+#ifdef B200_DEBUG_NO_TMA  // timing experiment only: the rings are never filled, results are garbage
+          mbar_arrive(full1 + 8 * s);
+          (void)m0; (void)r_row0;
+#else
           mbar_expect_tx(full1 + 8 * s, T::kS1Bytes);
           const uint32_t a_dst = ring1 + s * T::kS1Bytes;
           tma_load_2d(a_dst, &tmap_a, full1 + 8 * s, st * T::kBK, m0);
           tma_load_2d(a_dst + T::kABytes, &tmap_r, full1 + 8 * s, st * T::kBK, r_row0);
+#endif
         }
       }
     }
@@ -155,8 +162,13 @@ oft_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ C
         for (int st = 0; st < units * T::kStagesPerUnit; ++st, ++it) {
           const int s = it % T::kS2;
           if (!(ok = mbar_wait(empty2 + 8 * s, ((it / T::kS2) & 1) ^ 1, ctx, 11))) break;
+#ifdef B200_DEBUG_NO_TMA
+          mbar_arrive(full2 + 8 * s);
+          (void)n0;
+#else
           mbar_expect_tx(full2 + 8 * s, T::kS2Bytes);
           tma_load_2d(ring2 + s * T::kS2Bytes, &tmap_b, full2 + 8 * s, st * T::kBK, n0);
+#endif
         }
       }
     }
@@ -167,36 +179,59 @@ oft_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ C
     // tensor pipe retires them, and the mbarriers already carry every ordering between the two.
     setmaxnreg_dec<96>();
     if (lane == 0) {
+      // The tensor pipe queues only a couple of MMAs per issuing thread, so whatever this thread does
+      // between two stages (barrier waits, commits) is time the pipe may sit idle.  Each stage
+      // therefore looks at the next stage's barriers (test_wait, non-blocking) after its first two
+      // MMAs are queued, and the next stage only waits for what that look did not find complete.
       constexpr uint32_t idesc1 = umma_idesc(kFmtF16, 0, 0, T::kBM, T::kB);
       const uint64_t a_desc0 = umma_desc_sw128(ring1, 16, 1024), r_desc0 = umma_desc_sw128(ring1 + T::kABytes, 16, 1024);
-      int s = 0, xb = 0;
+      const unsigned total_stages = total_units * T::kStagesPerUnit;
+      int s = 0, xb = 0, su = 0;
       uint32_t ph_s = 0, ph_xb = 0;
-      bool ok = true;
-      for (unsigned g = 0; ok && g < total_units; ++g) {
-        if (!(ok = mbar_wait(x_empty + 8 * xb, ph_xb ^ 1, ctx, 20))) break;  // MMA2 is done with this buffer
+      unsigned g = 0;
+      bool have_full = false, have_buf = false, ok = true;
+      for (unsigned j = 0; ok && j < total_stages; ++j) {
+        if (su == 0) {
+          if (!have_buf && !(ok = mbar_wait(x_empty + 8 * xb, ph_xb ^ 1, ctx, 20))) break;  // MMA2 is done with this buffer
+          trace_stamp(ctx, g, 0);
+        }
+        if (!have_full && !(ok = mbar_wait(full1 + 8 * s, ph_s, ctx, 21))) break;
         tc_fence_after();
         const uint32_t d1 = tmem_base + T::kColXr + xb * T::kUnitK;
+        const uint64_t a_desc = a_desc0 + static_cast<uint64_t>(s * (T::kS1Bytes >> 4));
+        const uint64_t r_desc = r_desc0 + static_cast<uint64_t>(s * (T::kS1Bytes >> 4));
+        const bool unit_ends = (su == T::kStagesPerUnit - 1);
+        int s_n = s + 1, xb_n = xb;
+        uint32_t ph_s_n = ph_s, ph_xb_n = ph_xb;
+        if (s_n == T::kS1) { s_n = 0; ph_s_n ^= 1; }
+        if (unit_ends && ++xb_n == T::kXrBufs) { xb_n = 0; ph_xb_n ^= 1; }
 #pragma unroll
-        for (int su = 0; su < T::kStagesPerUnit; ++su) {
-          if (!(ok = mbar_wait(full1 + 8 * s, ph_s, ctx, 21))) break;
-          tc_fence_after();
-          const uint64_t a_desc = a_desc0 + static_cast<uint64_t>(s * (T::kS1Bytes >> 4));
-          const uint64_t r_desc = r_desc0 + static_cast<uint64_t>(s * (T::kS1Bytes >> 4));
-#pragma unroll
-          for (int kk = 0; kk < T::kBK / 16; ++kk) {
-            // b < 64: the stage holds 64/b diagonal blocks; slice kk belongs to block (kk*16)/b and
-            // lands in XRacc columns [blk*b, blk*b+b).  b >= 64: one block, accumulated over the unit.
-            constexpr bool small = T::kB < 64;
-            const int blk = small ? (kk * 16) / T::kB : 0;
-            const uint32_t accum = small ? ((((kk * 16) % T::kB) != 0) ? 1u : 0u) : ((su > 0 || kk > 0) ? 1u : 0u);
-            umma_f16_ss(d1 + blk * T::kB, a_desc + kk * 2, r_desc + kk * 2, idesc1, accum);
+        for (int kk = 0; kk < T::kBK / 16; ++kk) {
+          if (kk == 2) {
+            const bool more = j + 1 < total_stages;
+            have_full = more && mbar_test_wait(full1 + 8 * s_n, ph_s_n);
+            have_buf = more && unit_ends && mbar_test_wait(x_empty + 8 * xb_n, ph_xb_n ^ 1);
           }
-          umma_commit(empty1 + 8 * s);
-          if (++s == T::kS1) { s = 0; ph_s ^= 1; }
+          // b < 64: the stage holds 64/b diagonal blocks; slice kk belongs to block (kk*16)/b and
+          // lands in XR columns [blk*b, blk*b+b).  b >= 64: one block, accumulated over the unit.
+          constexpr bool small = T::kB < 64;
+          const int blk = small ? (kk * 16) / T::kB : 0;
+          const uint32_t accum = small ? ((((kk * 16) % T::kB) != 0) ? 1u : 0u) : ((su > 0 || kk > 0) ? 1u : 0u);
+          umma_f16_ss(d1 + blk * T::kB, a_desc + kk * 2, r_desc + kk * 2, idesc1, accum);
         }
-        if (!ok) break;
-        umma_commit(x_acc + 8 * xb);
-        if (++xb == T::kXrBufs) { xb = 0; ph_xb ^= 1; }
+        umma_commit(empty1 + 8 * s);
+        s = s_n;
+        ph_s = ph_s_n;
+        if (unit_ends) {
+          umma_commit(x_acc + 8 * xb);
+          trace_stamp(ctx, g, 1);
+          xb = xb_n;
+          ph_xb = ph_xb_n;
+          su = 0;
+          ++g;
+        } else {
+          ++su;
+        }
       }
     }
     __syncwarp();
@@ -206,36 +241,55 @@ oft_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ C
     if (lane == 0) {
       constexpr uint32_t idesc2 = umma_idesc(kFmtF16, 0, 0, T::kBM, T::kBN);
       const uint64_t b_desc0 = umma_desc_sw128(ring2, 16, 1024);
-      int s = 0, xb = 0, ku = 0;
+      const unsigned total_stages = total_units * T::kStagesPerUnit;
+      int s = 0, xb = 0, ku = 0, su = 0;
       uint32_t ph_s = 0, ph_xb = 0, ph_acc = 0;
-      bool ok = true;
-      for (unsigned u = 0; ok && u < total_units; ++u) {
-        if (ku == 0) {  // first unit of a tile: the epilogue must have drained the accumulator
-          if (!(ok = mbar_wait(acc_empty, ph_acc ^ 1, ctx, 22))) break;
+      unsigned u = 0;
+      bool have_full = false, have_half = false, ok = true;
+      for (unsigned j = 0; ok && j < total_stages; ++j) {
+        if (su == 0) {
+          // first unit of a tile: the epilogue must have drained the accumulator (never looked at
+          // early: the epilogue of this tile cannot start before this thread commits the tile)
+          if (ku == 0 && !(ok = mbar_wait(acc_empty, ph_acc ^ 1, ctx, 22))) break;
+          if (!have_half && !(ok = mbar_wait(x_half + 8 * xb, ph_xb, ctx, 23))) break;
+          trace_stamp(ctx, u, 4);
         }
-        if (!(ok = mbar_wait(x_half + 8 * xb, ph_xb, ctx, 23))) break;
+        if (!have_full && !(ok = mbar_wait(full2 + 8 * s, ph_s, ctx, 24))) break;
         tc_fence_after();
-        const uint32_t a_tmem = tmem_base + T::kColXr + xb * T::kUnitK;
+        const uint32_t a_tmem = tmem_base + T::kColXr + xb * T::kUnitK + su * (T::kBK / 2);
+        const uint64_t b_desc = b_desc0 + static_cast<uint64_t>(s * (T::kS2Bytes >> 4));
+        const bool unit_ends = (su == T::kStagesPerUnit - 1);
+        int s_n = s + 1, xb_n = xb;
+        uint32_t ph_s_n = ph_s, ph_xb_n = ph_xb;
+        if (s_n == T::kS2) { s_n = 0; ph_s_n ^= 1; }
+        if (unit_ends && ++xb_n == T::kXrBufs) { xb_n = 0; ph_xb_n ^= 1; }
 #pragma unroll
-        for (int su = 0; su < T::kStagesPerUnit; ++su) {
-          if (!(ok = mbar_wait(full2 + 8 * s, ph_s, ctx, 24))) break;
-          tc_fence_after();
-          const uint64_t b_desc = b_desc0 + static_cast<uint64_t>(s * (T::kS2Bytes >> 4));
-#pragma unroll
-          for (int kk = 0; kk < T::kBK / 16; ++kk) {
-            const uint32_t accum = (su > 0 || kk > 0) ? 1u : (ku > 0 ? 1u : 0u);
-            umma_f16_ts(tmem_base + T::kColAcc, a_tmem + su * (T::kBK / 2) + kk * 8, b_desc + kk * 2, idesc2, accum);
+        for (int kk = 0; kk < T::kBK / 16; ++kk) {
+          if (kk == 2) {
+            const bool more = j + 1 < total_stages;
+            have_full = more && mbar_test_wait(full2 + 8 * s_n, ph_s_n);
+            have_half = more && unit_ends && mbar_test_wait(x_half + 8 * xb_n, ph_xb_n);
           }
-          umma_commit(empty2 + 8 * s);
-          if (++s == T::kS2) { s = 0; ph_s ^= 1; }
+          const uint32_t accum = (su > 0 || kk > 0) ? 1u : (ku > 0 ? 1u : 0u);
+          umma_f16_ts(tmem_base + T::kColAcc, a_tmem + kk * 8, b_desc + kk * 2, idesc2, accum);
         }
-        if (!ok) break;
-        umma_commit(x_empty + 8 * xb);
-        if (++xb == T::kXrBufs) { xb = 0; ph_xb ^= 1; }
-        if (++ku == units) {
-          umma_commit(acc_full);
-          ku = 0;
-          ph_acc ^= 1;
+        umma_commit(empty2 + 8 * s);
+        s = s_n;
+        ph_s = ph_s_n;
+        if (unit_ends) {
+          umma_commit(x_empty + 8 * xb);
+          trace_stamp(ctx, u, 5);
+          xb = xb_n;
+          ph_xb = ph_xb_n;
+          su = 0;
+          ++u;
+          if (++ku == units) {
+            umma_commit(acc_full);
+            ku = 0;
+            ph_acc ^= 1;
+          }
+        } else {
+          ++su;
         }
       }
     }
@@ -253,6 +307,7 @@ oft_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ C
     for (unsigned g = 0; ok && g < total_units; ++g) {
       if (!(ok = mbar_wait_warp(x_acc + 8 * xb, ph_xb, ctx, 30))) break;
       tc_fence_after();
+      if (threadIdx.x == 128) trace_stamp(ctx, g, 2);
 #ifdef B200_PROFILE_WAITS
       const long long cv0 = clock64();
 #endif
@@ -277,6 +332,7 @@ oft_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ C
       tmem_wait_st();
       tc_fence_before();
       mbar_arrive(x_half + 8 * xb);
+      if (threadIdx.x == 128) trace_stamp(ctx, g, 3);
 #ifdef B200_PROFILE_WAITS
       if (threadIdx.x == 128) { ctx.prof_cycles[3] += clock64() - cv0; ctx.prof_count[3] += 1; ctx.prof_site[3] = 51; }  // unit converted
 #endif

@@ -52,6 +52,22 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
   return ok != 0;
 }
 
+// Non-blocking look at a barrier phase (try_wait may suspend the thread; this never does).
+__device__ __forceinline__ bool mbar_test_wait(uint32_t bar, uint32_t parity) {
+#ifdef B200_NO_PEEK  // timing experiment: never look ahead
+  return false;
+#endif
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+
 // Shared by every role of a CTA: where to raise the abort flag and where to record the failure.
 struct WaitCtx {
   volatile int* abort_flag;  // shared memory, one per CTA
@@ -67,6 +83,8 @@ struct WaitCtx {
 // has to spin adds its cycles to a per-site counter (and site+64 counts those waits), read back by b200_wait_profile.
 constexpr int kWaitSites = 64;
 constexpr int kStatusInts = 4;
+constexpr int kTraceUnits = 32, kTraceEvents = 8;  // profiling build: clock64 stamps of CTA 0, units [kTraceFirst, +32)
+constexpr int kTraceFirst = 70;
 
 __device__ __noinline__ void report_timeout(const WaitCtx& ctx, int site, uint32_t parity) {
   *ctx.abort_flag = 1;
@@ -109,6 +127,14 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, const W
   return ok;
 #else
   return mbar_wait_impl(bar, parity, ctx, site);
+#endif
+}
+__device__ __forceinline__ void trace_stamp(const WaitCtx& ctx, unsigned unit, int event) {
+#ifdef B200_PROFILE_WAITS
+  if (blockIdx.x == 0 && unit >= kTraceFirst && unit < kTraceFirst + kTraceUnits) {
+    unsigned long long* tr = reinterpret_cast<unsigned long long*>(ctx.status + kStatusInts) + 2 * kWaitSites;
+    tr[(unit - kTraceFirst) * kTraceEvents + event] = static_cast<unsigned long long>(clock64());
+  }
 #endif
 }
 __device__ __forceinline__ void wait_profile_flush(const WaitCtx& ctx) {

@@ -1,0 +1,60 @@
+"""CPU: autotune generator and runner plumbing (no GPU, no nvcc: executables are faked)."""
+import asyncio
+import json
+import math
+import os
+import stat
+
+from cute_mma_b200.autotune import gen_oft_autotune_config as gen
+from cute_mma_b200.autotune import runner_oft
+
+
+def test_generator_writes_complete_include_dirs(tmp_path):
+    rows = gen.generate(str(tmp_path), b=64)
+    assert len(rows) >= 20
+    for r in rows:
+        d = tmp_path / r["config"]
+        text = (d / "oft_config.hpp").read_text()
+        assert f"bN = {r['bN']};" in text and f"bP1 = {r['bP1']};" in text and f"bP2 = {r['bP2']};" in text
+        assert (d / "gemm_config.hpp").exists()
+        assert r["smem"] <= gen.SMEM_LIMIT
+    assert (tmp_path / "config_csvs" / "param.csv").read_text().startswith("config,bN,bP1,bP2,smem")
+    # the larger R tile of b = 128 rules out more candidates, and needs two XR buffers in tensor memory
+    assert len(list(gen.candidates(128))) < len(rows)
+    assert all((512 - c["bN"]) // 128 >= 2 for c in gen.candidates(128))
+
+
+def test_smem_formula_matches_the_library(lib):
+    from cute_mma_b200 import ops
+
+    info = ops.kernel_info(lib)["oft"]
+    assert gen.smem_bytes(info["bN"], info["bP1"], info["bP2"], 64) == info["b64"]["smem"]
+    assert gen.smem_bytes(info["bN"], info["bP1"], info["bP2"], 128) == info["b128"]["smem"]
+
+
+def test_stdout_contract_is_parsed_like_the_reference():
+    line = "TFLOPS/s (AR_W): [1012.34], (AR_W_sparse): 1990.10, (A_RW): 998.20, Time: 0.551 ms\n"
+    assert runner_oft.get_flops("M = 4096\n" + line) == 1012.34
+    assert math.isnan(runner_oft.get_flops("CUDA call failed with status 1"))
+
+
+def _fake_exe(path, body):
+    path.write_text("#!/bin/sh\n" + body)
+    path.chmod(path.stat().st_mode | stat.S_IEXEC)
+    return str(path)
+
+
+def test_sweep_checkpoints_and_resumes(tmp_path):
+    good = _fake_exe(tmp_path / "good", 'echo "gpu=$CUDA_VISIBLE_DEVICES"; echo "TFLOPS/s (AR_W): [123.45], x"\n')
+    bad = _fake_exe(tmp_path / "bad", 'echo "launch failed" 1>&2; exit 1\n')
+    results = str(tmp_path / "r.jsonl")
+    out = asyncio.run(runner_oft.sweep({"a": good, "b": bad}, ["-t", "1"], 2, results, 30.0))
+    assert out["a"]["value"] == 123.45 and math.isnan(out["b"]["value"]) and "launch failed" in out["b"]["stderr"]
+    assert "gpu=" in out["a"]["stdout"]
+    lines = [json.loads(x) for x in open(results)]
+    assert {r["key"] for r in lines} == {"a", "b"}
+    # restart: finished keys are skipped, only the new one runs
+    marker = tmp_path / "ran_again"
+    good2 = _fake_exe(tmp_path / "good2", f'touch {marker}; echo "[1.00]"\n')
+    out2 = asyncio.run(runner_oft.sweep({"a": good2, "c": good}, ["-t", "1"], 1, results, 30.0))
+    assert not marker.exists() and out2["a"]["value"] == 123.45 and out2["c"]["value"] == 123.45
