@@ -219,6 +219,55 @@ int stage_reserve(DeviceState* st, int slot, size_t bytes) {
   return B200_OK;
 }
 
+// ---- scratch of the entry point that allocates nothing ------------------------------------------------
+// Lives in the library image: every GPU that loads the library holds these bytes until the process
+// exits.  In host code the name below is only a host-side stand-in for the symbol, never a device
+// address; the address a kernel may use comes from cudaGetSymbolAddress, per device.
+constexpr size_t kStaticScratchBytes = 64 * 1024;
+static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
+
+struct StaticScratchState {
+  bool ready = false;
+  int sm_count = 0;
+  void* scratch = nullptr;  // device address of g_static_scratch on this device
+};
+StaticScratchState g_static[kMaxDevices];
+std::mutex g_static_mu;
+
+// Device scratch one fused-OFT launch needs beyond its inputs and outputs: the status record of the
+// bounded waits followed by the wait-profile words (the same layout the allocated workspace has).
+size_t oft_scratch_bytes(int /*m*/, int /*n*/, int /*k*/, int /*reconn_sz*/) { return kWorkspaceBytes; }
+
+// Once per device, with that device current.  Calls nothing that allocates device memory.
+int static_scratch_state(StaticScratchState** out) {
+  int dev = 0;
+  CUDA_TRY(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= kMaxDevices) return fail(B200_EINVAL, "device ordinal %d out of range", dev);
+  std::lock_guard<std::mutex> lock(g_static_mu);
+  StaticScratchState& st = g_static[dev];
+  if (!st.ready) {
+    int major = 0;
+    CUDA_TRY(cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev));
+    if (major != 10) return fail(B200_EUNSUPPORTED, "device %d is not sm_100; this library contains sm_100a code only", dev);
+    CUDA_TRY(cudaDeviceGetAttribute(&st.sm_count, cudaDevAttrMultiProcessorCount, dev));
+    void* ptr = nullptr;
+    CUDA_TRY(cudaGetSymbolAddress(&ptr, g_static_scratch));
+    if (!ptr) return fail(B200_ECUDA, "cudaGetSymbolAddress returned a null address for the static scratch");
+    CUDA_TRY(cudaMemset(ptr, 0, kWorkspaceBytes));  // the status record must start at zero
+    if (!g_encode) {
+      void* fn = nullptr;
+      cudaDriverEntryPointQueryResult q;
+      CUDA_TRY(cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &q));
+      if (q != cudaDriverEntryPointSuccess || !fn) return fail(B200_ECUDA, "cuTensorMapEncodeTiled not available from the driver");
+      g_encode = reinterpret_cast<EncodeFn>(fn);
+    }
+    st.scratch = ptr;
+    st.ready = true;
+  }
+  *out = &st;
+  return B200_OK;
+}
+
 }  // namespace
 
 extern "C" {
@@ -373,6 +422,42 @@ int b200_shutdown(void) {
   }
   cudaSetDevice(cur);
   return B200_OK;
+}
+
+int b200_oft_tn_f16_static(int m, int n, int k, int group_size, int reconn_sz, const void* A, int ldA, const void* B, int ldB,
+                           const void* R, int ldR, void* C, int ldC, void* stream_v) {
+  g_err.clear();
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
+  if (int rc = common_dims(m, n, k, A, B, C)) return rc;
+  if (reconn_sz <= 0 || group_size <= 0) return fail(B200_EINVAL, "group_size=%d and reconn_sz=%d must be positive", group_size, reconn_sz);
+  if (k % reconn_sz != 0) return fail(B200_EINVAL, "k=%d is not a multiple of reconn_sz=%d", k, reconn_sz);
+  if (n % group_size != 0) return fail(B200_EINVAL, "n=%d is not a multiple of group_size=%d", n, group_size);
+  if (ldC < n) return fail(B200_EINVAL, "ldC=%d smaller than n=%d (C is row-major)", ldC, n);
+  if (m > 0 && n > 0 && k > 0 && !R) return fail(B200_EINVAL, "R is null");
+  const size_t need = oft_scratch_bytes(m, n, k, reconn_sz);
+  if (need > kStaticScratchBytes)
+    return fail(B200_EUNSUPPORTED, "this problem needs %zu bytes of device scratch; the static scratch of b200_oft_tn_f16_static holds %zu",
+                need, kStaticScratchBytes);
+  if (m == 0 || n == 0) return B200_OK;
+  if (k == 0) {
+    CUDA_TRY(cudaMemset2DAsync(C, static_cast<size_t>(ldC) * 2, 0, static_cast<size_t>(n) * 2, m, stream));
+    return B200_OK;
+  }
+  StaticScratchState* ss;
+  if (int rc = static_scratch_state(&ss)) return rc;
+  // Every call shares the one array, which still holds what the last call left there.  The status
+  // record is the part that must start at zero; clear it in stream order ahead of the kernel.
+  CUDA_TRY(cudaMemsetAsync(ss->scratch, 0, kStatusInts * sizeof(int), stream));
+  DeviceState view;  // what the launcher reads: SM count and where the kernel's scratch is
+  view.sm_count = ss->sm_count;
+  view.status = static_cast<int*>(ss->scratch);
+  switch (reconn_sz) {
+    case 16: return launch_oft<16>(m, n, k, group_size, A, ldA, B, ldB, R, ldR, C, ldC, stream, &view);
+    case 32: return launch_oft<32>(m, n, k, group_size, A, ldA, B, ldB, R, ldR, C, ldC, stream, &view);
+    case 64: return launch_oft<64>(m, n, k, group_size, A, ldA, B, ldB, R, ldR, C, ldC, stream, &view);
+    case 128: return launch_oft<128>(m, n, k, group_size, A, ldA, B, ldB, R, ldR, C, ldC, stream, &view);
+    default: return fail(B200_EUNSUPPORTED, "reconn_sz=%d not compiled in (16, 32, 64, 128)", reconn_sz);
+  }
 }
 
 }  // extern "C"

@@ -23,7 +23,7 @@ OK, EINVAL, EUNSUPPORTED, ECUDA, EDEVICE = 0, 1, 2, 3, 4
 
 # every symbol include/cute_mma_b200.h declares
 SYMBOLS = (
-    "b200_oft_tn_f16", "b200_oft_tn_f16_host", "b200_gemm_tn_f16", "b200_gemm_nt_f16", "b200_gemm_tn_tf32",
+    "b200_oft_tn_f16", "b200_oft_tn_f16_host", "b200_oft_tn_f16_static", "b200_gemm_tn_f16", "b200_gemm_nt_f16", "b200_gemm_tn_tf32",
     "b200_gemm_nt_tf32", "b200_gemm", "b200_shard_range", "b200_tile_coord", "b200_device_status", "b200_wait_profile", "b200_kernel_info",
     "b200_last_error", "b200_shutdown",
 )
@@ -54,6 +54,7 @@ def load_library(path: str | None = None):
     lib = ctypes.CDLL(p)
     i, vp, c = ctypes.c_int, ctypes.c_void_p, ctypes.c_char
     lib.b200_oft_tn_f16.argtypes = [i, i, i, i, i, vp, i, vp, i, vp, i, vp, i, vp]
+    lib.b200_oft_tn_f16_static.argtypes = [i, i, i, i, i, vp, i, vp, i, vp, i, vp, i, vp]
     lib.b200_oft_tn_f16_host.argtypes = [i, i, i, i, i, vp, i, vp, i, vp, i, vp, i]
     for name in ("b200_gemm_tn_f16", "b200_gemm_nt_f16", "b200_gemm_tn_tf32", "b200_gemm_nt_tf32"):
         getattr(lib, name).argtypes = [i, i, i, vp, i, vp, i, vp, i, vp]
@@ -101,6 +102,14 @@ def oft_tn(m, n, k, A, ldA, B, ldB, R, ldR, C, ldC, stream=None, *, group_size=N
     lib = lib or load_library()
     gs = n if group_size is None else group_size
     _check(lib, lib.b200_oft_tn_f16(m, n, k, gs, reconn_sz, _ptr(A), ldA, _ptr(B), ldB, _ptr(R), ldR, _ptr(C), ldC, _stream(stream)))
+
+
+def oft_tn_static(m, n, k, A, ldA, B, ldB, R, ldR, C, ldC, stream=None, *, group_size=None, reconn_sz=8, lib=None) -> None:
+    """oft_tn for callers that must not allocate device memory: the kernel's scratch is a fixed array
+    inside the library (see b200_oft_tn_f16_static in the header for the sharing rules)."""
+    lib = lib or load_library()
+    gs = n if group_size is None else group_size
+    _check(lib, lib.b200_oft_tn_f16_static(m, n, k, gs, reconn_sz, _ptr(A), ldA, _ptr(B), ldB, _ptr(R), ldR, _ptr(C), ldC, _stream(stream)))
 
 
 def oft_tn_host(m, n, k, A, ldA, B, ldB, R, ldR, C, ldC, *, group_size=None, reconn_sz=8, lib=None) -> None:

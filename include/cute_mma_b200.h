@@ -44,6 +44,28 @@ int b200_oft_tn_f16_host(int m, int n, int k, int group_size, int reconn_sz,
                          const void* A, int ldA, const void* B, int ldB, const void* R, int ldR,
                          void* C, int ldC);
 
+/* The same fused product for callers that must not allocate device memory.  It has no counterpart in
+ * the reference.  Some programs hand all of a GPU's memory to their own pool when they start, so a later
+ * cudaMalloc fails; others run this call on a path where the device-wide synchronisation that cudaMalloc
+ * implies is not acceptable.  b200_oft_tn_f16 creates a small per-device workspace with cudaMalloc the
+ * first time it runs on a device; this entry point calls no cudaMalloc, no cudaFree and no allocating
+ * library routine, ever.  The device scratch its kernel needs beyond A, B, R and C (the record in which
+ * a kernel reports a bounded wait that ran out, plus the profiling words of -DB200_PROFILE_WAITS builds:
+ * about 3 KB today) lives in a 64 KB array inside the library image, which every GPU that loads the
+ * library keeps until the process exits.  A problem whose scratch need exceeds those 64 KB is refused
+ * with B200_EUNSUPPORTED and a message naming both sizes.
+ *   - Arguments, layouts and result are exactly those of b200_oft_tn_f16 (same kernel, same bits).
+ *   - The first call on each device looks up the array's device address, reads two device attributes
+ *     and zeroes the record with a synchronous cudaMemset; make that first call, with the device
+ *     current, before any stream capture begins.  Later calls only enqueue work on `stream`.
+ *   - All calls on a device share the one array, and it keeps whatever the previous call left in it.
+ *     The record is cleared in stream order before each launch; two calls whose kernels overlap on the
+ *     GPU (different streams, no dependency) race on it.  Serialise them.
+ *   - b200_device_status reports the allocated workspace, not this array. */
+int b200_oft_tn_f16_static(int m, int n, int k, int group_size, int reconn_sz,
+                           const void* A, int ldA, const void* B, int ldB, const void* R, int ldR,
+                           void* C, int ldC, void* stream);
+
 /* Plain GEMM  C(i,j) = sum_l A(i,l) B(j,l),  C column-major: C(i,j) at C[i + j*ldC].
  * Replace gemm_tn / gemm_nt<TO,TR> (gemm_sm80_tc.cu:163-228 / 95-160).
  *   tn: A(i,l) at A[i*ldA + l], B(j,l) at B[j*ldB + l]   (both K-contiguous)
