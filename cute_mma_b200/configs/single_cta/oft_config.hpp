@@ -1,0 +1,16 @@
+// Compile-time tile hyperparameters of the fused OFT kernel, selected by include path like the
+// reference's default_configs/oft_config.hpp:4-12.
+//   bM, bN  C tile per CTA (bM fixed at 128; bN multiple of 32, <= 256)
+//   bK      K extent of one shared-memory stage (64 fp16 = one 128-byte swizzle row)
+//   bP1     depth of the {A, R} ring feeding the rotation MMA   (the reference's producer ring)
+//   bP2     depth of the {B} ring feeding the main contraction  (the reference's consumer ring)
+// The reference's warp_layout1 / warp_layout2 have no counterpart: one thread issues each MMA.
+#pragma once
+
+struct CurrCompParams {
+  static const unsigned int bM = 128;
+  static const unsigned int bN = 256;
+  static const unsigned int bK = 64;
+  static const unsigned int bP1 = 3;
+  static const unsigned int bP2 = 4;
+};

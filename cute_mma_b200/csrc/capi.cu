@@ -17,6 +17,7 @@
 #include "gemm_config.hpp"   // resolved through -I<config dir>
 #include "oft_config.hpp"
 #include "gemm_kernel.cuh"
+#include "gemm2_kernel.cuh"
 #include "oft_kernel.cuh"
 
 namespace {
@@ -124,10 +125,16 @@ int common_dims(int m, int n, int k, const void* A, const void* B, void* C) {
 }
 
 // ---- plain GEMM --------------------------------------------------------------------------------------
+// ctas = 2 in gemm_config.hpp selects the CTA-pair kernel (256 x bN tile per pair of SMs).
+template <class P, class = void> struct CtasOf { static constexpr int value = 1; };
+template <class P> struct CtasOf<P, decltype((void)P::ctas)> { static constexpr int value = P::ctas; };
+
 template <typename TIn, typename TOut, bool kNT, class P>
 int launch_gemm(int m, int n, int k, const void* A, int ldA, const void* B, int ldB, void* C, int ldC, void* stream_v) {
-  using T = GemmTraits<TIn, TOut, kNT, kNT, P::bN, P::bP>;
-  static_assert(P::bM == T::kBM && P::bK == T::kBK, "gemm_config.hpp: bM must be 128 and bK one 128-byte row");
+  constexpr bool kPair = CtasOf<P>::value == 2;
+  using T1 = GemmTraits<TIn, TOut, kNT, kNT, P::bN, kPair ? 4 : P::bP>;
+  using T2 = Gemm2Traits<TIn, TOut, kNT, kNT, P::bN, kPair ? P::bP : 6>;
+  static_assert(P::bM == T1::kBM && P::bK == T1::kBK, "gemm_config.hpp: bM must be 128 and bK one 128-byte row");
   g_err.clear();
   if (int rc = common_dims(m, n, k, A, B, C)) return rc;
   if (ldC < m) return fail(B200_EINVAL, "ldC=%d smaller than m=%d (C is column-major)", ldC, m);
@@ -139,20 +146,29 @@ int launch_gemm(int m, int n, int k, const void* A, int ldA, const void* B, int 
   }
   DeviceState* st;
   if (int rc = device_state(&st)) return rc;
+  constexpr int kBoxN = kPair ? T2::kBNHalf : T1::kBN;
   CUtensorMap ma, mb;
   if (!kNT) {  // K contiguous
-    if (int rc = make_map(&ma, A, sizeof(TIn), k, m, ldA, T::kBK, T::kBM, "A")) return rc;
-    if (int rc = make_map(&mb, B, sizeof(TIn), k, n, ldB, T::kBK, T::kBN, "B")) return rc;
+    if (int rc = make_map(&ma, A, sizeof(TIn), k, m, ldA, T1::kBK, T1::kBM, "A")) return rc;
+    if (int rc = make_map(&mb, B, sizeof(TIn), k, n, ldB, T1::kBK, kBoxN, "B")) return rc;
   } else {     // M / N contiguous, one 128-byte column chunk per copy
-    if (int rc = make_map(&ma, A, sizeof(TIn), m, k, ldA, T::kChunk, T::kBK, "A", T::kA32Atom)) return rc;
-    if (int rc = make_map(&mb, B, sizeof(TIn), n, k, ldB, T::kChunk, T::kBK, "B", T::kB32Atom)) return rc;
+    if (int rc = make_map(&ma, A, sizeof(TIn), m, k, ldA, T1::kChunk, T1::kBK, "A", T1::kA32Atom)) return rc;
+    if (int rc = make_map(&mb, B, sizeof(TIn), n, k, ldB, T1::kChunk, T1::kBK, "B", T1::kB32Atom)) return rc;
   }
-  auto kernel = gemm_kernel<T>;
-  if (int rc = opt_in_smem(kernel, T::kSmemBytes)) return rc;
-  const long long tiles = static_cast<long long>((m + T::kBM - 1) / T::kBM) * ((n + T::kBN - 1) / T::kBN);
-  const int grid = static_cast<int>(tiles < st->sm_count ? tiles : st->sm_count);
   GemmArgs args{m, n, k, C, ldC, st->status};
-  kernel<<<grid, T::kThreads, T::kSmemBytes, stream>>>(ma, mb, args);
+  if constexpr (kPair) {
+    auto kernel = gemm2_kernel<T2>;
+    if (int rc = opt_in_smem(kernel, T2::kSmemBytes)) return rc;
+    const long long tiles = static_cast<long long>((m + 2 * T2::kBM - 1) / (2 * T2::kBM)) * ((n + T2::kBN - 1) / T2::kBN);
+    const int pairs = static_cast<int>(tiles < st->sm_count / 2 ? tiles : st->sm_count / 2);
+    kernel<<<2 * pairs, T2::kThreads, T2::kSmemBytes, stream>>>(ma, mb, args);  // cluster dimension (2,1,1) is part of the kernel
+  } else {
+    auto kernel = gemm_kernel<T1>;
+    if (int rc = opt_in_smem(kernel, T1::kSmemBytes)) return rc;
+    const long long tiles = static_cast<long long>((m + T1::kBM - 1) / T1::kBM) * ((n + T1::kBN - 1) / T1::kBN);
+    const int grid = static_cast<int>(tiles < st->sm_count ? tiles : st->sm_count);
+    kernel<<<grid, T1::kThreads, T1::kSmemBytes, stream>>>(ma, mb, args);
+  }
   CUDA_TRY(cudaGetLastError());
   return B200_OK;
 }

@@ -1,0 +1,226 @@
+// Plain GEMM on CTA pairs (tcgen05 cta_group::2): two CTAs on neighbouring SMs share one
+// 256 x bN tile of C.  Each CTA loads its own 128 rows of A and its own half of the B tile (bN/2
+// rows of N), so an SM pulls 32 KB per K stage from L2 instead of 48 KB and the ring is 6 deep; one
+// thread of the even ("leader") CTA issues MMAs that read both CTAs' shared memory and write both
+// CTAs' tensor memory.  Same operator and layouts as gemm_kernel.cuh (gemm_sm80_tc.cu:95-228).
+//
+// Protocol (per CTA, identical shared-memory layout in both):
+//   full[s]     leader's barrier only: 1 arrival (leader's expect_tx) + the bytes of BOTH CTAs' copies;
+//               the peer's TMA copies name the leader's barrier (pair form of cp.async.bulk.tensor)
+//   empty[s]    one arrival per use from the leader's multicast tcgen05.commit (mask 0b11)
+//   accfull[a]  one arrival per tile from the leader's multicast commit
+//   accempty[a] leader's barrier only: 256 arrivals = the epilogue threads of both CTAs (the peer's
+//               arrive through the cluster address of the leader's barrier)
+// No load carries a multicast qualifier.  Both CTAs reach a cluster barrier before tensor memory is
+// freed and before either exits, so no CTA leaves while its pair may still touch its memory.
+#pragma once
+#include "gemm_kernel.cuh"
+
+namespace b200 {
+
+template <typename TIn_, typename TOut_, bool kAMn_, bool kBMn_, int kBN_, int kStages_>
+struct Gemm2Traits {
+  using TIn = TIn_;
+  using TOut = TOut_;
+  static constexpr bool kAMn = kAMn_, kBMn = kBMn_;
+  static constexpr int kBM = 128;                  // rows of C per CTA; the pair covers 256
+  static constexpr int kBN = kBN_;                 // columns of C per pair (tcgen05 N)
+  static constexpr int kBNHalf = kBN / 2;          // rows of the B tile each CTA loads
+  static constexpr int kElem = sizeof(TIn);
+  static constexpr int kBK = 128 / kElem;
+  static constexpr int kUmmaK = 32 / kElem;
+  static constexpr int kChunk = 128 / kElem;
+  static constexpr int kStages = kStages_;
+  static constexpr int kABytes = kBM * 128;
+  static constexpr int kBBytes = kBNHalf * 128;
+  static constexpr int kStageBytes = kABytes + kBBytes;
+  static constexpr int kAccBufs = 2;
+  static constexpr int kTmemCols = 512;
+  static constexpr int kThreads = 192;
+  static constexpr int kNumBars = 2 * kStages + 2 * kAccBufs;
+  static constexpr int kSmemBytes = kStages * kStageBytes + kNumBars * 8 + 64 + 1024;
+  static constexpr int kFmt = (kElem == 2) ? kFmtF16 : kFmtTF32;
+  static constexpr bool kA32Atom = kAMn && kElem == 4, kB32Atom = kBMn && kElem == 4;
+  static_assert(kBN % 64 == 0 && kBN >= 64 && kBN <= 256, "bN must be a multiple of 64 up to 256");
+  static_assert(kBNHalf % kChunk == 0, "each CTA's half of the B tile must be whole 128-byte chunks");
+  static_assert(kAccBufs * kBN <= kTmemCols, "accumulators exceed tensor memory");
+  static_assert(kSmemBytes <= 232448, "shared memory ring too large");
+};
+
+template <class T>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(T::kThreads, 1)
+gemm2_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b, const GemmArgs args) {
+  using TOut = typename T::TOut;
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
+  const uint32_t bars = smem_base + T::kStages * T::kStageBytes;
+  auto full_bar = [&](int s) { return bars + 8u * s; };
+  auto empty_bar = [&](int s) { return bars + 8u * (T::kStages + s); };
+  auto accfull_bar = [&](int a) { return bars + 8u * (2 * T::kStages + a); };
+  auto accempty_bar = [&](int a) { return bars + 8u * (2 * T::kStages + T::kAccBufs + a); };
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem_gen + T::kStages * T::kStageBytes + T::kNumBars * 8);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  const WaitCtx ctx{abort_flag, args.status, kWaitLimitNs};
+#ifdef B200_PROFILE_WAITS
+  const long long kernel_c0 = clock64();
+#endif
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_ctarank();  // 0 = leader (issues the MMAs), 1 = peer
+  const unsigned pair = blockIdx.x >> 1, num_pairs = gridDim.x >> 1;
+  const unsigned tiles_m = (args.m + 2 * T::kBM - 1) / (2 * T::kBM), tiles_n = (args.n + T::kBN - 1) / T::kBN;
+  const unsigned num_tiles = tiles_m * tiles_n;
+  const int k_steps = (args.k + T::kBK - 1) / T::kBK;
+
+  if (threadIdx.x == 0) {
+    *abort_flag = 0;
+    for (int s = 0; s < T::kStages; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
+    for (int a = 0; a < T::kAccBufs; ++a) { mbar_init(accfull_bar(a), 1); mbar_init(accempty_bar(a), 256); }
+    fence_mbar_init();
+    fence_proxy_async_smem();
+    prefetch_tmap(&tmap_a);
+    prefetch_tmap(&tmap_b);
+  }
+  if (warp == 1) {
+    tmem_alloc_pair(smem_u32(tmem_slot), T::kTmemCols);
+    tmem_relinquish_pair();
+  }
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();  // the pair's barriers exist before anything arrives on them from the other CTA
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ TMA producer (both CTAs)
+    if (lane == 0) {
+      uint32_t it = 0;
+      bool ok = true;
+      for (unsigned tile = pair; ok && tile < num_tiles; tile += num_pairs) {
+        unsigned tm, tn;
+        tile_coord(tiles_m, tiles_n, tile, tm, tn);
+        const int m0 = tm * 2 * T::kBM + rank * T::kBM;      // this CTA's rows of A and C
+        const int n0 = tn * T::kBN + rank * T::kBNHalf;      // this CTA's half of the B tile
+        for (int ks = 0; ks < k_steps; ++ks, ++it) {
+          const int s = it % T::kStages;
+          if (!(ok = mbar_wait(empty_bar(s), ((it / T::kStages) & 1) ^ 1, ctx, 1))) break;
+          if (rank == 0) mbar_expect_tx(full_bar(s), 2 * T::kStageBytes);  // both CTAs' bytes land on this barrier
+          const uint32_t a_dst = smem_base + s * T::kStageBytes, b_dst = a_dst + T::kABytes;
+          const int k0 = ks * T::kBK;
+          if constexpr (!T::kAMn) {
+            tma_load_2d_pair(a_dst, &tmap_a, full_bar(s), k0, m0);
+          } else {
+#pragma unroll
+            for (int c = 0; c < T::kBM / T::kChunk; ++c)
+              tma_load_2d_pair(a_dst + c * (T::kBK * 128), &tmap_a, full_bar(s), m0 + c * T::kChunk, k0);
+          }
+          if constexpr (!T::kBMn) {
+            tma_load_2d_pair(b_dst, &tmap_b, full_bar(s), k0, n0);
+          } else {
+#pragma unroll
+            for (int c = 0; c < T::kBNHalf / T::kChunk; ++c)
+              tma_load_2d_pair(b_dst + c * (T::kBK * 128), &tmap_b, full_bar(s), n0 + c * T::kChunk, k0);
+          }
+        }
+      }
+    }
+    __syncwarp();
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer (leader CTA only)
+    if (lane == 0 && rank == 0) {
+      constexpr uint32_t idesc = umma_idesc(T::kFmt, T::kAMn, T::kBMn, 2 * T::kBM, T::kBN);
+      constexpr uint32_t a_adv = T::kAMn ? T::kUmmaK * 128 : 32, b_adv = T::kBMn ? T::kUmmaK * 128 : 32;
+      constexpr uint32_t a_lbo = T::kAMn ? T::kBK * 128 : 16, b_lbo = T::kBMn ? T::kBK * 128 : 16;
+      uint32_t it = 0, tcount = 0;
+      bool ok = true, have_full = false;
+      const uint64_t a_desc0 = umma_desc_sw128(smem_base, a_lbo, T::kA32Atom ? 512 : 1024, T::kA32Atom ? 1 : 2);
+      const uint64_t b_desc0 = umma_desc_sw128(smem_base + T::kABytes, b_lbo, T::kB32Atom ? 512 : 1024, T::kB32Atom ? 1 : 2);
+      for (unsigned tile = pair; ok && tile < num_tiles; tile += num_pairs, ++tcount) {
+        const int a = tcount % T::kAccBufs;
+        if (!(ok = mbar_wait(accempty_bar(a), ((tcount / T::kAccBufs) & 1) ^ 1, ctx, 2))) break;
+        const uint32_t d_tmem = tmem_base + a * T::kBN;
+        const bool last_tile = tile + num_pairs >= num_tiles;
+        for (int ks = 0; ks < k_steps; ++ks, ++it) {
+          const int s = it % T::kStages;
+          if (!have_full && !(ok = mbar_wait(full_bar(s), (it / T::kStages) & 1, ctx, 3))) break;
+          tc_fence_after();
+          const uint64_t a_desc = a_desc0 + static_cast<uint64_t>(s * (T::kStageBytes >> 4));
+          const uint64_t b_desc = b_desc0 + static_cast<uint64_t>(s * (T::kStageBytes >> 4));
+#pragma unroll
+          for (int kk = 0; kk < T::kBK / T::kUmmaK; ++kk) {
+            if (kk == (T::kBK / T::kUmmaK) / 2) {
+              const bool more = !(last_tile && ks + 1 == k_steps);
+              have_full = more && mbar_test_wait(full_bar((it + 1) % T::kStages), ((it + 1) / T::kStages) & 1);
+            }
+            const uint32_t acc = (ks > 0 || kk > 0) ? 1u : 0u;
+            if constexpr (T::kFmt == kFmtF16)
+              umma_f16_ss_pair(d_tmem, a_desc + ((kk * a_adv) >> 4), b_desc + ((kk * b_adv) >> 4), idesc, acc);
+            else
+              umma_tf32_ss_pair(d_tmem, a_desc + ((kk * a_adv) >> 4), b_desc + ((kk * b_adv) >> 4), idesc, acc);
+          }
+          umma_commit_pair(empty_bar(s), 3);  // frees the stage in both CTAs
+        }
+        if (ok) umma_commit_pair(accfull_bar(a), 3);
+      }
+    }
+    __syncwarp();
+  } else {
+    // ------------------------------------------------------------------ epilogue (warps 2..5, both CTAs)
+    const int quad = warp & 3;
+    uint32_t tcount = 0;
+    bool ok = true;
+    TOut* __restrict__ C = reinterpret_cast<TOut*>(args.C);
+    for (unsigned tile = pair; ok && tile < num_tiles; tile += num_pairs, ++tcount) {
+      unsigned tm, tn;
+      tile_coord(tiles_m, tiles_n, tile, tm, tn);
+      const int a = tcount % T::kAccBufs;
+      if (!(ok = mbar_wait_warp(accfull_bar(a), (tcount / T::kAccBufs) & 1, ctx, 4))) break;
+      tc_fence_after();
+      const int row = tm * 2 * T::kBM + rank * T::kBM + quad * 32 + lane;
+      const uint32_t t_row = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + a * T::kBN;
+#pragma unroll 1
+      for (int c = 0; c < T::kBN / 32; ++c) {
+        uint32_t v[32];
+        tmem_ld_x32(t_row + c * 32, v);
+        tmem_wait_ld();
+        const int col0 = tn * T::kBN + c * 32;
+        if (row < args.m) {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            if (col0 + j < args.n) {
+              const float f = __uint_as_float(v[j]);
+              if constexpr (sizeof(TOut) == 2) C[row + static_cast<long long>(col0 + j) * args.ldC] = __float2half_rn(f);
+              else C[row + static_cast<long long>(col0 + j) * args.ldC] = f;
+            }
+          }
+        }
+      }
+      tc_fence_before();
+      mbar_arrive_cluster(mapa_shared(accempty_bar(a), 0));  // the leader's barrier collects both CTAs
+    }
+  }
+
+  // ---------------------------------------------------------------------- teardown
+#ifdef B200_PROFILE_WAITS
+  if (threadIdx.x == 0) {
+    ctx.prof_cycles[7] += static_cast<unsigned long long>(clock64() - kernel_c0);
+    ctx.prof_count[7] += 1u;
+    ctx.prof_site[7] = 63;
+  }
+#endif
+  wait_profile_flush(ctx);
+  __syncthreads();
+  if (*abort_flag) {
+    for (int i = 0; i < 200; ++i) __nanosleep(1000);
+    __syncthreads();
+  }
+  tc_fence_before();
+  cluster_sync_all();  // neither CTA frees tensor memory or exits while its pair may still use it
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc_pair(tmem_base, T::kTmemCols);
+  }
+}
+
+}  // namespace b200

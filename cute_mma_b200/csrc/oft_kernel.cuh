@@ -42,7 +42,7 @@ struct OftTraits {
   static constexpr int kTmemUsed = kBN + kXrBufs * kUnitK;
   static constexpr int kTmemCols = 512;
   static constexpr int kThreads = 384;
-  static constexpr int kNumBars = 2 * kS1 + 2 * kS2 + 3 * kXrBufs + 2;
+  static constexpr int kNumBars = 2 * kS1 + 2 * kS2 + (2 + kStagesPerUnit) * kXrBufs + 2;
   static constexpr int kSmemBytes = kS1 * kS1Bytes + kS2 * kS2Bytes + kNumBars * 8 + 64 + 1024;
   static_assert(kB == 16 || kB == 32 || kB == 64 || kB == 128, "block edge must be 16, 32, 64 or 128");
   static_assert(kBN % 32 == 0 && kBN >= 32 && kBN <= 256, "bN must be a multiple of 32 up to 256");
@@ -76,7 +76,7 @@ oft_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ C
   const uint32_t full2 = bars + 8u * bi;  bi += T::kS2;        // {B} stage filled
   const uint32_t empty2 = bars + 8u * bi; bi += T::kS2;        // {B} stage read by MMA2
   const uint32_t x_acc = bars + 8u * bi;   bi += T::kXrBufs;   // XR buffer holds the fp32 result of MMA1 (commit)
-  const uint32_t x_half = bars + 8u * bi;  bi += T::kXrBufs;   // XR buffer holds the fp16 image (converters)
+  const uint32_t x_half = bars + 8u * bi;  bi += T::kXrBufs * T::kStagesPerUnit;  // fp16 image of one 64-column slice ready (converters)
   const uint32_t x_empty = bars + 8u * bi; bi += T::kXrBufs;   // XR buffer read by MMA2 (commit)
   const uint32_t acc_full = bars + 8u * bi;  bi += 1;
   const uint32_t acc_empty = bars + 8u * bi; bi += 1;
@@ -99,7 +99,8 @@ oft_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ C
     *abort_flag = 0;
     for (int s = 0; s < T::kS1; ++s) { mbar_init(full1 + 8 * s, 1); mbar_init(empty1 + 8 * s, 1); }
     for (int s = 0; s < T::kS2; ++s) { mbar_init(full2 + 8 * s, 1); mbar_init(empty2 + 8 * s, 1); }
-    for (int i = 0; i < T::kXrBufs; ++i) { mbar_init(x_acc + 8 * i, 1); mbar_init(x_half + 8 * i, 128); mbar_init(x_empty + 8 * i, 1); }
+    for (int i = 0; i < T::kXrBufs; ++i) { mbar_init(x_acc + 8 * i, 1); mbar_init(x_empty + 8 * i, 1); }
+    for (int i = 0; i < T::kXrBufs * T::kStagesPerUnit; ++i) mbar_init(x_half + 8 * i, 128);
     mbar_init(acc_full, 1);
     mbar_init(acc_empty, 128);
     fence_mbar_init();
@@ -247,13 +248,11 @@ oft_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ C
       unsigned u = 0;
       bool have_full = false, have_half = false, ok = true;
       for (unsigned j = 0; ok && j < total_stages; ++j) {
-        if (su == 0) {
-          // first unit of a tile: the epilogue must have drained the accumulator (never looked at
-          // early: the epilogue of this tile cannot start before this thread commits the tile)
-          if (ku == 0 && !(ok = mbar_wait(acc_empty, ph_acc ^ 1, ctx, 22))) break;
-          if (!have_half && !(ok = mbar_wait(x_half + 8 * xb, ph_xb, ctx, 23))) break;
-          trace_stamp(ctx, u, 4);
-        }
+        // first stage of a tile: the epilogue must have drained the accumulator (never looked at
+        // early: the epilogue of this tile cannot start before this thread commits the tile)
+        if (su == 0 && ku == 0 && !(ok = mbar_wait(acc_empty, ph_acc ^ 1, ctx, 22))) break;
+        if (!have_half && !(ok = mbar_wait(x_half + 8 * (xb * T::kStagesPerUnit + su), ph_xb, ctx, 23))) break;
+        if (su == 0) trace_stamp(ctx, u, 4);
         if (!have_full && !(ok = mbar_wait(full2 + 8 * s, ph_s, ctx, 24))) break;
         tc_fence_after();
         const uint32_t a_tmem = tmem_base + T::kColXr + xb * T::kUnitK + su * (T::kBK / 2);
@@ -263,28 +262,33 @@ oft_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ C
         uint32_t ph_s_n = ph_s, ph_xb_n = ph_xb;
         if (s_n == T::kS2) { s_n = 0; ph_s_n ^= 1; }
         if (unit_ends && ++xb_n == T::kXrBufs) { xb_n = 0; ph_xb_n ^= 1; }
+        const int su_n = unit_ends ? 0 : su + 1;
 #pragma unroll
         for (int kk = 0; kk < T::kBK / 16; ++kk) {
           if (kk == 2) {
             const bool more = j + 1 < total_stages;
             have_full = more && mbar_test_wait(full2 + 8 * s_n, ph_s_n);
-            have_half = more && unit_ends && mbar_test_wait(x_half + 8 * xb_n, ph_xb_n);
+            have_half = more && mbar_test_wait(x_half + 8 * (xb_n * T::kStagesPerUnit + su_n), ph_xb_n);
           }
           const uint32_t accum = (su > 0 || kk > 0) ? 1u : (ku > 0 ? 1u : 0u);
           umma_f16_ts(tmem_base + T::kColAcc, a_tmem + kk * 8, b_desc + kk * 2, idesc2, accum);
         }
+        // (committing a stage only after the next stage's first MMAs are queued was tried and cost
+        // 15-20 % in cycles: the release has to follow its MMAs directly)
         umma_commit(empty2 + 8 * s);
+        if (unit_ends) {
+          umma_commit(x_empty + 8 * xb);
+          if (ku + 1 == units) umma_commit(acc_full);
+        }
         s = s_n;
         ph_s = ph_s_n;
         if (unit_ends) {
-          umma_commit(x_empty + 8 * xb);
           trace_stamp(ctx, u, 5);
           xb = xb_n;
           ph_xb = ph_xb_n;
           su = 0;
           ++u;
           if (++ku == units) {
-            umma_commit(acc_full);
             ku = 0;
             ph_acc ^= 1;
           }
@@ -328,10 +332,11 @@ oft_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ C
         }
         tmem_st_x16(buf + h * 32, p0);
         tmem_st_x16(buf + h * 32 + 16, p1);
+        // each 64-column slice is handed to MMA2 as soon as it is written (b = 128 has two per unit)
+        tmem_wait_st();
+        tc_fence_before();
+        mbar_arrive(x_half + 8 * (xb * T::kStagesPerUnit + h));
       }
-      tmem_wait_st();
-      tc_fence_before();
-      mbar_arrive(x_half + 8 * xb);
       if (threadIdx.x == 128) trace_stamp(ctx, g, 3);
 #ifdef B200_PROFILE_WAITS
       if (threadIdx.x == 128) { ctx.prof_cycles[3] += clock64() - cv0; ctx.prof_count[3] += 1; ctx.prof_site[3] = 51; }  // unit converted
