@@ -13,4 +13,5 @@ struct CurrCompParams {
   static const unsigned int bK = 64;
   static const unsigned int bP1 = 3;
   static const unsigned int bP2 = 4;
+  static const int ctas = 1;
 };

@@ -5,9 +5,11 @@
 // with the checks the reference leaves out (shape, alignment, shared-memory opt-in).
 #include <cstdarg>
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 #include <mutex>
 #include <string>
+#include <type_traits>
 
 #include <cuda.h>
 #include <cuda_fp16.h>
@@ -19,6 +21,7 @@
 #include "gemm_kernel.cuh"
 #include "gemm2_kernel.cuh"
 #include "oft_kernel.cuh"
+#include "oft2_kernel.cuh"
 
 namespace {
 
@@ -109,6 +112,16 @@ int make_map(CUtensorMap* map, const void* base, int elem_bytes, long long inner
   return B200_OK;
 }
 
+// Tile order of a launch.  B200_RASTER (integer) overrides it for experiments.
+int raster_for(long long b_bytes, bool oft) {
+  if (const char* e = std::getenv("B200_RASTER")) return std::atoi(e);
+  // Measured on the GPU: the two orders cost the same cycles, but when B is larger than what L2 keeps
+  // beside the A panels, bands of 8 tile rows move less data, draw less power and so run at a higher
+  // clock under the power cap (OFT slab M 65536, N 3584, K 8192: 668 -> 748 TFLOP/s).  The plain GEMM
+  // at 8192^3 showed no gain and keeps the z-curve.
+  return (oft && b_bytes > (40ll << 20)) ? 8 : 0;
+}
+
 template <class Kernel>
 int opt_in_smem(Kernel kernel, int bytes) {
   // The reference never raises the dynamic shared-memory limit and so cannot launch any tile
@@ -155,7 +168,7 @@ int launch_gemm(int m, int n, int k, const void* A, int ldA, const void* B, int 
     if (int rc = make_map(&ma, A, sizeof(TIn), m, k, ldA, T1::kChunk, T1::kBK, "A", T1::kA32Atom)) return rc;
     if (int rc = make_map(&mb, B, sizeof(TIn), n, k, ldB, T1::kChunk, T1::kBK, "B", T1::kB32Atom)) return rc;
   }
-  GemmArgs args{m, n, k, C, ldC, st->status};
+  GemmArgs args{m, n, k, C, ldC, st->status, raster_for(static_cast<long long>(n) * k * sizeof(TIn), false)};
   if constexpr (kPair) {
     auto kernel = gemm2_kernel<T2>;
     if (int rc = opt_in_smem(kernel, T2::kSmemBytes)) return rc;
@@ -174,10 +187,16 @@ int launch_gemm(int m, int n, int k, const void* A, int ldA, const void* B, int 
 }
 
 // ---- fused OFT ---------------------------------------------------------------------------------------
+// ctas = 2 in oft_config.hpp selects the CTA-pair kernel (256 x bN tile per pair of SMs).
+constexpr bool kOftPair = CtasOf<CurrCompParams>::value == 2;
+template <int kB>
+using OftT = std::conditional_t<kOftPair, Oft2Traits<kB, CurrCompParams::bN, CurrCompParams::bP1, CurrCompParams::bP2>,
+                                OftTraits<kB, CurrCompParams::bN, CurrCompParams::bP1, CurrCompParams::bP2>>;
+
 template <int kB>
 int launch_oft(int m, int n, int k, int group_size, const void* A, int ldA, const void* B, int ldB, const void* R, int ldR,
                void* C, int ldC, cudaStream_t stream, DeviceState* st) {
-  using T = OftTraits<kB, CurrCompParams::bN, CurrCompParams::bP1, CurrCompParams::bP2>;
+  using T = OftT<kB>;
   static_assert(CurrCompParams::bM == T::kBM && CurrCompParams::bK == T::kBK, "oft_config.hpp: bM must be 128 and bK 64");
   if constexpr (!T::kFits) {
     return fail(B200_EUNSUPPORTED, "reconn_sz=%d needs %d bytes of shared memory with this tile configuration (limit 232448)", kB, T::kSmemBytes);
@@ -185,16 +204,24 @@ int launch_oft(int m, int n, int k, int group_size, const void* A, int ldA, cons
   if (group_size != n && group_size % T::kBN != 0)
     return fail(B200_EUNSUPPORTED, "group_size=%d must equal n or be a multiple of the N tile %d", group_size, T::kBN);
   const int n_groups = n / group_size;
+  constexpr int kRowsPerCta = kOftPair ? 2 : 1;  // a pair splits the R tile and the B tile between its CTAs
   CUtensorMap ma, mr, mb;
   if (int rc = make_map(&ma, A, 2, k, m, ldA, T::kBK, T::kBM, "A")) return rc;
-  if (int rc = make_map(&mr, R, 2, k, static_cast<long long>(n_groups) * kB, ldR, T::kBK, kB, "R")) return rc;
-  if (int rc = make_map(&mb, B, 2, k, n, ldB, T::kBK, T::kBN, "B")) return rc;
-  auto kernel = oft_kernel<T>;
-  if (int rc = opt_in_smem(kernel, T::kSmemBytes)) return rc;
-  const long long tiles = static_cast<long long>((m + T::kBM - 1) / T::kBM) * ((n + T::kBN - 1) / T::kBN);
-  const int grid = static_cast<int>(tiles < st->sm_count ? tiles : st->sm_count);
-  OftArgs args{m, n, k, group_size, static_cast<__half*>(C), ldC, st->status};
-  kernel<<<grid, T::kThreads, T::kSmemBytes, stream>>>(ma, mr, mb, args);
+  if (int rc = make_map(&mr, R, 2, k, static_cast<long long>(n_groups) * kB, ldR, T::kBK, kB / kRowsPerCta, "R")) return rc;
+  if (int rc = make_map(&mb, B, 2, k, n, ldB, T::kBK, T::kBN / kRowsPerCta, "B")) return rc;
+  OftArgs args{m, n, k, group_size, static_cast<__half*>(C), ldC, st->status, raster_for(static_cast<long long>(n) * k * 2, true)};
+  const long long tiles = static_cast<long long>((m + kRowsPerCta * T::kBM - 1) / (kRowsPerCta * T::kBM)) * ((n + T::kBN - 1) / T::kBN);
+  if constexpr (kOftPair) {
+    auto kernel = oft2_kernel<T>;
+    if (int rc = opt_in_smem(kernel, T::kSmemBytes)) return rc;
+    const int pairs = static_cast<int>(tiles < st->sm_count / 2 ? tiles : st->sm_count / 2);
+    kernel<<<2 * pairs, T::kThreads, T::kSmemBytes, stream>>>(ma, mr, mb, args);  // cluster dimension (2,1,1) is part of the kernel
+  } else {
+    auto kernel = oft_kernel<T>;
+    if (int rc = opt_in_smem(kernel, T::kSmemBytes)) return rc;
+    const int grid = static_cast<int>(tiles < st->sm_count ? tiles : st->sm_count);
+    kernel<<<grid, T::kThreads, T::kSmemBytes, stream>>>(ma, mr, mb, args);
+  }
   CUDA_TRY(cudaGetLastError());
   return B200_OK;
   }
@@ -406,15 +433,15 @@ const char* b200_kernel_info(void) {
   static char buf[768];
   using PH = Params<half, half, MMA_T, MMA_N>;
   using PF = Params<float, float, MMA_N, MMA_T>;
-  using O64 = OftTraits<64, CurrCompParams::bN, CurrCompParams::bP1, CurrCompParams::bP2>;
-  using O128 = OftTraits<128, CurrCompParams::bN, CurrCompParams::bP1, CurrCompParams::bP2>;
+  using O64 = OftT<64>;
+  using O128 = OftT<128>;
   snprintf(buf, sizeof buf,
            "{\"arch\": \"sm_100a\", \"gemm_half_tn\": {\"bM\": %d, \"bN\": %d, \"bK\": %d, \"bP\": %d}, "
            "\"gemm_float_nt\": {\"bM\": %d, \"bN\": %d, \"bK\": %d, \"bP\": %d}, "
-           "\"oft\": {\"bM\": %d, \"bN\": %d, \"bK\": %d, \"bP1\": %d, \"bP2\": %d, \"threads\": %d, "
+           "\"oft\": {\"ctas\": %d, \"bM\": %d, \"bN\": %d, \"bK\": %d, \"bP1\": %d, \"bP2\": %d, \"threads\": %d, "
            "\"b64\": {\"smem\": %d, \"tmem_cols\": %d, \"xr_bufs\": %d}, "
            "\"b128\": {\"smem\": %d, \"tmem_cols\": %d, \"xr_bufs\": %d}}}",
-           PH::bM, PH::bN, PH::bK, PH::bP, PF::bM, PF::bN, PF::bK, PF::bP, (int)CurrCompParams::bM, (int)CurrCompParams::bN,
+           PH::bM, PH::bN, PH::bK, PH::bP, PF::bM, PF::bN, PF::bK, PF::bP, kOftPair ? 2 : 1, (int)CurrCompParams::bM, (int)CurrCompParams::bN,
            (int)CurrCompParams::bK, (int)CurrCompParams::bP1, (int)CurrCompParams::bP2, O64::kThreads, O64::kSmemBytes,
            O64::kTmemUsed, O64::kXrBufs, O128::kSmemBytes, O128::kTmemUsed, O128::kXrBufs);
   return buf;

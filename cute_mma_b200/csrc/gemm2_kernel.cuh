@@ -99,7 +99,7 @@ gemm2_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__
       bool ok = true;
       for (unsigned tile = pair; ok && tile < num_tiles; tile += num_pairs) {
         unsigned tm, tn;
-        tile_coord(tiles_m, tiles_n, tile, tm, tn);
+        tile_coord_r(args.raster, tiles_m, tiles_n, tile, tm, tn);
         const int m0 = tm * 2 * T::kBM + rank * T::kBM;      // this CTA's rows of A and C
         const int n0 = tn * T::kBN + rank * T::kBNHalf;      // this CTA's half of the B tile
         for (int ks = 0; ks < k_steps; ++ks, ++it) {
@@ -173,7 +173,7 @@ gemm2_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__
     TOut* __restrict__ C = reinterpret_cast<TOut*>(args.C);
     for (unsigned tile = pair; ok && tile < num_tiles; tile += num_pairs, ++tcount) {
       unsigned tm, tn;
-      tile_coord(tiles_m, tiles_n, tile, tm, tn);
+      tile_coord_r(args.raster, tiles_m, tiles_n, tile, tm, tn);
       const int a = tcount % T::kAccBufs;
       if (!(ok = mbar_wait_warp(accfull_bar(a), (tcount / T::kAccBufs) & 1, ctx, 4))) break;
       tc_fence_after();

@@ -46,6 +46,7 @@ struct GemmArgs {
   void* C;
   long long ldC;
   int* status;
+  int raster;  // 0: z-curve tile order; g > 0: bands of g tile rows
 };
 
 template <class T>
@@ -98,7 +99,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
       bool ok = true;
       for (unsigned tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x) {
         unsigned tm, tn;
-        tile_coord(tiles_m, tiles_n, tile, tm, tn);
+        tile_coord_r(args.raster, tiles_m, tiles_n, tile, tm, tn);
         const int m0 = tm * T::kBM, n0 = tn * T::kBN;
         for (int ks = 0; ks < k_steps; ++ks, ++it) {
           const int s = it % T::kStages;
@@ -175,7 +176,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
     TOut* __restrict__ C = reinterpret_cast<TOut*>(args.C);
     for (unsigned tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x, ++tcount) {
       unsigned tm, tn;
-      tile_coord(tiles_m, tiles_n, tile, tm, tn);
+      tile_coord_r(args.raster, tiles_m, tiles_n, tile, tm, tn);
       const int a = tcount % T::kAccBufs;
       if (!(ok = mbar_wait_warp(accfull_bar(a), (tcount / T::kAccBufs) & 1, ctx, 4))) break;
       tc_fence_after();

@@ -59,6 +59,7 @@ struct OftArgs {
   __half* C;
   long long ldC;
   int* status;
+  int raster;  // 0: z-curve tile order; g > 0: bands of g tile rows
 };
 
 template <class T>
@@ -131,7 +132,7 @@ oft_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ C
       bool ok = true;
       for (unsigned tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x) {
         unsigned tm, tn;
-        tile_coord(tiles_m, tiles_n, tile, tm, tn);
+        tile_coord_r(args.raster, tiles_m, tiles_n, tile, tm, tn);
         const int m0 = tm * T::kBM;
         const int r_row0 = ((tn * T::kBN) / args.group_size) * T::kB;  // first stored R row of this tile's group
         for (int st = 0; st < units * T::kStagesPerUnit; ++st, ++it) {
@@ -158,7 +159,7 @@ oft_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ C
       bool ok = true;
       for (unsigned tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x) {
         unsigned tm, tn;
-        tile_coord(tiles_m, tiles_n, tile, tm, tn);
+        tile_coord_r(args.raster, tiles_m, tiles_n, tile, tm, tn);
         const int n0 = tn * T::kBN;
         for (int st = 0; st < units * T::kStagesPerUnit; ++st, ++it) {
           const int s = it % T::kS2;
@@ -353,7 +354,7 @@ oft_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ C
     bool ok = true;
     for (unsigned tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x, ++tcount) {
       unsigned tm, tn;
-      tile_coord(tiles_m, tiles_n, tile, tm, tn);
+      tile_coord_r(args.raster, tiles_m, tiles_n, tile, tm, tn);
       if (!(ok = mbar_wait_warp(acc_full, tcount & 1, ctx, 40))) break;
       tc_fence_after();
       const int row = tm * T::kBM + quad * 32 + lane;

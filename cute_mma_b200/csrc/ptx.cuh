@@ -261,7 +261,7 @@ __device__ __forceinline__ uint32_t mapa_shared(uint32_t addr, uint32_t rank) {
   return r;
 }
 __device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
-  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+  asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
 }
 // In a CTA pair the shared-window address carries the CTA's rank in bit 24; clearing it names the
 // same location in the even (leader) CTA.
@@ -371,6 +371,21 @@ __host__ __device__ inline void tile_coord(unsigned tiles_m, unsigned tiles_n, u
     rem_m /= pm;
     rem_n /= pn;
   }
+}
+
+// Tile order selected at launch: raster <= 0 is the z-curve above; raster = g > 0 walks bands of g tile
+// rows, inside a band tile-column by tile-column (m fastest), so the g row panels of A stay in L2 while
+// the band sweeps once over all of B.  Better than the z-curve when B is much larger than L2.
+__host__ __device__ inline void tile_coord_r(int raster, unsigned tiles_m, unsigned tiles_n, unsigned idx, unsigned& tm, unsigned& tn) {
+  if (raster <= 0) {
+    tile_coord(tiles_m, tiles_n, idx, tm, tn);
+    return;
+  }
+  const unsigned g = static_cast<unsigned>(raster);
+  const unsigned band = idx / (g * tiles_n), r = idx % (g * tiles_n);
+  const unsigned rows = (tiles_m - band * g) < g ? (tiles_m - band * g) : g;
+  tn = r / rows;
+  tm = band * g + r % rows;
 }
 
 }  // namespace b200

@@ -15,10 +15,10 @@ def test_generator_writes_complete_include_dirs(tmp_path):
     for r in rows:
         d = tmp_path / r["config"]
         text = (d / "oft_config.hpp").read_text()
-        assert f"bN = {r['bN']};" in text and f"bP1 = {r['bP1']};" in text and f"bP2 = {r['bP2']};" in text
+        assert f"bN = {r['bN']};" in text and f"bP1 = {r['bP1']};" in text and f"bP2 = {r['bP2']};" in text and f"ctas = {r['ctas']};" in text
         assert (d / "gemm_config.hpp").exists()
         assert r["smem"] <= gen.SMEM_LIMIT
-    assert (tmp_path / "config_csvs" / "param.csv").read_text().startswith("config,bN,bP1,bP2,smem")
+    assert (tmp_path / "config_csvs" / "param.csv").read_text().startswith("config,ctas,bN,bP1,bP2,smem")
     # the larger R tile of b = 128 rules out more candidates, and needs two XR buffers in tensor memory
     assert len(list(gen.candidates(128))) < len(rows)
     assert all((512 - c["bN"]) // 128 >= 2 for c in gen.candidates(128))
@@ -28,8 +28,8 @@ def test_smem_formula_matches_the_library(lib):
     from cute_mma_b200 import ops
 
     info = ops.kernel_info(lib)["oft"]
-    assert gen.smem_bytes(info["bN"], info["bP1"], info["bP2"], 64) == info["b64"]["smem"]
-    assert gen.smem_bytes(info["bN"], info["bP1"], info["bP2"], 128) == info["b128"]["smem"]
+    assert gen.smem_bytes(info["bN"], info["bP1"], info["bP2"], 64, info["ctas"]) == info["b64"]["smem"]
+    assert gen.smem_bytes(info["bN"], info["bP1"], info["bP2"], 128, info["ctas"]) == info["b128"]["smem"]
 
 
 def test_stdout_contract_is_parsed_like_the_reference():
