@@ -38,7 +38,13 @@ NOMINAL_FP16_TFLOPS = 2250.0  # vendor dense fp16 figure, context only
 
 # DRAM bytes of one launch of the dominant kernel, from the ncu capture summarised under profiles/
 # (dram__bytes_read.sum + dram__bytes_write.sum); None until a capture exists for the workload.
-NCU_TRAFFIC_BYTES = {}
+NCU_TRAFFIC_BYTES = {
+    # per launch at N = 1, ncu one-pass counters on the full workload (read 85.7 GB + write 5.8 GB; 17x the
+    # algorithmic 5.3 GB: concurrently running tiles share their panels of X and W through L2 only partly)
+    "oft_large_m65536_k8192_n28672_b128": 91.55e9,
+    # ncu --set full capture of the same shape (read 363 MB + write 154 MB; algorithmic 303 MB)
+    "oft_proj_m16384_k4096_n4096_b64": 517.2e6,
+}
 
 
 def measured_peaks():
@@ -183,6 +189,38 @@ def run_reference_arm(args, workload):
 # --------------------------------------------------------------------------------------- GPU arm
 
 
+def projection_shape_rate(lib, dev, stream):
+    """Device-timed rate of the single-GPU projection shape (M 16384, K = N 4096, b 64, Cayley blocks),
+    reported beside the headline workload at N = 1: 50 launches after 5 warm-up launches."""
+    import torch
+
+    from cute_mma_b200 import inputs, ops
+
+    name = "oft_proj_m16384_k4096_n4096_b64"
+    m, k, n, b, _, wsigma = WORKLOADS[name]
+    g = torch.Generator(device=dev).manual_seed(99)
+    dX = torch.randn((m, k), generator=g, device=dev, dtype=torch.float32).to(torch.float16)
+    dW = (torch.randn((n, k), generator=g, device=dev, dtype=torch.float32) * wsigma).to(torch.float16)
+    dR = torch.from_numpy(inputs.pack_r(inputs.blocks_cayley(1, k // b, b, 7))).to(dev)
+    dY = torch.empty((m, n), dtype=torch.float16, device=dev)
+    for _ in range(5):
+        ops.oft_tn(m, n, k, dX, k, dW, k, dR, k, dY, n, stream, reconn_sz=b, lib=lib)
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record(stream)
+    for _ in range(50):
+        ops.oft_tn(m, n, k, dX, k, dW, k, dR, k, dY, n, stream, reconn_sz=b, lib=lib)
+    e1.record(stream)
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / 50
+    assert ops.device_status(lib)[0] == 0
+    tf = flops_of(m, k, n, b) / (ms * 1e-3) * 1e-12
+    peaks = measured_peaks()
+    return {"workload": name, "value": tf, "unit": "TFLOP/s", "ms_per_step": ms, "steps": 50,
+            "frac_of_measured_bf16_burst": tf / peaks["bf16_burst"], "frac_of_nominal_fp16": tf / NOMINAL_FP16_TFLOPS}
+
+
+
 def run_gpu_arm(args, workload):
     import numpy as np
     import torch
@@ -199,6 +237,8 @@ def run_gpu_arm(args, workload):
     dev = torch.device("cuda", local_rank)
     if world > 1:
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        if os.environ.get("NCCL_DEBUG", "").upper() in ("", "VERSION"):
+            os.environ["NCCL_DEBUG"] = "WARN"  # keep NCCL's version banner off stdout: rank 0 prints one JSON line
         dist.init_process_group("nccl", device_id=dev)
     lib = ops.load_library()  # raises if the CUDA library is missing: there is no fallback
 
@@ -307,7 +347,7 @@ def run_gpu_arm(args, workload):
                        "kernel": ops.kernel_info(lib)["oft"]},
             "roofline": {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak,
                          "peak_source": f"{peaks['source']} bf16 {'sustained' if timed_s >= 2.0 else 'burst'} (cuBLAS matmul on this pool)",
-                         "traffic": NCU_TRAFFIC_BYTES.get(workload), "frac_of_nominal_fp16": achieved / NOMINAL_FP16_TFLOPS,
+                         "traffic": (NCU_TRAFFIC_BYTES.get(workload) if world == 1 else None), "frac_of_nominal_fp16": achieved / NOMINAL_FP16_TFLOPS,
                          "kernel": "oft_kernel", "launch_ms": ms_local},
             "e2e": {"value": total_flops / e2e_s * 1e-12, "unit": "TFLOP/s", "h2d_bytes_per_step": int(th[0].item()),
                     "d2h_bytes_per_step": int(th[1].item()), "ms_per_step": e2e_s * 1e3, "steps": args.e2e_steps,
@@ -316,6 +356,8 @@ def run_gpu_arm(args, workload):
         }
         if allgather_ms is not None:
             line["allgather_y_ms"] = allgather_ms
+        if world == 1 and workload == DEFAULT_WORKLOAD:
+            line["also"] = projection_shape_rate(lib, dev, stream)
         if world == 1 and not args.no_cpu_baseline:
             cb = cpu_reference_rate(m, k, n, b, kind, 12.0)
             cb.pop("seconds", None)

@@ -209,7 +209,16 @@ int launch_oft(int m, int n, int k, int group_size, const void* A, int ldA, cons
   if (int rc = make_map(&ma, A, 2, k, m, ldA, T::kBK, T::kBM, "A")) return rc;
   if (int rc = make_map(&mr, R, 2, k, static_cast<long long>(n_groups) * kB, ldR, T::kBK, kB / kRowsPerCta, "R")) return rc;
   if (int rc = make_map(&mb, B, 2, k, n, ldB, T::kBK, T::kBN / kRowsPerCta, "B")) return rc;
-  OftArgs args{m, n, k, group_size, static_cast<__half*>(C), ldC, st->status, raster_for(static_cast<long long>(n) * k * 2, true)};
+  const int raster = raster_for(static_cast<long long>(n) * k * 2, true);
+  // L2 eviction priorities of the A and B loads.  Keeping the band's rows of A (evict_last) and streaming B
+  // (evict_first) was measured at the large workload: 10 % less DRAM traffic but no gain in time, so both
+  // stay at normal priority.
+  unsigned long long hint_a = kL2EvictNormal, hint_b = kL2EvictNormal;
+  if (const char* e = std::getenv("B200_L2_HINTS")) {  // experiments: two letters out of n/f/l for A and B
+    auto pick = [](char c) { return c == 'f' ? kL2EvictFirst : (c == 'l' ? kL2EvictLast : kL2EvictNormal); };
+    if (e[0] && e[1]) { hint_a = pick(e[0]); hint_b = pick(e[1]); }
+  }
+  OftArgs args{m, n, k, group_size, static_cast<__half*>(C), ldC, st->status, raster, hint_a, hint_b};
   const long long tiles = static_cast<long long>((m + kRowsPerCta * T::kBM - 1) / (kRowsPerCta * T::kBM)) * ((n + T::kBN - 1) / T::kBN);
   if constexpr (kOftPair) {
     auto kernel = oft2_kernel<T>;

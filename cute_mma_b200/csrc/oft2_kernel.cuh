@@ -123,8 +123,8 @@ oft2_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
           if (!(ok = mbar_wait(empty1 + 8 * s, ((it / T::kS1) & 1) ^ 1, ctx, 10))) break;
           if (rank == 0) mbar_expect_tx(full1 + 8 * s, 2 * T::kS1Bytes);
           const uint32_t a_dst = ring1 + s * T::kS1Bytes;
-          tma_load_2d_pair(a_dst, &tmap_a, full1 + 8 * s, st * T::kBK, m0);
-          tma_load_2d_pair(a_dst + T::kABytes, &tmap_r, full1 + 8 * s, st * T::kBK, r_row0);
+          tma_load_2d_pair_hint(a_dst, &tmap_a, full1 + 8 * s, st * T::kBK, m0, args.hint_a);
+          tma_load_2d_pair_hint(a_dst + T::kABytes, &tmap_r, full1 + 8 * s, st * T::kBK, r_row0, kL2EvictLast);
         }
       }
     }
@@ -143,7 +143,7 @@ oft2_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
           const int s = it % T::kS2;
           if (!(ok = mbar_wait(empty2 + 8 * s, ((it / T::kS2) & 1) ^ 1, ctx, 11))) break;
           if (rank == 0) mbar_expect_tx(full2 + 8 * s, 2 * T::kS2Bytes);
-          tma_load_2d_pair(ring2 + s * T::kS2Bytes, &tmap_b, full2 + 8 * s, st * T::kBK, n0);
+          tma_load_2d_pair_hint(ring2 + s * T::kS2Bytes, &tmap_b, full2 + 8 * s, st * T::kBK, n0, args.hint_b);
         }
       }
     }

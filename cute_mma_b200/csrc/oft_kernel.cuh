@@ -60,6 +60,7 @@ struct OftArgs {
   long long ldC;
   int* status;
   int raster;  // 0: z-curve tile order; g > 0: bands of g tile rows
+  unsigned long long hint_a, hint_b;  // L2 eviction priority of the A and B tile loads (pair kernel)
 };
 
 template <class T>
