@@ -76,7 +76,7 @@ class ClockSampler:
         try:
             self.out = tempfile.NamedTemporaryFile("w+", suffix=".csv", delete=False)
             self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.gpu), f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
-                                          "-lms", "100"], stdout=self.out, stderr=subprocess.DEVNULL)
+                                          "-lms", "20"], stdout=self.out, stderr=subprocess.DEVNULL)
         except Exception:
             self.proc = None
 

@@ -236,6 +236,41 @@ int launch_oft(int m, int n, int k, int group_size, const void* A, int ldA, cons
   }
 }
 
+// ---- reconn_sz = 8 -----------------------------------------------------------------------------------
+// tcgen05.mma needs N >= 16 and K = 16, so 8 x 8 blocks cannot be multiplied one by one.  Two
+// neighbouring blocks (kb = 2j, 2j+1) of a group are embedded in one 16 x 16 block that is zero outside
+// its two 8 x 8 diagonal corners, which leaves every sum unchanged (the added products are exact zeros):
+//   Rx[g*16 + q'][16j + p'] = R[g*8 + (q' & 7)][16j + p']  if (q' >= 8) == (p' >= 8),  else 0
+// and the product then runs as reconn_sz = 16 on Rx.  Rx is device scratch of 2x the size of R.
+__global__ void expand_r8_kernel(const __half* __restrict__ R, long long ldR, __half* __restrict__ Rx, long long ldx,
+                                 int n_groups, int k) {
+  const long long chunks_per_row = ldx / 8;  // 8 halves = 16 bytes = one 8-wide block column
+  const long long total = static_cast<long long>(n_groups) * 16 * chunks_per_row;
+  for (long long idx = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; idx < total;
+       idx += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const long long row = idx / chunks_per_row, c8 = idx % chunks_per_row;
+    const int q = static_cast<int>(row % 16);
+    const long long g = row / 16;
+    uint4 v = make_uint4(0u, 0u, 0u, 0u);
+    if (((q >= 8) == ((c8 & 1) != 0)) && 8 * c8 < k)
+      v = *reinterpret_cast<const uint4*>(R + (g * 8 + (q & 7)) * ldR + 8 * c8);
+    *reinterpret_cast<uint4*>(Rx + row * ldx + 8 * c8) = v;
+  }
+}
+
+inline long long r8_ld(int k) { return (static_cast<long long>(k) + 15) / 16 * 16; }
+inline size_t r8_bytes(int n_groups, int k) { return static_cast<size_t>(n_groups) * 16 * r8_ld(k) * 2; }
+
+int expand_r8(const void* R, int ldR, void* Rx, int n_groups, int k, cudaStream_t stream) {
+  if (reinterpret_cast<uintptr_t>(R) & 15) return fail(B200_EINVAL, "R: base pointer must be 16-byte aligned");
+  if ((static_cast<long long>(ldR) * 2) % 16 != 0 || ldR < k) return fail(B200_EINVAL, "R: leading dimension %d must be >= k and a multiple of 8 elements", ldR);
+  const long long total = static_cast<long long>(n_groups) * 16 * (r8_ld(k) / 8);
+  const int blocks = static_cast<int>(total / 256 + 1 < 4096 ? total / 256 + 1 : 4096);
+  expand_r8_kernel<<<blocks, 256, 0, stream>>>(static_cast<const __half*>(R), ldR, static_cast<__half*>(Rx), r8_ld(k), n_groups, k);
+  CUDA_TRY(cudaGetLastError());
+  return B200_OK;
+}
+
 int oft_dispatch(int m, int n, int k, int group_size, int b, const void* A, int ldA, const void* B, int ldB, const void* R, int ldR,
                  void* C, int ldC, cudaStream_t stream) {
   g_err.clear();
@@ -252,12 +287,21 @@ int oft_dispatch(int m, int n, int k, int group_size, int b, const void* A, int 
   }
   DeviceState* st;
   if (int rc = device_state(&st)) return rc;
+  if (b == 8) {  // scratch from the stream-ordered allocator: no device-wide synchronisation, no sharing between calls
+    const int n_groups = n / group_size;
+    void* rx = nullptr;
+    CUDA_TRY(cudaMallocAsync(&rx, r8_bytes(n_groups, k), stream));
+    int rc = expand_r8(R, ldR, rx, n_groups, k, stream);
+    if (rc == B200_OK) rc = launch_oft<16>(m, n, k, group_size, A, ldA, B, ldB, rx, static_cast<int>(r8_ld(k)), C, ldC, stream, st);
+    cudaFreeAsync(rx, stream);
+    return rc;
+  }
   switch (b) {
     case 16: return launch_oft<16>(m, n, k, group_size, A, ldA, B, ldB, R, ldR, C, ldC, stream, st);
     case 32: return launch_oft<32>(m, n, k, group_size, A, ldA, B, ldB, R, ldR, C, ldC, stream, st);
     case 64: return launch_oft<64>(m, n, k, group_size, A, ldA, B, ldB, R, ldR, C, ldC, stream, st);
     case 128: return launch_oft<128>(m, n, k, group_size, A, ldA, B, ldB, R, ldR, C, ldC, stream, st);
-    default: return fail(B200_EUNSUPPORTED, "reconn_sz=%d not compiled in (16, 32, 64, 128)", b);
+    default: return fail(B200_EUNSUPPORTED, "reconn_sz=%d not compiled in (8, 16, 32, 64, 128)", b);
   }
 }
 
@@ -288,7 +332,12 @@ std::mutex g_static_mu;
 
 // Device scratch one fused-OFT launch needs beyond its inputs and outputs: the status record of the
 // bounded waits followed by the wait-profile words (the same layout the allocated workspace has).
-size_t oft_scratch_bytes(int /*m*/, int /*n*/, int /*k*/, int /*reconn_sz*/) { return kWorkspaceBytes; }
+// reconn_sz = 8 adds the expanded copy of R (see expand_r8_kernel) at kStaticRxOffset.
+constexpr size_t kStaticRxOffset = 4096;
+static_assert(kWorkspaceBytes <= kStaticRxOffset, "status record and profile words must fit below the expanded R");
+size_t oft_scratch_bytes(int n_groups, int k, int reconn_sz) {
+  return reconn_sz == 8 ? kStaticRxOffset + r8_bytes(n_groups, k) : kWorkspaceBytes;
+}
 
 // Once per device, with that device current.  Calls nothing that allocates device memory.
 int static_scratch_state(StaticScratchState** out) {
@@ -486,7 +535,7 @@ int b200_oft_tn_f16_static(int m, int n, int k, int group_size, int reconn_sz, c
   if (n % group_size != 0) return fail(B200_EINVAL, "n=%d is not a multiple of group_size=%d", n, group_size);
   if (ldC < n) return fail(B200_EINVAL, "ldC=%d smaller than n=%d (C is row-major)", ldC, n);
   if (m > 0 && n > 0 && k > 0 && !R) return fail(B200_EINVAL, "R is null");
-  const size_t need = oft_scratch_bytes(m, n, k, reconn_sz);
+  const size_t need = oft_scratch_bytes(n / group_size, k, reconn_sz);
   if (need > kStaticScratchBytes)
     return fail(B200_EUNSUPPORTED, "this problem needs %zu bytes of device scratch; the static scratch of b200_oft_tn_f16_static holds %zu",
                 need, kStaticScratchBytes);
@@ -503,12 +552,17 @@ int b200_oft_tn_f16_static(int m, int n, int k, int group_size, int reconn_sz, c
   DeviceState view;  // what the launcher reads: SM count and where the kernel's scratch is
   view.sm_count = ss->sm_count;
   view.status = static_cast<int*>(ss->scratch);
+  if (reconn_sz == 8) {
+    void* rx = static_cast<unsigned char*>(ss->scratch) + kStaticRxOffset;
+    if (int rc = expand_r8(R, ldR, rx, n / group_size, k, stream)) return rc;
+    return launch_oft<16>(m, n, k, group_size, A, ldA, B, ldB, rx, static_cast<int>(r8_ld(k)), C, ldC, stream, &view);
+  }
   switch (reconn_sz) {
     case 16: return launch_oft<16>(m, n, k, group_size, A, ldA, B, ldB, R, ldR, C, ldC, stream, &view);
     case 32: return launch_oft<32>(m, n, k, group_size, A, ldA, B, ldB, R, ldR, C, ldC, stream, &view);
     case 64: return launch_oft<64>(m, n, k, group_size, A, ldA, B, ldB, R, ldR, C, ldC, stream, &view);
     case 128: return launch_oft<128>(m, n, k, group_size, A, ldA, B, ldB, R, ldR, C, ldC, stream, &view);
-    default: return fail(B200_EUNSUPPORTED, "reconn_sz=%d not compiled in (16, 32, 64, 128)", reconn_sz);
+    default: return fail(B200_EUNSUPPORTED, "reconn_sz=%d not compiled in (8, 16, 32, 64, 128)", reconn_sz);
   }
 }
 

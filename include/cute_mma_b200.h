@@ -31,8 +31,10 @@ enum {
  *   A [m][k] ldA, B [n][k] ldB (= W^T), R [(n/group_size)*reconn_sz][k] ldR, C [m][n] ldC, all fp16,
  *   all row-major; stored R block (g,kb) = rows g*b.., cols kb*b.. holds the TRANSPOSE of the
  *   mathematical rotation.  fp32 accumulation, X.R rounded to fp16 (RNE) before the main product.
- * reconn_sz in {16, 32, 64, 128}; k % reconn_sz == 0; n % group_size == 0; group_size == n or a
- * multiple of the kernel's N tile. */
+ * reconn_sz in {8, 16, 32, 64, 128}; k % reconn_sz == 0; n % group_size == 0; group_size == n or a
+ * multiple of the kernel's N tile.  reconn_sz = 8 (the reference's default) first expands R into pairs of
+ * 8 x 8 blocks embedded in zero-padded 16 x 16 blocks (device scratch of twice the size of R, taken from
+ * the stream-ordered allocator, cudaMallocAsync / cudaFreeAsync on `stream`) and then runs as 16. */
 int b200_oft_tn_f16(int m, int n, int k, int group_size, int reconn_sz,
                     const void* A, int ldA, const void* B, int ldB, const void* R, int ldR,
                     void* C, int ldC, void* stream);
@@ -51,7 +53,8 @@ int b200_oft_tn_f16_host(int m, int n, int k, int group_size, int reconn_sz,
  * first time it runs on a device; this entry point calls no cudaMalloc, no cudaFree and no allocating
  * library routine, ever.  The device scratch its kernel needs beyond A, B, R and C (the record in which
  * a kernel reports a bounded wait that ran out, plus the profiling words of -DB200_PROFILE_WAITS builds:
- * about 3 KB today) lives in a 64 KB array inside the library image, which every GPU that loads the
+ * about 3 KB, plus for reconn_sz = 8 the expanded copy of R: 32 * (n / group_size) * k bytes) lives in a
+ * 64 KB array inside the library image, which every GPU that loads the
  * library keeps until the process exits.  A problem whose scratch need exceeds those 64 KB is refused
  * with B200_EUNSUPPORTED and a message naming both sizes.
  *   - Arguments, layouts and result are exactly those of b200_oft_tn_f16 (same kernel, same bits).

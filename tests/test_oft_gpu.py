@@ -54,6 +54,9 @@ CASES = [
     (72, 40, 128, 16, None),       # smaller than one tile
     (256, 512, 256, 32, 256),      # two N-groups, each with its own R
     (128, 768, 128, 16, 256),      # three groups
+    (256, 512, 256, 8, None),      # 8 x 8 blocks (the reference's default edge): expanded to 16 x 16 pairs
+    (200, 328, 264, 8, None),      # odd number of 8-wide blocks (K = 33 * 8), ragged M and N
+    (256, 512, 128, 8, 256),       # 8 x 8 blocks, two N-groups
 ]
 
 
@@ -172,6 +175,38 @@ def _sampled_parity(lib, cuda, m, n, k, b, kind, wsigma, n_rows, seed):
     diff = (dC2.float() - twice).abs()
     assert bool((diff <= twice.abs() * 2.0 ** -10 + 2.0 ** -13).all())
     assert float((diff != 0).float().mean()) < 1e-3
+
+
+def test_oft_reference_benchmark_point_sampled(lib, cuda):
+    """The reference's own benchmark point (autotune/runner_oft.py:64): M = N = K = 8192, group 256 (32
+    N-groups, each with its own R), 8 x 8 blocks; positive U[0,1) operands and permutation blocks as in
+    its driver, on sampled rows.  With K/b = 1024 re-roundings of a sum that grows to ~2000 (fp16 ulp 1-2)
+    cpu_oft_tn itself drifts from exact arithmetic by up to 2e-2 relative here, so the reference's
+    relative-error count (cute_oft_pc.cu:31-77, 5e-3) is applied against the exact result (fp64
+    accumulation of the same fp16 XR), and the oracle is compared with its own drift allowed for."""
+    import torch
+    from cute_mma_b200 import inputs
+
+    m = n = k = 8192
+    gs, b = 256, 8
+    G = n // gs
+    g = torch.Generator(device=cuda).manual_seed(8)
+    dA = torch.rand((m, k), generator=g, device=cuda).to(torch.float16)
+    dB = torch.rand((n, k), generator=g, device=cuda).to(torch.float16)
+    R = inputs.pack_r(inputs.blocks_permutation(G, k // b, b, 8))
+    dR = torch.from_numpy(R).to(cuda)
+    dC = torch.empty((m, n), dtype=torch.float16, device=cuda)
+    ops.oft_tn(m, n, k, dA, k, dB, k, dR, k, dC, n, group_size=gs, reconn_sz=b, lib=lib)
+    assert ops.device_status(lib)[0] == 0
+    rows = np.unique(np.concatenate([[0, 255, 256, m - 1], np.random.default_rng(8).integers(0, m, 12)]))
+    idx = torch.from_numpy(rows).to(cuda)
+    ref = oracle.cpu_oft_tn(dA[idx].cpu().numpy(), R, dB.cpu().numpy(), len(rows), gs, G, k, b, threads=oracle.num_threads())
+    got = dC[idx].cpu().numpy()
+    truth = oracle.oft_f64(dA[idx].cpu().numpy(), R, dB.cpu().numpy(), len(rows), gs, G, k, b, round_xr=True)
+    errors, worst = oracle.check_result(got, truth.astype(np.float16), 5e-3)
+    assert errors == 0, (errors, worst)
+    bad, worst_n = oft_ok(got, ref, truth=truth)
+    assert bad == 0, (bad, worst_n)
 
 
 def test_oft_projection_shape_sampled(lib, cuda):

@@ -46,5 +46,18 @@ def test_static_scratch_entry_point_validates_like_the_other(lib, cuda):
         ops.oft_tn_static(64, 64, 60, d, 64, d, 64, d, 64, d, 64, reconn_sz=16, lib=lib)  # k not a multiple of b
     assert e.value.code == ops.EINVAL
     with pytest.raises(ops.Error) as e:
-        ops.oft_tn_static(64, 64, 64, d, 64, d, 64, d, 64, d, 64, reconn_sz=8, lib=lib)   # block edge not built
+        ops.oft_tn_static(64, 64, 48, d, 64, d, 64, d, 64, d, 64, reconn_sz=24, lib=lib)  # block edge not built
     assert e.value.code == ops.EUNSUPPORTED
+
+
+def test_static_scratch_entry_point_small_blocks_and_its_size_limit(lib, cuda):
+    """8 x 8 blocks need an expanded copy of R as scratch: it fits the library's array for a small K and
+    is refused, with both sizes in the message, when it does not."""
+    want, got = _both(lib, cuda, 256, 512, 512, 8, seed=23)   # 16 rows x 512 columns of fp16 = 16 KB of scratch
+    assert np.array_equal(want.view(np.uint16), got.view(np.uint16))
+    import torch
+
+    d = torch.zeros(64 * 4096, dtype=torch.float16, device=cuda)
+    with pytest.raises(ops.Error) as e:
+        ops.oft_tn_static(64, 64, 4096, d, 4096, d, 4096, d, 4096, d, 64, reconn_sz=8, lib=lib)  # 128 KB needed
+    assert e.value.code == ops.EUNSUPPORTED and "65536" in e.value.message
