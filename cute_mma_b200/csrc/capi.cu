@@ -236,6 +236,21 @@ int launch_oft(int m, int n, int k, int group_size, const void* A, int ldA, cons
   }
 }
 
+// ---- self-test of the bounded-wait path ---------------------------------------------------------------
+// One thread waits on an mbarrier that nothing ever arrives on, with a short limit: the wait gives up,
+// records {code, CTA, site 99, parity} and the kernel returns normally.  Nothing faults or hangs.
+__global__ void wait_timeout_selftest_kernel(int* status, unsigned long long limit_ns) {
+  __shared__ uint64_t bar;
+  __shared__ int abort_flag;
+  if (threadIdx.x == 0) {
+    abort_flag = 0;
+    mbar_init(smem_u32(&bar), 1);
+    fence_mbar_init();
+    const WaitCtx ctx{&abort_flag, status, limit_ns};
+    (void)mbar_wait(smem_u32(&bar), 0, ctx, 99);
+  }
+}
+
 // ---- reconn_sz = 8 -----------------------------------------------------------------------------------
 // tcgen05.mma needs N >= 16 and K = 16, so 8 x 8 blocks cannot be multiplied one by one.  Two
 // neighbouring blocks (kb = 2j, 2j+1) of a group are embedded in one 16 x 16 block that is zero outside
@@ -467,6 +482,19 @@ int b200_device_status(int out[4]) {
     CUDA_TRY(cudaMemset(st->status, 0, sizeof host));
     return fail(B200_EDEVICE, "a bounded wait ran out in CTA %d at wait site %d (parity %d)", host[1], host[2], host[3]);
   }
+  return B200_OK;
+}
+
+int b200_selftest_wait_timeout(unsigned limit_us, int out[4]) {
+  g_err.clear();
+  if (limit_us == 0 || limit_us > 100000) return fail(B200_EINVAL, "limit_us must be in 1..100000");
+  DeviceState* st;
+  if (int rc = device_state(&st)) return rc;
+  wait_timeout_selftest_kernel<<<1, 32>>>(st->status, static_cast<unsigned long long>(limit_us) * 1000ull);
+  CUDA_TRY(cudaGetLastError());
+  const int rc = b200_device_status(out);  // synchronises, reads and clears the record
+  if (rc != B200_EDEVICE) return fail(B200_ECUDA, "the wait did not report a timeout (status call returned %d)", rc);
+  g_err.clear();
   return B200_OK;
 }
 

@@ -24,7 +24,7 @@ OK, EINVAL, EUNSUPPORTED, ECUDA, EDEVICE = 0, 1, 2, 3, 4
 # every symbol include/cute_mma_b200.h declares
 SYMBOLS = (
     "b200_oft_tn_f16", "b200_oft_tn_f16_host", "b200_oft_tn_f16_static", "b200_gemm_tn_f16", "b200_gemm_nt_f16", "b200_gemm_tn_tf32",
-    "b200_gemm_nt_tf32", "b200_gemm", "b200_shard_range", "b200_tile_coord", "b200_device_status", "b200_wait_profile", "b200_kernel_info",
+    "b200_gemm_nt_tf32", "b200_gemm", "b200_shard_range", "b200_tile_coord", "b200_device_status", "b200_selftest_wait_timeout", "b200_wait_profile", "b200_kernel_info",
     "b200_last_error", "b200_shutdown",
 )
 
@@ -62,6 +62,7 @@ def load_library(path: str | None = None):
     lib.b200_shard_range.argtypes = [i, i, i, i, ctypes.POINTER(i), ctypes.POINTER(i)]
     lib.b200_tile_coord.argtypes = [ctypes.c_uint, ctypes.c_uint, ctypes.c_uint, ctypes.POINTER(ctypes.c_uint), ctypes.POINTER(ctypes.c_uint)]
     lib.b200_device_status.argtypes = [ctypes.POINTER(ctypes.c_int)]
+    lib.b200_selftest_wait_timeout.argtypes = [ctypes.c_uint, ctypes.POINTER(ctypes.c_int)]
     lib.b200_wait_profile.argtypes = [ctypes.POINTER(ctypes.c_ulonglong), i]
     lib.b200_kernel_info.restype = ctypes.c_char_p
     lib.b200_last_error.restype = ctypes.c_char_p
@@ -162,6 +163,14 @@ def device_status(lib=None, raise_on_error: bool = True):
     rc = lib.b200_device_status(out)
     if rc != OK and raise_on_error:
         raise Error(rc, lib.b200_last_error().decode())
+    return list(out)
+
+
+def selftest_wait_timeout(limit_us: int = 1000, lib=None):
+    """Runs the bounded-wait self-test; returns the status record the timed-out wait wrote."""
+    lib = lib or load_library()
+    out = (ctypes.c_int * 4)()
+    _check(lib, lib.b200_selftest_wait_timeout(limit_us, out))
     return list(out)
 
 

@@ -101,6 +101,13 @@ int b200_tile_coord(unsigned tiles_m, unsigned tiles_n, unsigned idx, unsigned* 
  * Clears the record.  Returns B200_EDEVICE when out[0] != 0. */
 int b200_device_status(int out[4]);
 
+/* Exercises the kernels' failure path without any fault: a one-thread kernel waits, with a limit of
+ * limit_us microseconds (1..100000), on a barrier nothing arrives on; the wait gives up, records
+ * {1, CTA 0, site 99, parity 0} and the kernel returns.  Returns B200_OK when exactly that was
+ * observed (out receives the record) and leaves the status record cleared.  The reference has no
+ * failure detection (errors surface as cudaErrors at the next synchronisation). */
+int b200_selftest_wait_timeout(unsigned limit_us, int out[4]);
+
 /* In-kernel stage timers (the reference has no tracing beyond cudaEvent timing, cute_oft_pc.cu:372-377).
  * A library built with -DB200_PROFILE_WAITS adds, per wait site of the kernels' mbarrier protocol,
  * the cycles spent waiting (out[site]) and the number of waits (out[64 + site]); this call

@@ -58,3 +58,26 @@ def test_sweep_checkpoints_and_resumes(tmp_path):
     good2 = _fake_exe(tmp_path / "good2", f'touch {marker}; echo "[1.00]"\n')
     out2 = asyncio.run(runner_oft.sweep({"a": good2, "c": good}, ["-t", "1"], 1, results, 30.0))
     assert not marker.exists() and out2["a"]["value"] == 123.45 and out2["c"]["value"] == 123.45
+
+
+def test_gemm_generator_writes_all_specialisations(tmp_path):
+    from cute_mma_b200.autotune import gen_autotune_config as gg
+
+    counts = gg.generate(str(tmp_path))
+    assert set(counts) == set(gg.KEYS) and all(n >= 20 for n in counts.values())
+    text = (tmp_path / "float_float" / "NT" / "config0" / "gemm_config.hpp").read_text()
+    assert text.count("template <> struct Params<") == 4 and "MMA_N, MMA_T" in text
+    assert (tmp_path / "float_float" / "NT" / "config0" / "oft_config.hpp").exists()
+    assert (tmp_path / "config_csvs" / "half_half_TN_param.csv").read_text().startswith("id,ctas,bN,bP,smem")
+    for c in gg.candidates():
+        assert gg.smem_bytes(**c) <= gg.SMEM_LIMIT
+    assert {"ctas": 2, "bN": 256, "bP": 6} in list(gg.candidates())       # the shipped default is in the space
+    assert {"ctas": 1, "bN": 256, "bP": 5} not in list(gg.candidates())   # 5 x 48 KB does not fit
+
+
+def test_gemm_stdout_contract_is_parsed_like_the_reference():
+    from cute_mma_b200.autotune import runner
+
+    assert runner.get_flops("CUTE_GEMM:     [1234567.8]GFlop/s  (0.7440)ms") == 1234567.8
+    assert runner.get_flops("CUTE_GEMM:     [ 912.5]GFlop/s  (0.1000)ms") == 912.5
+    assert math.isnan(runner.get_flops("cute_mma_b200 call failed with status 3"))

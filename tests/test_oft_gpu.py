@@ -218,3 +218,15 @@ def test_oft_large_slab_sampled(lib, cuda):
     """One GPU's slab of the N-sharded large configuration at 8 GPUs (N = 28672/8 = 3584), K = 8192,
     b = 128, QR blocks; M reduced to 8192 rows to keep the run short (rows are independent)."""
     _sampled_parity(lib, cuda, 8192, 3584, 8192, 128, "qr", 0.02, 12, seed=5)
+
+
+def test_bounded_wait_reports_and_recovers(lib, cuda):
+    """A wait that runs out is reported through the status record and leaves the context usable
+    (no trap, no fault): the self-test waits 2 ms on a barrier nothing sets."""
+    rec = ops.selftest_wait_timeout(2000, lib=lib)
+    assert rec[0] == 1 and rec[2] == 99
+    assert ops.device_status(lib)[0] == 0          # record cleared
+    m, n, k, b = 128, 256, 128, 64                 # and the next real launch works
+    A, R, B = make_oft_case(m, n, k, b, seed=31)
+    got = run_oft(lib, cuda, A, R, B, m, n, k, b)
+    assert oft_ok(got, oracle_full(A, R, B, m, n, k, b))[0] == 0
