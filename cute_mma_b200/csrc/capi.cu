@@ -50,13 +50,14 @@ constexpr int kMaxDevices = 64;
 struct DeviceState {
   bool ready = false;
   int sm_count = 0;
+  long long l2_bytes = 126ll << 20;
   int* status = nullptr;            // 4 ints, zeroed; kernels record a timed-out wait here
   void* stage[4] = {nullptr, nullptr, nullptr, nullptr};  // staging of the host-buffer entry point
   size_t stage_bytes[4] = {0, 0, 0, 0};
   cudaStream_t host_stream = nullptr;
 };
 // workspace layout: kStatusInts ints of status, then 2 * kWaitSites 64-bit wait-profile counters
-constexpr int kProfileWords = 2 * kWaitSites + kTraceUnits * kTraceEvents;  // counters, then the unit trace
+constexpr int kProfileWords = 2 * kWaitSites + kTraceUnits * kTraceEvents + kSkewCtas * kSkewTiles;  // counters, unit trace, tile-end times
 constexpr size_t kWorkspaceBytes = kStatusInts * sizeof(int) + kProfileWords * sizeof(unsigned long long);
 DeviceState g_dev[kMaxDevices];
 std::mutex g_mu;        // guards g_dev initialisation
@@ -79,6 +80,7 @@ int device_state(DeviceState** out) {
     if (prop.major != 10)
       return fail(B200_EUNSUPPORTED, "device %d is sm_%d%d; this library contains sm_100a code only", dev, prop.major, prop.minor);
     st.sm_count = prop.multiProcessorCount;
+    st.l2_bytes = prop.l2CacheSize > 0 ? prop.l2CacheSize : (126ll << 20);
     CUDA_TRY(cudaMalloc(&st.status, kWorkspaceBytes));
     CUDA_TRY(cudaMemset(st.status, 0, kWorkspaceBytes));
     if (!g_encode) {
@@ -218,7 +220,16 @@ int launch_oft(int m, int n, int k, int group_size, const void* A, int ldA, cons
     auto pick = [](char c) { return c == 'f' ? kL2EvictFirst : (c == 'l' ? kL2EvictLast : kL2EvictNormal); };
     if (e[0] && e[1]) { hint_a = pick(e[0]); hint_b = pick(e[1]); }
   }
-  OftArgs args{m, n, k, group_size, static_cast<__half*>(C), ldC, st->status, raster, hint_a, hint_b};
+  // Cross-CTA phase lock of the tile rounds (pair kernel).  Without it the CTAs drift apart by up to a tile
+  // time (~80 us measured), the panels of A and B that concurrently running tiles share fall out of L2
+  // before the second reader arrives, and DRAM traffic grows to 17x the algorithmic bytes at M 65536,
+  // N 28672, K 8192.  Measured there: 5 % more cycles, 20 % less time (the saved DRAM power buys clock
+  // under the power cap).  It costs 5-9 % where B fits L2 a few times over, so it is on only when B
+  // exceeds three times the L2 size.  B200_TILE_SYNC=0/1 overrides.
+  int tile_sync = (kOftPair && static_cast<long long>(n) * k * 2 > 3ll * st->l2_bytes) ? 1 : 0;
+  if (const char* e = std::getenv("B200_TILE_SYNC")) tile_sync = kOftPair ? std::atoi(e) : 0;
+  if (tile_sync) CUDA_TRY(cudaMemsetAsync(st->status + 4, 0, 4 * sizeof(int), stream));  // the round counters start at zero
+  OftArgs args{m, n, k, group_size, static_cast<__half*>(C), ldC, st->status, raster, hint_a, hint_b, tile_sync};
   const long long tiles = static_cast<long long>((m + kRowsPerCta * T::kBM - 1) / (kRowsPerCta * T::kBM)) * ((n + T::kBN - 1) / T::kBN);
   if constexpr (kOftPair) {
     auto kernel = oft2_kernel<T>;
@@ -348,7 +359,7 @@ std::mutex g_static_mu;
 // Device scratch one fused-OFT launch needs beyond its inputs and outputs: the status record of the
 // bounded waits followed by the wait-profile words (the same layout the allocated workspace has).
 // reconn_sz = 8 adds the expanded copy of R (see expand_r8_kernel) at kStaticRxOffset.
-constexpr size_t kStaticRxOffset = 4096;
+constexpr size_t kStaticRxOffset = 36 * 1024;
 static_assert(kWorkspaceBytes <= kStaticRxOffset, "status record and profile words must fit below the expanded R");
 size_t oft_scratch_bytes(int n_groups, int k, int reconn_sz) {
   return reconn_sz == 8 ? kStaticRxOffset + r8_bytes(n_groups, k) : kWorkspaceBytes;

@@ -113,7 +113,16 @@ oft2_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
     if (lane == 0) {
       uint32_t it = 0;
       bool ok = true;
+      unsigned done_rounds = 0, sync_target = 0;
       for (unsigned tile = pair; ok && tile < num_tiles; tile += num_pairs) {
+        if (args.tile_sync && done_rounds > 0) {
+          if (!(ok = tile_round_sync(args.status + 4 + rank, sync_target, ctx, 12))) break;
+        }
+        {  // every pair that had a tile in this round takes part in the next rendezvous
+          const unsigned first = tile - pair, left = num_tiles - first;
+          sync_target += left < num_pairs ? left : num_pairs;
+          ++done_rounds;
+        }
         unsigned tm, tn;
         tile_coord_r(args.raster, tiles_m, tiles_n, tile, tm, tn);
         const int m0 = tm * 2 * T::kBM + rank * T::kBM;
@@ -127,6 +136,8 @@ oft2_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
           tma_load_2d_pair_hint(a_dst + T::kABytes, &tmap_r, full1 + 8 * s, st * T::kBK, r_row0, kL2EvictLast);
         }
       }
+      // leaving after its last round, this thread still counts for the rendezvous the others make
+      if (ok && args.tile_sync && done_rounds > 0) atomicAdd(args.status + 4 + rank, 1);
     }
     __syncwarp();
   } else if (warp == 1) {
@@ -135,7 +146,16 @@ oft2_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
     if (lane == 0) {
       uint32_t it = 0;
       bool ok = true;
+      unsigned done_rounds = 0, sync_target = 0;
       for (unsigned tile = pair; ok && tile < num_tiles; tile += num_pairs) {
+        if (args.tile_sync && done_rounds > 0) {
+          if (!(ok = tile_round_sync(args.status + 6 + rank, sync_target, ctx, 13))) break;
+        }
+        {
+          const unsigned first = tile - pair, left = num_tiles - first;
+          sync_target += left < num_pairs ? left : num_pairs;
+          ++done_rounds;
+        }
         unsigned tm, tn;
         tile_coord_r(args.raster, tiles_m, tiles_n, tile, tm, tn);
         const int n0 = tn * T::kBN + rank * T::kBNHalf;
@@ -145,7 +165,7 @@ oft2_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
           if (rank == 0) mbar_expect_tx(full2 + 8 * s, 2 * T::kS2Bytes);
           tma_load_2d_pair_hint(ring2 + s * T::kS2Bytes, &tmap_b, full2 + 8 * s, st * T::kBK, n0, args.hint_b);
         }
-      }
+      }      if (ok && args.tile_sync && done_rounds > 0) atomicAdd(args.status + 6 + rank, 1);
     }
     __syncwarp();
   } else if (warp == 2) {
@@ -313,6 +333,7 @@ oft2_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
       }
       tc_fence_before();
       mbar_arrive_cluster(mapa_shared(acc_empty, 0));
+      if (threadIdx.x == 256) skew_stamp(ctx, tcount);
       if (row < args.m) {
 #pragma unroll
         for (int c = 0; c < T::kBN / 32; ++c) {

@@ -82,9 +82,10 @@ struct WaitCtx {
 // In-kernel stage timers: when the library is built with -DB200_PROFILE_WAITS every wait that
 // has to spin adds its cycles to a per-site counter (and site+64 counts those waits), read back by b200_wait_profile.
 constexpr int kWaitSites = 64;
-constexpr int kStatusInts = 4;
+constexpr int kStatusInts = 8;   // 4 status words, then 4 tile-round counters of the cross-CTA phase lock
 constexpr int kTraceUnits = 32, kTraceEvents = 8;  // profiling build: clock64 stamps of CTA 0, units [kTraceFirst, +32)
 constexpr int kTraceFirst = 70;
+constexpr int kSkewCtas = 160, kSkewTiles = 24;  // profiling build: globaltimer at the end of each CTA's first tiles
 
 __device__ __noinline__ void report_timeout(const WaitCtx& ctx, int site, uint32_t parity) {
   *ctx.abort_flag = 1;
@@ -137,6 +138,14 @@ __device__ __forceinline__ void trace_stamp(const WaitCtx& ctx, unsigned unit, i
   }
 #endif
 }
+__device__ __forceinline__ void skew_stamp(const WaitCtx& ctx, unsigned tile_round) {
+#ifdef B200_PROFILE_WAITS
+  if (blockIdx.x < kSkewCtas && tile_round < kSkewTiles) {
+    unsigned long long* sk = reinterpret_cast<unsigned long long*>(ctx.status + kStatusInts) + 2 * kWaitSites + kTraceUnits * kTraceEvents;
+    sk[blockIdx.x * kSkewTiles + tile_round] = globaltimer_ns();
+  }
+#endif
+}
 __device__ __forceinline__ void wait_profile_flush(const WaitCtx& ctx) {
 #ifdef B200_PROFILE_WAITS
   unsigned long long* prof = reinterpret_cast<unsigned long long*>(ctx.status + kStatusInts);
@@ -146,6 +155,28 @@ __device__ __forceinline__ void wait_profile_flush(const WaitCtx& ctx) {
       atomicAdd(prof + kWaitSites + ctx.prof_site[i], static_cast<unsigned long long>(ctx.prof_count[i]));
     }
 #endif
+}
+
+// Cross-CTA phase lock for persistent kernels whose CTAs all are co-resident (grid <= SM count): the
+// calling thread announces that it finished tile round `round` and waits, bounded, until `target` threads
+// of its kind have done so.  Keeps concurrently running tiles within a few microseconds of each other so
+// that the operand panels they share are still in L2 when the second reader arrives.
+__device__ __forceinline__ bool tile_round_sync(int* counter, unsigned target, const WaitCtx& ctx, int site) {
+  __threadfence();
+  atomicAdd(counter, 1);
+  const unsigned long long t0 = globaltimer_ns();
+  int it = 0;
+  while (static_cast<unsigned>(*reinterpret_cast<volatile int*>(counter)) < target) {
+    if ((++it & 15) == 0) {
+      if (*ctx.abort_flag) return false;
+      if (globaltimer_ns() - t0 > ctx.limit_ns) {
+        report_timeout(ctx, site, target);
+        return false;
+      }
+    }
+    __nanosleep(64);
+  }
+  return true;
 }
 
 // Whole-warp form for roles whose next instruction is warp-collective (tcgen05.ld / st / wait):

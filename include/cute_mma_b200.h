@@ -111,8 +111,9 @@ int b200_selftest_wait_timeout(unsigned limit_us, int out[4]);
 /* In-kernel stage timers (the reference has no tracing beyond cudaEvent timing, cute_oft_pc.cu:372-377).
  * A library built with -DB200_PROFILE_WAITS adds, per wait site of the kernels' mbarrier protocol,
  * the cycles spent waiting (out[site]) and the number of waits (out[64 + site]); this call
- * synchronises the device, copies up to n counters and clears them (n <= 128; up to 384 also
- * returns a 32-unit x 8-event clock trace of CTA 0 used when tuning the OFT hand-off).  Ordinary builds return
+ * synchronises the device, copies up to n counters and clears them (n <= 128; larger n also
+ * returns a 32-unit x 8-event clock trace of CTA 0 and tile-end times of the first CTAs, used when
+ * tuning the OFT hand-off and the tile order).  Ordinary builds return
  * B200_EUNSUPPORTED. */
 int b200_wait_profile(unsigned long long* out, int n);
 

@@ -53,7 +53,7 @@ def test_static_scratch_entry_point_validates_like_the_other(lib, cuda):
 def test_static_scratch_entry_point_small_blocks_and_its_size_limit(lib, cuda):
     """8 x 8 blocks need an expanded copy of R as scratch: it fits the library's array for a small K and
     is refused, with both sizes in the message, when it does not."""
-    want, got = _both(lib, cuda, 256, 512, 512, 8, seed=23)   # 16 rows x 512 columns of fp16 = 16 KB of scratch
+    want, got = _both(lib, cuda, 256, 512, 512, 8, seed=23)   # 16 rows x 512 columns of fp16 = 16 KB of scratch beside the record
     assert np.array_equal(want.view(np.uint16), got.view(np.uint16))
     import torch
 
