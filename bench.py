@@ -39,9 +39,10 @@ NOMINAL_FP16_TFLOPS = 2250.0  # vendor dense fp16 figure, context only
 # DRAM bytes of one launch of the dominant kernel, from the ncu capture summarised under profiles/
 # (dram__bytes_read.sum + dram__bytes_write.sum); None until a capture exists for the workload.
 NCU_TRAFFIC_BYTES = {
-    # per launch at N = 1, ncu one-pass counters on the full workload (read 85.7 GB + write 5.8 GB; 17x the
-    # algorithmic 5.3 GB: concurrently running tiles share their panels of X and W through L2 only partly)
-    "oft_large_m65536_k8192_n28672_b128": 91.55e9,
+    # per launch at N = 1, ncu one-pass counters on the full workload: read 29.2 GB + write 5.7 GB against
+    # 5.3 GB algorithmic (every wave of 74 tiles re-reads its panels of X and W once; it was 91.5 GB before
+    # the CTAs' tile rounds were phase-locked)
+    "oft_large_m65536_k8192_n28672_b128": 34.94e9,
     # ncu --set full capture of the same shape (read 363 MB + write 154 MB; algorithmic 303 MB)
     "oft_proj_m16384_k4096_n4096_b64": 517.2e6,
 }
