@@ -124,6 +124,24 @@ int raster_for(long long b_bytes, bool oft) {
   return (oft && b_bytes > (40ll << 20)) ? 8 : 0;
 }
 
+// 3-D map over an MN-major matrix [outer = K rows][inner = MN contiguous], inner a multiple of `chunk`:
+// dimensions (chunk, K, inner / chunk) with strides (ld, chunk) elements, boxes of chunk x box_k x
+// box_chunks.  One copy then brings box_chunks 128-byte column chunks, laid out chunk after chunk in
+// shared memory exactly as the per-chunk 2-D copies would.  Returns B200_EUNSUPPORTED if the driver
+// refuses the descriptor (the caller falls back to the 2-D map).
+int make_map_chunks(CUtensorMap* map, const void* base, int elem_bytes, long long inner, long long outer, long long ld,
+                    int chunk, int box_k, int box_chunks, bool atom32) {
+  if (inner % chunk != 0 || (reinterpret_cast<uintptr_t>(base) & 15) || (ld * elem_bytes) % 16 != 0 || ld < inner) return B200_EUNSUPPORTED;
+  cuuint64_t dims[3] = {static_cast<cuuint64_t>(chunk), static_cast<cuuint64_t>(outer), static_cast<cuuint64_t>(inner / chunk)};
+  cuuint64_t strides[2] = {static_cast<cuuint64_t>(ld) * elem_bytes, static_cast<cuuint64_t>(chunk) * elem_bytes};
+  cuuint32_t box[3] = {static_cast<cuuint32_t>(chunk), static_cast<cuuint32_t>(box_k), static_cast<cuuint32_t>(box_chunks)};
+  cuuint32_t estr[3] = {1, 1, 1};
+  const CUtensorMapDataType dt = elem_bytes == 2 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32;
+  CUresult r = g_encode(map, dt, 3, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                        atom32 ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B : CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? B200_OK : B200_EUNSUPPORTED;
+}
+
 template <class Kernel>
 int opt_in_smem(Kernel kernel, int bytes) {
   // The reference never raises the dynamic shared-memory limit and so cannot launch any tile
@@ -163,14 +181,19 @@ int launch_gemm(int m, int n, int k, const void* A, int ldA, const void* B, int 
   if (int rc = device_state(&st)) return rc;
   constexpr int kBoxN = kPair ? T2::kBNHalf : T1::kBN;
   CUtensorMap ma, mb;
+  int a3d = 0, b3d = 0;
   if (!kNT) {  // K contiguous
     if (int rc = make_map(&ma, A, sizeof(TIn), k, m, ldA, T1::kBK, T1::kBM, "A")) return rc;
     if (int rc = make_map(&mb, B, sizeof(TIn), k, n, ldB, T1::kBK, kBoxN, "B")) return rc;
-  } else {     // M / N contiguous, one 128-byte column chunk per copy
-    if (int rc = make_map(&ma, A, sizeof(TIn), m, k, ldA, T1::kChunk, T1::kBK, "A", T1::kA32Atom)) return rc;
-    if (int rc = make_map(&mb, B, sizeof(TIn), n, k, ldB, T1::kChunk, T1::kBK, "B", T1::kB32Atom)) return rc;
+  } else {     // M / N contiguous: all 128-byte column chunks of a tile with one 3-D copy when the extent is
+               // a whole number of chunks (B200_NO_3D_MAPS=1 keeps the per-chunk 2-D copies), else one copy per chunk
+    const bool try3d = std::getenv("B200_NO_3D_MAPS") == nullptr;
+    if (try3d && make_map_chunks(&ma, A, sizeof(TIn), m, k, ldA, T1::kChunk, T1::kBK, T1::kBM / T1::kChunk, T1::kA32Atom) == B200_OK) a3d = 1;
+    else if (int rc = make_map(&ma, A, sizeof(TIn), m, k, ldA, T1::kChunk, T1::kBK, "A", T1::kA32Atom)) return rc;
+    if (try3d && make_map_chunks(&mb, B, sizeof(TIn), n, k, ldB, T1::kChunk, T1::kBK, kBoxN / T1::kChunk, T1::kB32Atom) == B200_OK) b3d = 1;
+    else if (int rc = make_map(&mb, B, sizeof(TIn), n, k, ldB, T1::kChunk, T1::kBK, "B", T1::kB32Atom)) return rc;
   }
-  GemmArgs args{m, n, k, C, ldC, st->status, raster_for(static_cast<long long>(n) * k * sizeof(TIn), false)};
+  GemmArgs args{m, n, k, C, ldC, st->status, raster_for(static_cast<long long>(n) * k * sizeof(TIn), false), a3d, b3d};
   if constexpr (kPair) {
     auto kernel = gemm2_kernel<T2>;
     if (int rc = opt_in_smem(kernel, T2::kSmemBytes)) return rc;

@@ -47,6 +47,7 @@ struct GemmArgs {
   long long ldC;
   int* status;
   int raster;  // 0: z-curve tile order; g > 0: bands of g tile rows
+  int a3d, b3d;  // MN-major operand described by a 3-D map (chunk, K, chunk index): one copy per tile instead of one per chunk
 };
 
 template <class T>
@@ -110,16 +111,24 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
           if constexpr (!T::kAMn) {
             tma_load_2d(a_dst, &tmap_a, full_bar(s), k0, m0);
           } else {
+            if (args.a3d) {
+              tma_load_3d(a_dst, &tmap_a, full_bar(s), 0, k0, m0 / T::kChunk);
+            } else {
 #pragma unroll
-            for (int c = 0; c < T::kBM / T::kChunk; ++c)
-              tma_load_2d(a_dst + c * (T::kBK * 128), &tmap_a, full_bar(s), m0 + c * T::kChunk, k0);
+              for (int c = 0; c < T::kBM / T::kChunk; ++c)
+                tma_load_2d(a_dst + c * (T::kBK * 128), &tmap_a, full_bar(s), m0 + c * T::kChunk, k0);
+            }
           }
           if constexpr (!T::kBMn) {
             tma_load_2d(b_dst, &tmap_b, full_bar(s), k0, n0);
           } else {
+            if (args.b3d) {
+              tma_load_3d(b_dst, &tmap_b, full_bar(s), 0, k0, n0 / T::kChunk);
+            } else {
 #pragma unroll
-            for (int c = 0; c < T::kBN / T::kChunk; ++c)
-              tma_load_2d(b_dst + c * (T::kBK * 128), &tmap_b, full_bar(s), n0 + c * T::kChunk, k0);
+              for (int c = 0; c < T::kBN / T::kChunk; ++c)
+                tma_load_2d(b_dst + c * (T::kBK * 128), &tmap_b, full_bar(s), n0 + c * T::kChunk, k0);
+            }
           }
         }
       }
