@@ -4,7 +4,8 @@
 // Base/Total TFLOPS lines and the parsed line
 //   TFLOPS/s (AR_W): [%.2f], (AR_W_sparse): %.2f, (A_RW): %.2f, Time: %.3f ms
 // group_size / reconn_sz default to the compile-time CurrKernelParams and can be overridden with
-// --group_size / --reconn_sz (0 = all of N in one group).  --correctness compares against a naive
+// --group_size / --reconn_sz (0 = all of N in one group); --mode A_RW times the other algebraic order
+// (weight transform + plain GEMM, what the reference's --cublas_mode A_RW runs through cuBLAS).  --correctness compares against a naive
 // CUDA restatement of the same arithmetic (one thread per output element) with the reference's
 // relative-error count (check_result, cute_oft_pc.cu:31-77).
 #include <algorithm>
@@ -49,6 +50,7 @@ int main(int argc, char** argv) {
   f.add({"--correctness"}, "0", true);
   f.add({"--group_size"}, std::to_string(CurrKernelParams::group_size));
   f.add({"--reconn_sz"}, std::to_string(CurrKernelParams::reconn_sz));
+  f.add({"--mode"}, "AR_W");  // AR_W: the fused kernel; A_RW: weight transform + plain GEMM (the reference's --cublas_mode names)
   try { f.parse(argc, argv); } catch (const std::exception& e) { fprintf(stderr, "%s\n", e.what()); return 1; }
   const int m = f.geti("--m"), n = f.geti("--n"), k = f.geti("--k");
   int group_size = f.geti("--group_size");
@@ -79,8 +81,10 @@ int main(int argc, char** argv) {
     GEMM_CHECK_CUDA(cudaMemcpy(dA, hA.data(), hA.size() * 2, cudaMemcpyHostToDevice));
     GEMM_CHECK_CUDA(cudaMemcpy(dB, hB.data(), hB.size() * 2, cudaMemcpyHostToDevice));
     GEMM_CHECK_CUDA(cudaMemcpy(dR, hR.data(), hR.size() * 2, cudaMemcpyHostToDevice));
+    const bool a_rw = f.gets("--mode") == "A_RW";
     auto run = [&]() {
-      B200_CHECK(b200_oft_tn_f16(m, n, k, group_size, reconn_sz, dA, k, dB, k, dR, k, dC, n, nullptr));
+      if (a_rw) B200_CHECK(b200_oft_tn_f16_a_rw(m, n, k, group_size, reconn_sz, dA, k, dB, k, dR, k, dC, n, nullptr));
+      else B200_CHECK(b200_oft_tn_f16(m, n, k, group_size, reconn_sz, dA, k, dB, k, dR, k, dC, n, nullptr));
     };
     if (f.getb("--correctness")) {
       run();

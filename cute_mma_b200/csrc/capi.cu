@@ -193,7 +193,10 @@ int launch_gemm(int m, int n, int k, const void* A, int ldA, const void* B, int 
     if (try3d && make_map_chunks(&mb, B, sizeof(TIn), n, k, ldB, T1::kChunk, T1::kBK, kBoxN / T1::kChunk, T1::kB32Atom) == B200_OK) b3d = 1;
     else if (int rc = make_map(&mb, B, sizeof(TIn), n, k, ldB, T1::kChunk, T1::kBK, "B", T1::kB32Atom)) return rc;
   }
-  GemmArgs args{m, n, k, C, ldC, st->status, raster_for(static_cast<long long>(n) * k * sizeof(TIn), false), a3d, b3d};
+  int tile_sync = 0;  // cross-CTA phase lock of the tile rounds (see launch_oft); experiments only for the plain GEMM
+  if (const char* e = std::getenv("B200_GEMM_TILE_SYNC")) tile_sync = kPair ? std::atoi(e) : 0;
+  if (tile_sync) CUDA_TRY(cudaMemsetAsync(st->status + 4, 0, 4 * sizeof(int), stream));
+  GemmArgs args{m, n, k, C, ldC, st->status, raster_for(static_cast<long long>(n) * k * sizeof(TIn), false), tile_sync, a3d, b3d};
   if constexpr (kPair) {
     auto kernel = gemm2_kernel<T2>;
     if (int rc = opt_in_smem(kernel, T2::kSmemBytes)) return rc;
@@ -268,6 +271,50 @@ int launch_oft(int m, int n, int k, int group_size, const void* A, int ldA, cons
   CUDA_TRY(cudaGetLastError());
   return B200_OK;
   }
+}
+
+// ---- A_RW algebra: pre-transformed weight ----------------------------------------------------------------
+// Y = X . (R . W): the rotation is folded into the weight once (cublas_oft.hpp:20-43 does this with batched
+// cuBLAS calls), after which every product is a plain GEMM.  In the stored layouts
+//   Bt[g*gs + j][kb*b + p] = half( sum_q R[g*b + q][kb*b + p] * B[g*gs + j][kb*b + q] )      fp32 accumulate
+// One CTA transforms 64 rows of one N-group against one b x b block; 2*N*K*b FLOPs in all, on the CUDA cores
+// (it runs once per weight update, not once per product).
+__global__ void __launch_bounds__(256) transform_weight_kernel(const __half* __restrict__ B, long long ldB, const __half* __restrict__ R,
+                                                               long long ldR, __half* __restrict__ Bt, long long ldBt, int group_size, int b,
+                                                               int chunks_per_group) {
+  extern __shared__ __half tw_smem[];
+  __half* sR = tw_smem;            // [b][b]   sR[q][p]
+  __half* sB = tw_smem + b * b;    // [64][b]  sB[r][q]
+  const int kb = blockIdx.x, g = blockIdx.y / chunks_per_group, c = blockIdx.y % chunks_per_group;
+  const int rows = min(64, group_size - c * 64);
+  const long long row0 = static_cast<long long>(g) * group_size + c * 64, col0 = static_cast<long long>(kb) * b;
+  for (int i = threadIdx.x; i < b * b; i += blockDim.x) sR[i] = R[(static_cast<long long>(g) * b + i / b) * ldR + col0 + i % b];
+  for (int i = threadIdx.x; i < rows * b; i += blockDim.x) sB[i] = B[(row0 + i / b) * ldB + col0 + i % b];
+  __syncthreads();
+  for (int i = threadIdx.x; i < rows * b; i += blockDim.x) {
+    const int r = i / b, p = i % b;
+    float acc = 0.f;
+    for (int q = 0; q < b; ++q) acc += __half2float(sB[r * b + q]) * __half2float(sR[q * b + p]);
+    Bt[(row0 + r) * ldBt + col0 + p] = __float2half_rn(acc);
+  }
+}
+
+int transform_weight(int n, int k, int group_size, int b, const void* B, int ldB, const void* R, int ldR, void* Bt, int ldBt, cudaStream_t stream) {
+  if (n < 0 || k < 0 || b <= 0 || group_size <= 0) return fail(B200_EINVAL, "bad transform_weight sizes (n=%d k=%d group_size=%d reconn_sz=%d)", n, k, group_size, b);
+  if (b > 128) return fail(B200_EUNSUPPORTED, "reconn_sz=%d: the weight transform handles block edges up to 128", b);
+  if (k % b != 0) return fail(B200_EINVAL, "k=%d is not a multiple of reconn_sz=%d", k, b);
+  if (n % group_size != 0) return fail(B200_EINVAL, "n=%d is not a multiple of group_size=%d", n, group_size);
+  if (ldB < k || ldR < k || ldBt < k) return fail(B200_EINVAL, "leading dimension smaller than k=%d", k);
+  if (n == 0 || k == 0) return B200_OK;
+  if (!B || !R || !Bt) return fail(B200_EINVAL, "B, R or the output is null");
+  const int chunks = (group_size + 63) / 64, n_groups = n / group_size;
+  const size_t smem = (static_cast<size_t>(b) * b + 64 * b) * sizeof(__half);
+  CUDA_TRY(cudaFuncSetAttribute(transform_weight_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
+  if (static_cast<long long>(n_groups) * chunks > 65535) return fail(B200_EUNSUPPORTED, "too many row chunks for one launch");
+  transform_weight_kernel<<<dim3(k / b, n_groups * chunks), 256, smem, stream>>>(static_cast<const __half*>(B), ldB, static_cast<const __half*>(R), ldR,
+                                                                             static_cast<__half*>(Bt), ldBt, group_size, b, chunks);
+  CUDA_TRY(cudaGetLastError());
+  return B200_OK;
 }
 
 // ---- self-test of the bounded-wait path ---------------------------------------------------------------
@@ -517,6 +564,35 @@ int b200_device_status(int out[4]) {
     return fail(B200_EDEVICE, "a bounded wait ran out in CTA %d at wait site %d (parity %d)", host[1], host[2], host[3]);
   }
   return B200_OK;
+}
+
+int b200_transform_weight_f16(int n, int k, int group_size, int reconn_sz, const void* B, int ldB, const void* R, int ldR,
+                              void* Bt, int ldBt, void* stream) {
+  g_err.clear();
+  return transform_weight(n, k, group_size, reconn_sz, B, ldB, R, ldR, Bt, ldBt, static_cast<cudaStream_t>(stream));
+}
+
+int b200_oft_tn_f16_a_rw(int m, int n, int k, int group_size, int reconn_sz, const void* A, int ldA, const void* B, int ldB,
+                         const void* R, int ldR, void* C, int ldC, void* stream_v) {
+  g_err.clear();
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
+  if (int rc = common_dims(m, n, k, A, B, C)) return rc;
+  if (ldC < n) return fail(B200_EINVAL, "ldC=%d smaller than n=%d (C is row-major)", ldC, n);
+  if (m == 0 || n == 0) return B200_OK;
+  if (k == 0) {
+    CUDA_TRY(cudaMemset2DAsync(C, static_cast<size_t>(ldC) * 2, 0, static_cast<size_t>(n) * 2, m, stream));
+    return B200_OK;
+  }
+  const int ldt = (k + 7) & ~7;
+  void* bt = nullptr;
+  CUDA_TRY(cudaMallocAsync(&bt, static_cast<size_t>(n) * ldt * 2, stream));
+  int rc = transform_weight(n, k, group_size, reconn_sz, B, ldB, R, ldR, bt, ldt, stream);
+  // row-major C[m][n] is the column-major (n x m, ld = ldC) result of  Bt . A^T:  gemm_tn with the operands swapped
+  if (rc == B200_OK) rc = b200_gemm_tn_f16(n, m, k, bt, ldt, A, ldA, C, ldC, stream);
+  const std::string keep = g_err;
+  cudaFreeAsync(bt, stream);
+  g_err = keep;
+  return rc;
 }
 
 int b200_selftest_wait_timeout(unsigned limit_us, int out[4]) {

@@ -97,7 +97,16 @@ gemm2_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__
     if (lane == 0) {
       uint32_t it = 0;
       bool ok = true;
+      unsigned done_rounds = 0, sync_target = 0;
       for (unsigned tile = pair; ok && tile < num_tiles; tile += num_pairs) {
+        if (args.tile_sync && done_rounds > 0) {
+          if (!(ok = tile_round_sync(args.status + 4 + rank, sync_target, ctx, 5))) break;
+        }
+        {
+          const unsigned first = tile - pair, left = num_tiles - first;
+          sync_target += left < num_pairs ? left : num_pairs;
+          ++done_rounds;
+        }
         unsigned tm, tn;
         tile_coord_r(args.raster, tiles_m, tiles_n, tile, tm, tn);
         const int m0 = tm * 2 * T::kBM + rank * T::kBM;      // this CTA's rows of A and C
@@ -132,6 +141,7 @@ gemm2_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__
           }
         }
       }
+      if (ok && args.tile_sync && done_rounds > 0) atomicAdd(args.status + 4 + rank, 1);
     }
     __syncwarp();
   } else if (warp == 1) {

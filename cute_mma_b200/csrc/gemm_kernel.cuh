@@ -47,6 +47,7 @@ struct GemmArgs {
   long long ldC;
   int* status;
   int raster;  // 0: z-curve tile order; g > 0: bands of g tile rows
+  int tile_sync;  // pair kernel: producers of all CTAs start each tile round together (status[4..5] are the counters)
   int a3d, b3d;  // MN-major operand described by a 3-D map (chunk, K, chunk index): one copy per tile instead of one per chunk
 };
 

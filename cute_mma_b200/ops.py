@@ -23,7 +23,7 @@ OK, EINVAL, EUNSUPPORTED, ECUDA, EDEVICE = 0, 1, 2, 3, 4
 
 # every symbol include/cute_mma_b200.h declares
 SYMBOLS = (
-    "b200_oft_tn_f16", "b200_oft_tn_f16_host", "b200_oft_tn_f16_static", "b200_gemm_tn_f16", "b200_gemm_nt_f16", "b200_gemm_tn_tf32",
+    "b200_oft_tn_f16", "b200_oft_tn_f16_host", "b200_oft_tn_f16_static", "b200_transform_weight_f16", "b200_oft_tn_f16_a_rw", "b200_gemm_tn_f16", "b200_gemm_nt_f16", "b200_gemm_tn_tf32",
     "b200_gemm_nt_tf32", "b200_gemm", "b200_shard_range", "b200_tile_coord", "b200_device_status", "b200_selftest_wait_timeout", "b200_wait_profile", "b200_kernel_info",
     "b200_last_error", "b200_shutdown",
 )
@@ -55,6 +55,8 @@ def load_library(path: str | None = None):
     i, vp, c = ctypes.c_int, ctypes.c_void_p, ctypes.c_char
     lib.b200_oft_tn_f16.argtypes = [i, i, i, i, i, vp, i, vp, i, vp, i, vp, i, vp]
     lib.b200_oft_tn_f16_static.argtypes = [i, i, i, i, i, vp, i, vp, i, vp, i, vp, i, vp]
+    lib.b200_oft_tn_f16_a_rw.argtypes = [i, i, i, i, i, vp, i, vp, i, vp, i, vp, i, vp]
+    lib.b200_transform_weight_f16.argtypes = [i, i, i, i, vp, i, vp, i, vp, i, vp]
     lib.b200_oft_tn_f16_host.argtypes = [i, i, i, i, i, vp, i, vp, i, vp, i, vp, i]
     for name in ("b200_gemm_tn_f16", "b200_gemm_nt_f16", "b200_gemm_tn_tf32", "b200_gemm_nt_tf32"):
         getattr(lib, name).argtypes = [i, i, i, vp, i, vp, i, vp, i, vp]
@@ -111,6 +113,20 @@ def oft_tn_static(m, n, k, A, ldA, B, ldB, R, ldR, C, ldC, stream=None, *, group
     lib = lib or load_library()
     gs = n if group_size is None else group_size
     _check(lib, lib.b200_oft_tn_f16_static(m, n, k, gs, reconn_sz, _ptr(A), ldA, _ptr(B), ldB, _ptr(R), ldR, _ptr(C), ldC, _stream(stream)))
+
+
+def transform_weight(n, k, B, ldB, R, ldR, Bt, ldBt, stream=None, *, group_size=None, reconn_sz=8, lib=None) -> None:
+    """Bt = weight with the rotation folded in (the A_RW order): see b200_transform_weight_f16."""
+    lib = lib or load_library()
+    gs = n if group_size is None else group_size
+    _check(lib, lib.b200_transform_weight_f16(n, k, gs, reconn_sz, _ptr(B), ldB, _ptr(R), ldR, _ptr(Bt), ldBt, _stream(stream)))
+
+
+def oft_tn_a_rw(m, n, k, A, ldA, B, ldB, R, ldR, C, ldC, stream=None, *, group_size=None, reconn_sz=8, lib=None) -> None:
+    """Same product as oft_tn computed as X . (R . W): weight transform, then one plain GEMM."""
+    lib = lib or load_library()
+    gs = n if group_size is None else group_size
+    _check(lib, lib.b200_oft_tn_f16_a_rw(m, n, k, gs, reconn_sz, _ptr(A), ldA, _ptr(B), ldB, _ptr(R), ldR, _ptr(C), ldC, _stream(stream)))
 
 
 def oft_tn_host(m, n, k, A, ldA, B, ldB, R, ldR, C, ldC, *, group_size=None, reconn_sz=8, lib=None) -> None:

@@ -69,6 +69,19 @@ int b200_oft_tn_f16_static(int m, int n, int k, int group_size, int reconn_sz,
                            const void* A, int ldA, const void* B, int ldB, const void* R, int ldR,
                            void* C, int ldC, void* stream);
 
+/* The other algebraic order of the same product, Y = X . (R . W)  ("A_RW", cublas_oft.hpp:20-65).
+ * b200_transform_weight_f16 replaces transform_weight (cublas_oft.hpp:20-43): it folds the rotation into the
+ * weight,  Bt[g*gs+j][kb*b+p] = half(sum_q R[g*b+q][kb*b+p] * B[g*gs+j][kb*b+q])  (fp32 accumulate), Bt [n][k]
+ * ldBt, any reconn_sz <= 128 that divides k.  b200_oft_tn_f16_a_rw does the transform into stream-ordered
+ * scratch and then one plain GEMM (cublas_oft.hpp:58-65); callers that reuse a weight transform it once and
+ * call b200_gemm_tn_f16(n, m, k, Bt, ldBt, A, ldA, C, ldC) themselves.  The result differs from
+ * b200_oft_tn_f16 only by rounding (R.W is rounded to fp16 instead of X.R). */
+int b200_transform_weight_f16(int n, int k, int group_size, int reconn_sz, const void* B, int ldB,
+                              const void* R, int ldR, void* Bt, int ldBt, void* stream);
+int b200_oft_tn_f16_a_rw(int m, int n, int k, int group_size, int reconn_sz,
+                         const void* A, int ldA, const void* B, int ldB, const void* R, int ldR,
+                         void* C, int ldC, void* stream);
+
 /* Plain GEMM  C(i,j) = sum_l A(i,l) B(j,l),  C column-major: C(i,j) at C[i + j*ldC].
  * Replace gemm_tn / gemm_nt<TO,TR> (gemm_sm80_tc.cu:163-228 / 95-160).
  *   tn: A(i,l) at A[i*ldA + l], B(j,l) at B[j*ldB + l]   (both K-contiguous)

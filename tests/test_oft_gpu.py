@@ -230,3 +230,33 @@ def test_bounded_wait_reports_and_recovers(lib, cuda):
     A, R, B = make_oft_case(m, n, k, b, seed=31)
     got = run_oft(lib, cuda, A, R, B, m, n, k, b)
     assert oft_ok(got, oracle_full(A, R, B, m, n, k, b))[0] == 0
+
+
+@pytest.mark.parametrize("m,n,k,b,gs", [(384, 512, 512, 64, None), (200, 328, 192, 32, None), (256, 512, 256, 8, 256), (128, 256, 256, 128, None)])
+def test_a_rw_order_matches_oracle(lib, cuda, m, n, k, b, gs):
+    """Y = X.(R.W) (cublas_oft.hpp:58-65): the weight transform against its definition, and the product
+    against the oracle (same tolerance as the fused order; only the place of the fp16 rounding differs)."""
+    import torch
+
+    A, R, B = make_oft_case(m, n, k, b, gs, seed=41)
+    g_sz = n if gs is None else gs
+    dA, dB, dR = (torch.from_numpy(x).to(cuda) for x in (A, B, R))
+    dBt = torch.full((n, k), float("nan"), dtype=torch.float16, device=cuda)
+    ops.transform_weight(n, k, dB, k, dR, k, dBt, k, group_size=gs, reconn_sz=b, lib=lib)
+    torch.cuda.synchronize()
+    Rb = R.astype(np.float64).reshape(n // g_sz, b, k // b, b)            # [g][q][kb][p]
+    Bb = B.astype(np.float64).reshape(n // g_sz, g_sz, k // b, b)         # [g][j][kb][q]
+    want = np.einsum("gqkp,gjkq->gjkp", Rb, Bb).reshape(n, k)
+    got_t = dBt.cpu().numpy().astype(np.float64)
+    assert np.abs(got_t - want).max() <= 2e-3 * (np.abs(want).max() + 1.0)
+    dC = torch.full((m + 1, n), -7.0, dtype=torch.float16, device=cuda)
+    ops.oft_tn_a_rw(m, n, k, dA, k, dB, k, dR, k, dC, n, group_size=gs, reconn_sz=b, lib=lib)
+    assert ops.device_status(lib)[0] == 0
+    out = dC.cpu().numpy()
+    assert np.all(out[m] == np.float16(-7.0))
+    ref = oracle_full(A, R, B, m, n, k, b, gs)
+    truth = oracle.oft_f64(A, R, B, m, g_sz, n // g_sz, k, b, round_xr=False)
+    assert oft_ok(out[:m], ref, truth=truth)[0] == 0
+    # against exact arithmetic on the fp16-rounded transformed weight (this order's only intermediate rounding)
+    exact = A.astype(np.float64) @ want.astype(np.float16).astype(np.float64).T
+    assert truth_ok(out[:m], exact)[0] == 0
