@@ -55,6 +55,7 @@ struct DeviceState {
   void* stage[4] = {nullptr, nullptr, nullptr, nullptr};  // staging of the host-buffer entry point
   size_t stage_bytes[4] = {0, 0, 0, 0};
   cudaStream_t host_stream = nullptr;
+  cudaMemPool_t pool = nullptr;     // stream-ordered scratch (expanded R, transformed weight); keeps its memory between calls
 };
 // workspace layout: kStatusInts ints of status, then 2 * kWaitSites 64-bit wait-profile counters
 constexpr int kProfileWords = 2 * kWaitSites + kTraceUnits * kTraceEvents + kSkewCtas * kSkewTiles;  // counters, unit trace, tile-end times
@@ -83,6 +84,17 @@ int device_state(DeviceState** out) {
     st.l2_bytes = prop.l2CacheSize > 0 ? prop.l2CacheSize : (126ll << 20);
     CUDA_TRY(cudaMalloc(&st.status, kWorkspaceBytes));
     CUDA_TRY(cudaMemset(st.status, 0, kWorkspaceBytes));
+    // A pool of the library's own: the default pool hands unused memory back to the driver at every
+    // synchronisation (release threshold 0), so a caller that synchronises between calls would pay a fresh
+    // allocation on the next one (measured: 0.95 -> 1.6 ms per call at M = N = K = 8192, 8 x 8 blocks).
+    cudaMemPoolProps props{};
+    props.allocType = cudaMemAllocationTypePinned;
+    props.handleTypes = cudaMemHandleTypeNone;
+    props.location.type = cudaMemLocationTypeDevice;
+    props.location.id = dev;
+    CUDA_TRY(cudaMemPoolCreate(&st.pool, &props));
+    unsigned long long keep = ~0ull;
+    CUDA_TRY(cudaMemPoolSetAttribute(st.pool, cudaMemPoolAttrReleaseThreshold, &keep));
     if (!g_encode) {
       void* fn = nullptr;
       cudaDriverEntryPointQueryResult q;
@@ -217,26 +229,31 @@ int launch_gemm(int m, int n, int k, const void* A, int ldA, const void* B, int 
 // ---- fused OFT ---------------------------------------------------------------------------------------
 // ctas = 2 in oft_config.hpp selects the CTA-pair kernel (256 x bN tile per pair of SMs).
 constexpr bool kOftPair = CtasOf<CurrCompParams>::value == 2;
-template <int kB>
-using OftT = std::conditional_t<kOftPair, Oft2Traits<kB, CurrCompParams::bN, CurrCompParams::bP1, CurrCompParams::bP2>,
+// kGT > 1 (pair kernel only): group_size = bN / kGT, several N-groups (each with its own R) inside one tile.
+// The R tiles of all groups travel with every stage of A, so the first ring gets shallower as they grow.
+constexpr int oft_stages1(int b, int gt) {
+  const int r_bytes = gt * (b / 2) * 128;
+  return r_bytes <= 8 * 1024 ? CurrCompParams::bP1 : (r_bytes <= 16 * 1024 ? 3 : 2);
+}
+template <int kB, int kGT>
+using OftT = std::conditional_t<kOftPair, Oft2Traits<kB, CurrCompParams::bN, oft_stages1(kB, kGT), CurrCompParams::bP2, kGT>,
                                 OftTraits<kB, CurrCompParams::bN, CurrCompParams::bP1, CurrCompParams::bP2>>;
 
-template <int kB>
-int launch_oft(int m, int n, int k, int group_size, const void* A, int ldA, const void* B, int ldB, const void* R, int ldR,
-               void* C, int ldC, cudaStream_t stream, DeviceState* st) {
-  using T = OftT<kB>;
+template <int kB, int kGT>
+int launch_oft_gt(int m, int n, int k, int group_size, const void* A, int ldA, const void* B, int ldB, const void* R, int ldR,
+                  void* C, int ldC, cudaStream_t stream, DeviceState* st) {
+  using T = OftT<kB, kGT>;
   static_assert(CurrCompParams::bM == T::kBM && CurrCompParams::bK == T::kBK, "oft_config.hpp: bM must be 128 and bK 64");
   if constexpr (!T::kFits) {
-    return fail(B200_EUNSUPPORTED, "reconn_sz=%d needs %d bytes of shared memory with this tile configuration (limit 232448)", kB, T::kSmemBytes);
+    return fail(B200_EUNSUPPORTED, "reconn_sz=%d with group_size=%d needs %d bytes of shared memory with this tile configuration (limit 232448)", kB,
+                group_size, T::kSmemBytes);
   } else {
-  if (group_size != n && group_size % T::kBN != 0)
-    return fail(B200_EUNSUPPORTED, "group_size=%d must equal n or be a multiple of the N tile %d", group_size, T::kBN);
   const int n_groups = n / group_size;
   constexpr int kRowsPerCta = kOftPair ? 2 : 1;  // a pair splits the R tile and the B tile between its CTAs
   CUtensorMap ma, mr, mb;
   if (int rc = make_map(&ma, A, 2, k, m, ldA, T::kBK, T::kBM, "A")) return rc;
   if (int rc = make_map(&mr, R, 2, k, static_cast<long long>(n_groups) * kB, ldR, T::kBK, kB / kRowsPerCta, "R")) return rc;
-  if (int rc = make_map(&mb, B, 2, k, n, ldB, T::kBK, T::kBN / kRowsPerCta, "B")) return rc;
+  if (int rc = make_map(&mb, B, 2, k, n, ldB, T::kBK, T::kBN / kRowsPerCta / kGT, "B")) return rc;  // one copy per N-group of the tile
   const int raster = raster_for(static_cast<long long>(n) * k * 2, true);
   // L2 eviction priorities of the A and B loads.  Keeping the band's rows of A (evict_last) and streaming B
   // (evict_first) was measured at the large workload: 10 % less DRAM traffic but no gain in time, so both
@@ -270,6 +287,30 @@ int launch_oft(int m, int n, int k, int group_size, const void* A, int ldA, cons
   }
   CUDA_TRY(cudaGetLastError());
   return B200_OK;
+  }
+}
+
+// group_size == n or a multiple of the N tile: one R per tile.  group_size a divisor of the N tile (the
+// reference's bN % group_size == 0 case, cute_oft_coop_pc.cu:383): bN / group_size groups per tile, pair kernel.
+template <int kB>
+int launch_oft(int m, int n, int k, int group_size, const void* A, int ldA, const void* B, int ldB, const void* R, int ldR,
+               void* C, int ldC, cudaStream_t stream, DeviceState* st) {
+  constexpr int kBN = CurrCompParams::bN;
+  if (group_size == n || group_size % kBN == 0) return launch_oft_gt<kB, 1>(m, n, k, group_size, A, ldA, B, ldB, R, ldR, C, ldC, stream, st);
+  if constexpr (kOftPair && kB <= 64) {
+    if (kBN % group_size == 0) {
+      switch (kBN / group_size) {
+        case 2: return launch_oft_gt<kB, 2>(m, n, k, group_size, A, ldA, B, ldB, R, ldR, C, ldC, stream, st);
+        case 4: return launch_oft_gt<kB, 4>(m, n, k, group_size, A, ldA, B, ldB, R, ldR, C, ldC, stream, st);
+        case 8: return launch_oft_gt<kB, 8>(m, n, k, group_size, A, ldA, B, ldB, R, ldR, C, ldC, stream, st);
+        default: break;
+      }
+    }
+    return fail(B200_EUNSUPPORTED, "group_size=%d must equal n, be a multiple of the N tile %d, or be %d, %d or %d", group_size, kBN, kBN / 2, kBN / 4,
+                kBN / 8);
+  } else {
+    return fail(B200_EUNSUPPORTED, "group_size=%d must equal n or be a multiple of the N tile %d (smaller groups need ctas = 2 and reconn_sz <= 64)",
+                group_size, kBN);
   }
 }
 
@@ -386,7 +427,7 @@ int oft_dispatch(int m, int n, int k, int group_size, int b, const void* A, int 
   if (b == 8) {  // scratch from the stream-ordered allocator: no device-wide synchronisation, no sharing between calls
     const int n_groups = n / group_size;
     void* rx = nullptr;
-    CUDA_TRY(cudaMallocAsync(&rx, r8_bytes(n_groups, k), stream));
+    CUDA_TRY(cudaMallocFromPoolAsync(&rx, r8_bytes(n_groups, k), st->pool, stream));
     int rc = expand_r8(R, ldR, rx, n_groups, k, stream);
     if (rc == B200_OK) rc = launch_oft<16>(m, n, k, group_size, A, ldA, B, ldB, rx, static_cast<int>(r8_ld(k)), C, ldC, stream, st);
     cudaFreeAsync(rx, stream);
@@ -585,7 +626,9 @@ int b200_oft_tn_f16_a_rw(int m, int n, int k, int group_size, int reconn_sz, con
   }
   const int ldt = (k + 7) & ~7;
   void* bt = nullptr;
-  CUDA_TRY(cudaMallocAsync(&bt, static_cast<size_t>(n) * ldt * 2, stream));
+  DeviceState* st = nullptr;
+  if (int rc = device_state(&st)) return rc;
+  CUDA_TRY(cudaMallocFromPoolAsync(&bt, static_cast<size_t>(n) * ldt * 2, st->pool, stream));  // stays in the library's pool until b200_shutdown
   int rc = transform_weight(n, k, group_size, reconn_sz, B, ldB, R, ldR, bt, ldt, stream);
   // row-major C[m][n] is the column-major (n x m, ld = ldC) result of  Bt . A^T:  gemm_tn with the operands swapped
   if (rc == B200_OK) rc = b200_gemm_tn_f16(n, m, k, bt, ldt, A, ldA, C, ldC, stream);
@@ -629,8 +672,8 @@ const char* b200_kernel_info(void) {
   static char buf[768];
   using PH = Params<half, half, MMA_T, MMA_N>;
   using PF = Params<float, float, MMA_N, MMA_T>;
-  using O64 = OftT<64>;
-  using O128 = OftT<128>;
+  using O64 = OftT<64, 1>;
+  using O128 = OftT<128, 1>;
   snprintf(buf, sizeof buf,
            "{\"arch\": \"sm_100a\", \"gemm_half_tn\": {\"bM\": %d, \"bN\": %d, \"bK\": %d, \"bP\": %d}, "
            "\"gemm_float_nt\": {\"bM\": %d, \"bN\": %d, \"bK\": %d, \"bP\": %d}, "
@@ -657,6 +700,7 @@ int b200_shutdown(void) {
     cudaFree(st.status);
     for (int i = 0; i < 4; ++i) cudaFree(st.stage[i]);
     if (st.host_stream) cudaStreamDestroy(st.host_stream);
+    if (st.pool) cudaMemPoolDestroy(st.pool);
     st = DeviceState{};
   }
   cudaSetDevice(cur);

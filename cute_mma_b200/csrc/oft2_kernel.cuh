@@ -17,19 +17,23 @@
 
 namespace b200 {
 
-template <int kB_, int kBN_, int kS1_, int kS2_>
+template <int kB_, int kBN_, int kS1_, int kS2_, int kGT_ = 1>
 struct Oft2Traits {
   static constexpr int kB = kB_;
   static constexpr int kBM = 128;                      // rows per CTA; the pair covers 256
   static constexpr int kBN = kBN_;
   static constexpr int kBNHalf = kBN / 2;
+  static constexpr int kGT = kGT_;                     // N-groups per tile (group_size = bN / kGT): one R and one XR per group
+  static constexpr int kGS = kBN / kGT;                // columns of one group inside the tile (tcgen05 N of MMA2)
+  static constexpr int kGSHalf = kGS / 2;              // rows of a group's B sub-tile held by each CTA
   static constexpr int kBK = 64;
   static constexpr int kUnitK = kB > 64 ? kB : 64;
   static constexpr int kStagesPerUnit = kUnitK / kBK;
   static constexpr int kS1 = kS1_;
   static constexpr int kS2 = kS2_;
   static constexpr int kABytes = kBM * 128;
-  static constexpr int kRBytes = (kB / 2) * 128;       // this CTA's half of the R tile: b/2 rows (q) x 64 columns of K
+  static constexpr int kRHalfBytes = (kB / 2) * 128;   // this CTA's half of one group's R tile: b/2 rows (q) x 64 columns of K
+  static constexpr int kRBytes = kGT * kRHalfBytes;
   static constexpr int kS1Bytes = kABytes + kRBytes;
   static constexpr int kS2Bytes = kBNHalf * 128;
   static constexpr int kXrBufs = (512 - kBN) / kUnitK;
@@ -43,7 +47,8 @@ struct Oft2Traits {
   static_assert(kB == 16 || kB == 32 || kB == 64 || kB == 128, "block edge must be 16, 32, 64 or 128");
   static_assert(kBN % 64 == 0 && kBN >= 64 && kBN <= 256, "bN must be a multiple of 64 up to 256");
   static_assert(kTmemUsed <= kTmemCols && kXrBufs >= 2, "tensor memory budget exceeded");
-  static_assert(kRBytes % 1024 == 0, "R half-tile must keep the next tile 1024-byte aligned");
+  static_assert(kRHalfBytes % 1024 == 0, "R half-tile must keep the next tile 1024-byte aligned");
+  static_assert(kGT == 1 || (kStagesPerUnit == 1 && kGS % 16 == 0 && (kGSHalf * 128) % 1024 == 0), "several groups per tile need b <= 64 and group_size >= 16");
   static constexpr bool kFits = kSmemBytes <= 232448;
 };
 
@@ -81,7 +86,7 @@ oft2_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
   const int units = (args.k + T::kUnitK - 1) / T::kUnitK;
   unsigned my_tiles = 0;
   if (pair < num_tiles) my_tiles = (num_tiles - pair + num_pairs - 1) / num_pairs;
-  const unsigned total_units = my_tiles * units;
+  const unsigned total_units = my_tiles * units * T::kGT;  // XR hand-offs of this CTA: one per unit and per N-group of the tile
 
   if (threadIdx.x == 0) {
     *abort_flag = 0;
@@ -126,14 +131,16 @@ oft2_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
         unsigned tm, tn;
         tile_coord_r(args.raster, tiles_m, tiles_n, tile, tm, tn);
         const int m0 = tm * 2 * T::kBM + rank * T::kBM;
-        const int r_row0 = ((tn * T::kBN) / args.group_size) * T::kB + rank * (T::kB / 2);  // this CTA's half of the block rows
+        const int r_row0 = ((tn * T::kBN) / args.group_size) * T::kB + rank * (T::kB / 2);  // this CTA's half of the first group's block rows
         for (int st = 0; st < units * T::kStagesPerUnit; ++st, ++it) {
           const int s = it % T::kS1;
           if (!(ok = mbar_wait(empty1 + 8 * s, ((it / T::kS1) & 1) ^ 1, ctx, 10))) break;
           if (rank == 0) mbar_expect_tx(full1 + 8 * s, 2 * T::kS1Bytes);
           const uint32_t a_dst = ring1 + s * T::kS1Bytes;
           tma_load_2d_pair_hint(a_dst, &tmap_a, full1 + 8 * s, st * T::kBK, m0, args.hint_a);
-          tma_load_2d_pair_hint(a_dst + T::kABytes, &tmap_r, full1 + 8 * s, st * T::kBK, r_row0, kL2EvictLast);
+#pragma unroll
+          for (int gl = 0; gl < T::kGT; ++gl)
+            tma_load_2d_pair_hint(a_dst + T::kABytes + gl * T::kRHalfBytes, &tmap_r, full1 + 8 * s, st * T::kBK, r_row0 + gl * T::kB, kL2EvictLast);
         }
       }
       // leaving after its last round, this thread still counts for the rendezvous the others make
@@ -158,12 +165,14 @@ oft2_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
         }
         unsigned tm, tn;
         tile_coord_r(args.raster, tiles_m, tiles_n, tile, tm, tn);
-        const int n0 = tn * T::kBN + rank * T::kBNHalf;
+        const int n0 = tn * T::kBN + rank * T::kGSHalf;  // this CTA's half of each group's columns
         for (int st = 0; st < units * T::kStagesPerUnit; ++st, ++it) {
           const int s = it % T::kS2;
           if (!(ok = mbar_wait(empty2 + 8 * s, ((it / T::kS2) & 1) ^ 1, ctx, 11))) break;
           if (rank == 0) mbar_expect_tx(full2 + 8 * s, 2 * T::kS2Bytes);
-          tma_load_2d_pair_hint(ring2 + s * T::kS2Bytes, &tmap_b, full2 + 8 * s, st * T::kBK, n0, args.hint_b);
+#pragma unroll
+          for (int gl = 0; gl < T::kGT; ++gl)
+            tma_load_2d_pair_hint(ring2 + s * T::kS2Bytes + gl * T::kGSHalf * 128, &tmap_b, full2 + 8 * s, st * T::kBK, n0 + gl * T::kGS, args.hint_b);
         }
       }      if (ok && args.tile_sync && done_rounds > 0) atomicAdd(args.status + 6 + rank, 1);
     }
@@ -174,45 +183,49 @@ oft2_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
     if (lane == 0 && rank == 0) {
       constexpr uint32_t idesc1 = umma_idesc(kFmtF16, 0, 0, 2 * T::kBM, T::kB);
       const uint64_t a_desc0 = umma_desc_sw128(ring1, 16, 1024), r_desc0 = umma_desc_sw128(ring1 + T::kABytes, 16, 1024);
-      const unsigned total_stages = total_units * T::kStagesPerUnit;
+      const unsigned total_stages = my_tiles * units * T::kStagesPerUnit;
       int s = 0, xb = 0, su = 0;
       uint32_t ph_s = 0, ph_xb = 0;
       bool have_full = false, have_buf = false, ok = true;
       for (unsigned j = 0; ok && j < total_stages; ++j) {
-        if (su == 0 && !have_buf && !(ok = mbar_wait(x_empty + 8 * xb, ph_xb ^ 1, ctx, 20))) break;
         if (!have_full && !(ok = mbar_wait(full1 + 8 * s, ph_s, ctx, 21))) break;
-        tc_fence_after();
-        const uint32_t d1 = tmem_base + T::kColXr + xb * T::kUnitK;
         const uint64_t a_desc = a_desc0 + static_cast<uint64_t>(s * (T::kS1Bytes >> 4));
-        const uint64_t r_desc = r_desc0 + static_cast<uint64_t>(s * (T::kS1Bytes >> 4));
         const bool unit_ends = (su == T::kStagesPerUnit - 1);
-        int s_n = s + 1, xb_n = xb;
-        uint32_t ph_s_n = ph_s, ph_xb_n = ph_xb;
+        int s_n = s + 1;
+        uint32_t ph_s_n = ph_s;
         if (s_n == T::kS1) { s_n = 0; ph_s_n ^= 1; }
-        if (unit_ends && ++xb_n == T::kXrBufs) { xb_n = 0; ph_xb_n ^= 1; }
 #pragma unroll
-        for (int kk = 0; kk < T::kBK / 16; ++kk) {
-          if (kk == 2) {
-            const bool more = j + 1 < total_stages;
-            have_full = more && mbar_test_wait(full1 + 8 * s_n, ph_s_n);
-            have_buf = more && unit_ends && mbar_test_wait(x_empty + 8 * xb_n, ph_xb_n ^ 1);
+        for (int gl = 0; gl < T::kGT; ++gl) {  // one XR per N-group of the tile, all from the same stage of A
+          if (su == 0 && !have_buf && !(ok = mbar_wait(x_empty + 8 * xb, ph_xb ^ 1, ctx, 20))) break;
+          tc_fence_after();
+          const uint32_t d1 = tmem_base + T::kColXr + xb * T::kUnitK;
+          const uint64_t r_desc = r_desc0 + static_cast<uint64_t>((s * T::kS1Bytes + gl * T::kRHalfBytes) >> 4);
+          int xb_n = xb;
+          uint32_t ph_xb_n = ph_xb;
+          if (unit_ends && ++xb_n == T::kXrBufs) { xb_n = 0; ph_xb_n ^= 1; }
+#pragma unroll
+          for (int kk = 0; kk < T::kBK / 16; ++kk) {
+            if (kk == 2) {
+              const bool more = (j + 1 < total_stages) || (gl + 1 < T::kGT);
+              if (gl == T::kGT - 1) have_full = (j + 1 < total_stages) && mbar_test_wait(full1 + 8 * s_n, ph_s_n);
+              have_buf = more && unit_ends && mbar_test_wait(x_empty + 8 * xb_n, ph_xb_n ^ 1);
+            }
+            constexpr bool small = T::kB < 64;
+            const int blk = small ? (kk * 16) / T::kB : 0;
+            const uint32_t accum = small ? ((((kk * 16) % T::kB) != 0) ? 1u : 0u) : ((su > 0 || kk > 0) ? 1u : 0u);
+            umma_f16_ss_pair(d1 + blk * T::kB, a_desc + kk * 2, r_desc + kk * 2, idesc1, accum);
           }
-          constexpr bool small = T::kB < 64;
-          const int blk = small ? (kk * 16) / T::kB : 0;
-          const uint32_t accum = small ? ((((kk * 16) % T::kB) != 0) ? 1u : 0u) : ((su > 0 || kk > 0) ? 1u : 0u);
-          umma_f16_ss_pair(d1 + blk * T::kB, a_desc + kk * 2, r_desc + kk * 2, idesc1, accum);
+          if (unit_ends) {
+            umma_commit_pair(x_acc + 8 * xb, 3);  // the converters of both CTAs start on their halves
+            xb = xb_n;
+            ph_xb = ph_xb_n;
+          }
         }
+        if (!ok) break;
         umma_commit_pair(empty1 + 8 * s, 3);
         s = s_n;
         ph_s = ph_s_n;
-        if (unit_ends) {
-          umma_commit_pair(x_acc + 8 * xb, 3);  // the converters of both CTAs start on their halves
-          xb = xb_n;
-          ph_xb = ph_xb_n;
-          su = 0;
-        } else {
-          ++su;
-        }
+        su = unit_ends ? 0 : su + 1;
       }
     }
     __syncwarp();
@@ -220,45 +233,51 @@ oft2_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
     // -------------------------------------------------------------- issuer of MMA2 (leader CTA only)
     setmaxnreg_dec<96>();
     if (lane == 0 && rank == 0) {
-      constexpr uint32_t idesc2 = umma_idesc(kFmtF16, 0, 0, 2 * T::kBM, T::kBN);
+      constexpr uint32_t idesc2 = umma_idesc(kFmtF16, 0, 0, 2 * T::kBM, T::kGS);
       const uint64_t b_desc0 = umma_desc_sw128(ring2, 16, 1024);
-      const unsigned total_stages = total_units * T::kStagesPerUnit;
+      const unsigned total_stages = my_tiles * units * T::kStagesPerUnit;
       int s = 0, xb = 0, ku = 0, su = 0;
       uint32_t ph_s = 0, ph_xb = 0, ph_acc = 0;
       bool have_full = false, have_half = false, ok = true;
       for (unsigned j = 0; ok && j < total_stages; ++j) {
         if (su == 0 && ku == 0 && !(ok = mbar_wait(acc_empty, ph_acc ^ 1, ctx, 22))) break;
-        if (!have_half && !(ok = mbar_wait(x_half + 8 * (xb * T::kStagesPerUnit + su), ph_xb, ctx, 23))) break;
         if (!have_full && !(ok = mbar_wait(full2 + 8 * s, ph_s, ctx, 24))) break;
-        tc_fence_after();
-        const uint32_t a_tmem = tmem_base + T::kColXr + xb * T::kUnitK + su * (T::kBK / 2);
-        const uint64_t b_desc = b_desc0 + static_cast<uint64_t>(s * (T::kS2Bytes >> 4));
         const bool unit_ends = (su == T::kStagesPerUnit - 1);
-        int s_n = s + 1, xb_n = xb;
-        uint32_t ph_s_n = ph_s, ph_xb_n = ph_xb;
+        int s_n = s + 1;
+        uint32_t ph_s_n = ph_s;
         if (s_n == T::kS2) { s_n = 0; ph_s_n ^= 1; }
-        if (unit_ends && ++xb_n == T::kXrBufs) { xb_n = 0; ph_xb_n ^= 1; }
         const int su_n = unit_ends ? 0 : su + 1;
 #pragma unroll
-        for (int kk = 0; kk < T::kBK / 16; ++kk) {
-          if (kk == 2) {
-            const bool more = j + 1 < total_stages;
-            have_full = more && mbar_test_wait(full2 + 8 * s_n, ph_s_n);
-            have_half = more && mbar_test_wait(x_half + 8 * (xb_n * T::kStagesPerUnit + su_n), ph_xb_n);
+        for (int gl = 0; gl < T::kGT; ++gl) {  // each N-group multiplies its own XR into its own columns of the accumulator
+          if (!have_half && !(ok = mbar_wait(x_half + 8 * (xb * T::kStagesPerUnit + su), ph_xb, ctx, 23))) break;
+          tc_fence_after();
+          const uint32_t a_tmem = tmem_base + T::kColXr + xb * T::kUnitK + su * (T::kBK / 2);
+          const uint64_t b_desc = b_desc0 + static_cast<uint64_t>((s * T::kS2Bytes + gl * T::kGSHalf * 128) >> 4);
+          int xb_n = xb;
+          uint32_t ph_xb_n = ph_xb;
+          if (unit_ends && ++xb_n == T::kXrBufs) { xb_n = 0; ph_xb_n ^= 1; }
+#pragma unroll
+          for (int kk = 0; kk < T::kBK / 16; ++kk) {
+            if (kk == 2) {
+              const bool more = (j + 1 < total_stages) || (gl + 1 < T::kGT);
+              if (gl == T::kGT - 1) have_full = (j + 1 < total_stages) && mbar_test_wait(full2 + 8 * s_n, ph_s_n);
+              have_half = more && mbar_test_wait(x_half + 8 * (xb_n * T::kStagesPerUnit + (T::kGT > 1 ? 0 : su_n)), ph_xb_n);
+            }
+            const uint32_t accum = (su > 0 || kk > 0) ? 1u : (ku > 0 ? 1u : 0u);
+            umma_f16_ts_pair(tmem_base + T::kColAcc + gl * T::kGS, a_tmem + kk * 8, b_desc + kk * 2, idesc2, accum);
           }
-          const uint32_t accum = (su > 0 || kk > 0) ? 1u : (ku > 0 ? 1u : 0u);
-          umma_f16_ts_pair(tmem_base + T::kColAcc, a_tmem + kk * 8, b_desc + kk * 2, idesc2, accum);
+          if (unit_ends) {
+            umma_commit_pair(x_empty + 8 * xb, 1);  // only the leader's MMA1 issuer waits for this
+            xb = xb_n;
+            ph_xb = ph_xb_n;
+          }
         }
+        if (!ok) break;
         umma_commit_pair(empty2 + 8 * s, 3);
-        if (unit_ends) {
-          umma_commit_pair(x_empty + 8 * xb, 1);  // only the leader's MMA1 issuer waits for this
-          if (ku + 1 == units) umma_commit_pair(acc_full, 3);
-        }
+        if (unit_ends && ku + 1 == units) umma_commit_pair(acc_full, 3);
         s = s_n;
         ph_s = ph_s_n;
         if (unit_ends) {
-          xb = xb_n;
-          ph_xb = ph_xb_n;
           su = 0;
           if (++ku == units) {
             ku = 0;

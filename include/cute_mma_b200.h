@@ -32,9 +32,11 @@ enum {
  *   all row-major; stored R block (g,kb) = rows g*b.., cols kb*b.. holds the TRANSPOSE of the
  *   mathematical rotation.  fp32 accumulation, X.R rounded to fp16 (RNE) before the main product.
  * reconn_sz in {8, 16, 32, 64, 128}; k % reconn_sz == 0; n % group_size == 0; group_size == n or a
- * multiple of the kernel's N tile.  reconn_sz = 8 (the reference's default) first expands R into pairs of
- * 8 x 8 blocks embedded in zero-padded 16 x 16 blocks (device scratch of twice the size of R, taken from
- * the stream-ordered allocator, cudaMallocAsync / cudaFreeAsync on `stream`) and then runs as 16. */
+ * multiple of the kernel's N tile (256), or, with reconn_sz <= 64, one half, quarter or eighth of it
+ * (the reference's bN % group_size == 0 case, cute_oft_coop_pc.cu:383).  reconn_sz = 8 (the reference's
+ * default) first expands R into pairs of 8 x 8 blocks embedded in zero-padded 16 x 16 blocks (device
+ * scratch of twice the size of R, stream-ordered on `stream` from a memory pool the library keeps until
+ * b200_shutdown) and then runs as 16. */
 int b200_oft_tn_f16(int m, int n, int k, int group_size, int reconn_sz,
                     const void* A, int ldA, const void* B, int ldB, const void* R, int ldR,
                     void* C, int ldC, void* stream);
