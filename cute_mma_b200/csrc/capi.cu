@@ -3,6 +3,7 @@
 // buffers of the host-buffer entry point).  Takes over the role of the reference's host launchers
 // oft_tn (cute_oft_coop_pc.cu:505-577) and gemm_tn / gemm_nt / gemm (gemm_sm80_tc.cu:95-228, 393-418),
 // with the checks the reference leaves out (shape, alignment, shared-memory opt-in).
+#include <cmath>
 #include <cstdarg>
 #include <cstdio>
 #include <cstdlib>
@@ -22,6 +23,7 @@
 #include "gemm2_kernel.cuh"
 #include "oft_kernel.cuh"
 #include "oft2_kernel.cuh"
+#include "xr_kernel.cuh"
 
 namespace {
 
@@ -205,10 +207,16 @@ int launch_gemm(int m, int n, int k, const void* A, int ldA, const void* B, int 
     if (try3d && make_map_chunks(&mb, B, sizeof(TIn), n, k, ldB, T1::kChunk, T1::kBK, kBoxN / T1::kChunk, T1::kB32Atom) == B200_OK) b3d = 1;
     else if (int rc = make_map(&mb, B, sizeof(TIn), n, k, ldB, T1::kChunk, T1::kBK, "B", T1::kB32Atom)) return rc;
   }
-  int tile_sync = 0;  // cross-CTA phase lock of the tile rounds (see launch_oft); experiments only for the plain GEMM
+  // Cross-CTA phase lock of the tile rounds and banded tile order (see launch_oft) when the operand that spans
+  // N is far larger than L2.  Measured at M 28672, N 65536, K 8192 (fp16): 34.2 ms with neither, 30.0 ms with
+  // bands of 8 tile rows, 25.7 ms with both.  At 8192^3 (128 MB operand) both cost a few per cent, so they stay off.
+  const bool big = kPair && static_cast<long long>(n) * k * static_cast<long long>(sizeof(TIn)) > 3ll * st->l2_bytes;
+  int tile_sync = big ? 1 : 0;
   if (const char* e = std::getenv("B200_GEMM_TILE_SYNC")) tile_sync = kPair ? std::atoi(e) : 0;
   if (tile_sync) CUDA_TRY(cudaMemsetAsync(st->status + 4, 0, 4 * sizeof(int), stream));
-  GemmArgs args{m, n, k, C, ldC, st->status, raster_for(static_cast<long long>(n) * k * sizeof(TIn), false), tile_sync, a3d, b3d};
+  int raster = raster_for(static_cast<long long>(n) * k * sizeof(TIn), false);
+  if (big && !std::getenv("B200_RASTER")) raster = 8;
+  GemmArgs args{m, n, k, C, ldC, st->status, raster, tile_sync, a3d, b3d};
   if constexpr (kPair) {
     auto kernel = gemm2_kernel<T2>;
     if (int rc = opt_in_smem(kernel, T2::kSmemBytes)) return rc;
@@ -290,12 +298,74 @@ int launch_oft_gt(int m, int n, int k, int group_size, const void* A, int ldA, c
   }
 }
 
+// ---- two-pass OFT: rotation pass + plain GEMM ---------------------------------------------------------------
+// The fused kernel recomputes X.R for every N tile of a group: per 64 columns of K a pair of SMs spends 726
+// cycles (b <= 64) or 963 cycles (b = 128) where the plain GEMM spends 570.  Writing X.R to memory once
+// (xr_kernel, bound by 4 bytes of traffic per element of X) and running the plain GEMM on it is cheaper as
+// soon as a group spans enough N tiles: measured at M 65536, K 8192, N 28672, b 128: 38.2 ms fused, 26 ms in
+// two passes.  Same arithmetic as the fused kernel: X.R rounded once to fp16, fp32 accumulation of the product.
+template <int kB>
+int launch_xr(int m, int k, const void* A, int ldA, const void* Rg, int ldR, void* XR, long long ldX, cudaStream_t stream, DeviceState* st) {
+  using T = XrTraits<kB, 6>;
+  CUtensorMap ma, mr;
+  if (int rc = make_map(&ma, A, 2, k, m, ldA, T::kBK, T::kBM, "A")) return rc;
+  if (int rc = make_map(&mr, Rg, 2, k, kB, ldR, T::kBK, kB, "R")) return rc;
+  XrArgs args{m, k, static_cast<__half*>(XR), ldX, st->status};
+  const long long units = static_cast<long long>((m + T::kBM - 1) / T::kBM) * ((k + T::kUnitK - 1) / T::kUnitK);
+  auto kernel = xr_kernel<T>;
+  if (int rc = opt_in_smem(kernel, T::kSmemBytes)) return rc;
+  kernel<<<static_cast<int>(units < st->sm_count ? units : st->sm_count), T::kThreads, T::kSmemBytes, stream>>>(ma, mr, args);
+  CUDA_TRY(cudaGetLastError());
+  return B200_OK;
+}
+
+template <int kB>
+int oft_two_pass(int m, int n, int k, int group_size, const void* A, int ldA, const void* B, int ldB, const void* R, int ldR,
+                 void* C, int ldC, cudaStream_t stream, DeviceState* st) {
+  if (!st->pool) return fail(B200_EUNSUPPORTED, "the two-pass path needs the library's scratch pool");
+  const long long ldx = (k + 7) & ~7;
+  void* xr = nullptr;
+  CUDA_TRY(cudaMallocFromPoolAsync(&xr, static_cast<size_t>(m) * ldx * 2, st->pool, stream));  // stays in the pool until b200_shutdown
+  int rc = B200_OK;
+  for (int g = 0; rc == B200_OK && g < n / group_size; ++g) {  // stream order serialises the groups on the one XR buffer
+    rc = launch_xr<kB>(m, k, A, ldA, static_cast<const __half*>(R) + static_cast<long long>(g) * kB * ldR, ldR, xr, ldx, stream, st);
+    // row-major C[m][n] is the column-major (n x m, ld = ldC) result of  W_g . XR^T:  gemm_tn with the operands swapped
+    if (rc == B200_OK)
+      rc = b200_gemm_tn_f16(group_size, m, k, static_cast<const __half*>(B) + static_cast<long long>(g) * group_size * ldB, ldB, xr,
+                            static_cast<int>(ldx), static_cast<__half*>(C) + static_cast<long long>(g) * group_size, ldC, stream);
+  }
+  const std::string keep = g_err;
+  cudaFreeAsync(xr, stream);
+  g_err = keep;
+  return rc;
+}
+
+// 0: choose by the cost estimate below, 1: fused kernel, 2: two passes.  Set by b200_oft_tn_f16_two_pass for its
+// own call and by B200_OFT_PATH for experiments.
+thread_local int g_oft_path = 0;
+
+bool prefer_two_pass(int m, int k, int group_size, int b, const DeviceState* st) {
+  int path = g_oft_path;
+  if (path == 0)
+    if (const char* e = std::getenv("B200_OFT_PATH")) path = std::atoi(e);
+  if (!st->pool || !kOftPair) return false;  // no scratch to put X.R in (static-scratch entry point) / single-CTA build
+  if (path == 1) return false;
+  if (path == 2) return true;
+  // Cycles of one SM pair per (256 x 256 tile, 64 columns of K), measured with in-kernel cycle counters.
+  const double units = std::ceil(m / 256.0) * std::ceil(group_size / 256.0) * std::ceil(k / 64.0);
+  const double pairs = st->sm_count / 2, hz = 1.4e9;
+  const double fused = units * (b == 128 ? 963.0 : 726.0) / (pairs * hz);
+  const double two = units * 570.0 / (pairs * hz) + 4.0 * m * static_cast<double>(k) / 5.5e12 + 8e-6;
+  return group_size >= 256 && two < 0.93 * fused;
+}
+
 // group_size == n or a multiple of the N tile: one R per tile.  group_size a divisor of the N tile (the
 // reference's bN % group_size == 0 case, cute_oft_coop_pc.cu:383): bN / group_size groups per tile, pair kernel.
 template <int kB>
 int launch_oft(int m, int n, int k, int group_size, const void* A, int ldA, const void* B, int ldB, const void* R, int ldR,
                void* C, int ldC, cudaStream_t stream, DeviceState* st) {
   constexpr int kBN = CurrCompParams::bN;
+  if (prefer_two_pass(m, k, group_size, kB, st)) return oft_two_pass<kB>(m, n, k, group_size, A, ldA, B, ldB, R, ldR, C, ldC, stream, st);
   if (group_size == n || group_size % kBN == 0) return launch_oft_gt<kB, 1>(m, n, k, group_size, A, ldA, B, ldB, R, ldR, C, ldC, stream, st);
   if constexpr (kOftPair && kB <= 64) {
     if (kBN % group_size == 0) {
@@ -513,6 +583,14 @@ extern "C" {
 int b200_oft_tn_f16(int m, int n, int k, int group_size, int reconn_sz, const void* A, int ldA, const void* B, int ldB,
                     const void* R, int ldR, void* C, int ldC, void* stream) {
   return oft_dispatch(m, n, k, group_size, reconn_sz, A, ldA, B, ldB, R, ldR, C, ldC, static_cast<cudaStream_t>(stream));
+}
+
+int b200_oft_tn_f16_two_pass(int m, int n, int k, int group_size, int reconn_sz, const void* A, int ldA, const void* B, int ldB,
+                             const void* R, int ldR, void* C, int ldC, void* stream) {
+  g_oft_path = 2;
+  const int rc = oft_dispatch(m, n, k, group_size, reconn_sz, A, ldA, B, ldB, R, ldR, C, ldC, static_cast<cudaStream_t>(stream));
+  g_oft_path = 0;
+  return rc;
 }
 
 int b200_oft_tn_f16_host(int m, int n, int k, int group_size, int reconn_sz, const void* A, int ldA, const void* B, int ldB,

@@ -23,7 +23,7 @@ OK, EINVAL, EUNSUPPORTED, ECUDA, EDEVICE = 0, 1, 2, 3, 4
 
 # every symbol include/cute_mma_b200.h declares
 SYMBOLS = (
-    "b200_oft_tn_f16", "b200_oft_tn_f16_host", "b200_oft_tn_f16_static", "b200_transform_weight_f16", "b200_oft_tn_f16_a_rw", "b200_gemm_tn_f16", "b200_gemm_nt_f16", "b200_gemm_tn_tf32",
+    "b200_oft_tn_f16", "b200_oft_tn_f16_two_pass", "b200_oft_tn_f16_host", "b200_oft_tn_f16_static", "b200_transform_weight_f16", "b200_oft_tn_f16_a_rw", "b200_gemm_tn_f16", "b200_gemm_nt_f16", "b200_gemm_tn_tf32",
     "b200_gemm_nt_tf32", "b200_gemm", "b200_shard_range", "b200_tile_coord", "b200_device_status", "b200_selftest_wait_timeout", "b200_wait_profile", "b200_kernel_info",
     "b200_last_error", "b200_shutdown",
 )
@@ -55,6 +55,7 @@ def load_library(path: str | None = None):
     i, vp, c = ctypes.c_int, ctypes.c_void_p, ctypes.c_char
     lib.b200_oft_tn_f16.argtypes = [i, i, i, i, i, vp, i, vp, i, vp, i, vp, i, vp]
     lib.b200_oft_tn_f16_static.argtypes = [i, i, i, i, i, vp, i, vp, i, vp, i, vp, i, vp]
+    lib.b200_oft_tn_f16_two_pass.argtypes = [i, i, i, i, i, vp, i, vp, i, vp, i, vp, i, vp]
     lib.b200_oft_tn_f16_a_rw.argtypes = [i, i, i, i, i, vp, i, vp, i, vp, i, vp, i, vp]
     lib.b200_transform_weight_f16.argtypes = [i, i, i, i, vp, i, vp, i, vp, i, vp]
     lib.b200_oft_tn_f16_host.argtypes = [i, i, i, i, i, vp, i, vp, i, vp, i, vp, i]
@@ -105,6 +106,14 @@ def oft_tn(m, n, k, A, ldA, B, ldB, R, ldR, C, ldC, stream=None, *, group_size=N
     lib = lib or load_library()
     gs = n if group_size is None else group_size
     _check(lib, lib.b200_oft_tn_f16(m, n, k, gs, reconn_sz, _ptr(A), ldA, _ptr(B), ldB, _ptr(R), ldR, _ptr(C), ldC, _stream(stream)))
+
+
+def oft_tn_two_pass(m, n, k, A, ldA, B, ldB, R, ldR, C, ldC, stream=None, *, group_size=None, reconn_sz=8, lib=None) -> None:
+    """oft_tn as a rotation pass (X.R written once to device scratch) followed by the plain GEMM, the route
+    oft_tn takes by itself when a group spans many N tiles (see b200_oft_tn_f16_two_pass in the header)."""
+    lib = lib or load_library()
+    gs = n if group_size is None else group_size
+    _check(lib, lib.b200_oft_tn_f16_two_pass(m, n, k, gs, reconn_sz, _ptr(A), ldA, _ptr(B), ldB, _ptr(R), ldR, _ptr(C), ldC, _stream(stream)))
 
 
 def oft_tn_static(m, n, k, A, ldA, B, ldB, R, ldR, C, ldC, stream=None, *, group_size=None, reconn_sz=8, lib=None) -> None:

@@ -41,6 +41,17 @@ int b200_oft_tn_f16(int m, int n, int k, int group_size, int reconn_sz,
                     const void* A, int ldA, const void* B, int ldB, const void* R, int ldR,
                     void* C, int ldC, void* stream);
 
+/* The same product in two passes: X.R (rounded to fp16, as above) is written once to device scratch of
+ * m * k * 2 bytes (stream-ordered on `stream`, from the pool the library keeps until b200_shutdown) and
+ * the plain fp16 GEMM runs on it, group by group.  b200_oft_tn_f16 takes this path by itself when its
+ * cost estimate says so (a group that spans many N tiles; B200_OFT_PATH=1 keeps it on the fused kernel);
+ * this entry point always does.  Counterpart in the reference: cublas_oft(..., RW_mode = false), the AR_W
+ * order with a batched cuBLAS GEMM for X.R and one cublasHgemm per group (cublas_oft.hpp:66-91); its own
+ * kernel never lets X.R leave the thread block (cute_oft_coop_pc.cu:19-186). */
+int b200_oft_tn_f16_two_pass(int m, int n, int k, int group_size, int reconn_sz,
+                             const void* A, int ldA, const void* B, int ldB, const void* R, int ldR,
+                             void* C, int ldC, void* stream);
+
 /* Same product with HOST buffers: copies A, B, R to the device, runs the kernel, copies C back and
  * synchronises before returning.  Device staging buffers are owned and reused by the library.
  * This is the call the end-to-end figure of bench.py times. */

@@ -1,4 +1,6 @@
 """GPU parity of the fused OFT kernel against the CPU oracle, through the C ABI."""
+import os
+
 import numpy as np
 import pytest
 
@@ -9,7 +11,7 @@ from oracle import oracle
 pytestmark = pytest.mark.gpu
 
 
-def run_oft(lib, cuda, A, R, B, m, n, k, b, group_size=None, ldA=None, ldB=None, ldR=None, ldC=None, canary=True):
+def run_oft(lib, cuda, A, R, B, m, n, k, b, group_size=None, ldA=None, ldB=None, ldR=None, ldC=None, canary=True, fn=None):
     """Uploads the operands (optionally with padded leading dimensions), runs b200_oft_tn_f16 and
     returns C[m,n] as numpy.  The padding of C is filled with a canary and must come back untouched."""
     import torch
@@ -24,7 +26,7 @@ def run_oft(lib, cuda, A, R, B, m, n, k, b, group_size=None, ldA=None, ldB=None,
 
     dA, dB, dR = up(A, ldA), up(B, ldB), up(R, ldR)
     dC = torch.full((m + 1, ldC), -7.0, dtype=torch.float16, device=cuda)  # one canary row + canary columns
-    ops.oft_tn(m, n, k, dA, ldA, dB, ldB, dR, ldR, dC, ldC, group_size=group_size, reconn_sz=b, lib=lib)
+    (fn or ops.oft_tn)(m, n, k, dA, ldA, dB, ldB, dR, ldR, dC, ldC, group_size=group_size, reconn_sz=b, lib=lib)
     st = ops.device_status(lib)
     assert st[0] == 0, st
     out = dC.cpu().numpy()
@@ -77,6 +79,76 @@ def test_oft_matches_oracle(lib, cuda, m, n, k, b, gs):
     assert bad_t == 0, f"{bad_t} elements further than 2e-3*(|y|+1) from exact arithmetic; worst {worst_t:.3e}"
     if k // b <= 4:  # few re-roundings in the oracle: the stated tolerance holds without any allowance
         assert oft_ok(got, ref)[0] == 0
+
+
+TWO_PASS_CASES = [
+    (128, 256, 64, 64, None),
+    (384, 512, 512, 64, None),
+    (384, 512, 512, 32, None),
+    (384, 512, 512, 16, None),
+    (256, 512, 512, 128, None),
+    (200, 328, 192, 64, None),     # ragged M and N
+    (136, 264, 96, 32, None),      # K not a multiple of the 64-wide unit
+    (200, 328, 264, 8, None),      # 8 x 8 blocks, odd number of them
+    (72, 40, 128, 16, None),       # smaller than one tile
+    (128, 768, 128, 16, 256),      # three groups: the passes repeat per group on the one X.R buffer
+    (256, 512, 256, 128, 256),
+]
+
+
+@pytest.mark.parametrize("m,n,k,b,gs", TWO_PASS_CASES)
+def test_oft_two_pass_matches_oracle_and_fused(lib, cuda, m, n, k, b, gs):
+    """Rotation pass + plain GEMM: same tolerances against the oracle as the fused kernel, and the two
+    routes agree with each other to fp32-summation-order noise (both round X.R to fp16 once)."""
+    A, R, B = make_oft_case(m, n, k, b, gs, seed=21, kind="qr")
+    ref = oracle_full(A, R, B, m, n, k, b, gs)
+    got = run_oft(lib, cuda, A, R, B, m, n, k, b, gs, fn=ops.oft_tn_two_pass)
+    truth = oracle.oft_f64(A, R, B, m, n if gs is None else gs, 1 if gs is None else n // gs, k, b, round_xr=True)
+    bad, worst = oft_ok(got, ref, truth=truth)
+    assert bad == 0, (bad, worst)
+    bad_t, worst_t = truth_ok(got, truth)
+    assert bad_t == 0, (bad_t, worst_t)
+    if k // b <= 4:
+        assert oft_ok(got, ref)[0] == 0
+    os.environ["B200_OFT_PATH"] = "1"
+    try:
+        fused = run_oft(lib, cuda, A, R, B, m, n, k, b, gs)
+    finally:
+        del os.environ["B200_OFT_PATH"]
+    d = np.abs(got.astype(np.float64) - fused.astype(np.float64))
+    assert np.all(d <= 2.0 ** -10 * (np.abs(fused.astype(np.float64)) + 1.0)), float(d.max())
+
+
+def test_oft_two_pass_padded_and_bit_exact_cases(lib, cuda):
+    m, n, k, b = 200, 328, 192, 64
+    A, R, B = make_oft_case(m, n, k, b, seed=3)
+    ref = oracle_full(A, R, B, m, n, k, b)
+    got = run_oft(lib, cuda, A, R, B, m, n, k, b, ldA=k + 8, ldB=k + 16, ldR=k + 24, ldC=n + 8, fn=ops.oft_tn_two_pass)
+    assert oft_ok(got, ref)[0] == 0
+    # 0/1 inputs with permutation blocks: every partial sum is an exactly representable integer
+    m, n, k, b = 256, 512, 256, 32
+    A, R, B = make_oft_case(m, n, k, b, seed=9, kind="perm", xdist="01")
+    ref = oracle_full(A, R, B, m, n, k, b)
+    got = run_oft(lib, cuda, A, R, B, m, n, k, b, fn=ops.oft_tn_two_pass)
+    assert np.array_equal(got.view(np.uint16), ref.view(np.uint16))
+
+
+def test_oft_path_choice_is_invisible(lib, cuda):
+    """A shape the cost estimate sends down the two-pass route (one group over many N tiles, b = 128) gives the
+    same answer, to summation-order noise, as the fused kernel forced by B200_OFT_PATH=1."""
+    import torch
+    m, n, k, b = 1024, 8192, 1024, 128
+    A, R, B = make_oft_case(m, n, k, b, seed=31, kind="qr", xdist="normal", wsigma=0.02)
+    auto = run_oft(lib, cuda, A, R, B, m, n, k, b)
+    os.environ["B200_OFT_PATH"] = "1"
+    try:
+        fused = run_oft(lib, cuda, A, R, B, m, n, k, b)
+    finally:
+        del os.environ["B200_OFT_PATH"]
+    d = np.abs(auto.astype(np.float64) - fused.astype(np.float64))
+    assert np.all(d <= 2.0 ** -10 * (np.abs(fused.astype(np.float64)) + 1.0)), float(d.max())
+    truth = oracle.oft_f64(A, R, B, m, n, 1, k, b, round_xr=True)
+    assert truth_ok(auto, truth)[0] == 0
 
 
 def test_oft_group_size_limits(lib, cuda):
