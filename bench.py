@@ -36,15 +36,18 @@ DEFAULT_WORKLOAD = "oft_large_m65536_k8192_n28672_b128"
 METRIC = "oft_fused_gemm_tflops"
 NOMINAL_FP16_TFLOPS = 2250.0  # vendor dense fp16 figure, context only
 
-# DRAM bytes of one launch of the dominant kernel, from the ncu capture summarised under profiles/
-# (dram__bytes_read.sum + dram__bytes_write.sum); None until a capture exists for the workload.
+# DRAM bytes of one launch of the dominant kernel, from the ncu captures summarised under profiles/
+# (dram__bytes_read.sum + dram__bytes_write.sum), keyed by workload and by the route the library takes;
+# None until a capture exists.
 NCU_TRAFFIC_BYTES = {
-    # per launch at N = 1, ncu one-pass counters on the full workload: read 29.2 GB + write 5.7 GB against
-    # 5.3 GB algorithmic (every wave of 74 tiles re-reads its panels of X and W once; it was 91.5 GB before
-    # the CTAs' tile rounds were phase-locked)
-    "oft_large_m65536_k8192_n28672_b128": 34.94e9,
+    # fused kernel, per launch at N = 1, one-pass counters on the full workload: read 29.2 GB + write 5.7 GB
+    # against 5.3 GB algorithmic (every wave of 74 tiles re-reads its panels of X and W once)
+    ("oft_large_m65536_k8192_n28672_b128", "fused"): 34.94e9,
+    # two-pass route, GEMM pass (gemm2_kernel), same one-pass counters: read 28.05 GB + write 3.75 GB against
+    # 5.3 GB algorithmic; the rotation pass before it moves 1.08 + 1.02 GB, exactly its algorithmic bytes
+    ("oft_large_m65536_k8192_n28672_b128", "two_pass"): 31.80e9,
     # ncu --set full capture of the same shape (read 363 MB + write 154 MB; algorithmic 303 MB)
-    "oft_proj_m16384_k4096_n4096_b64": 517.2e6,
+    ("oft_proj_m16384_k4096_n4096_b64", "fused"): 517.2e6,
 }
 
 
@@ -217,7 +220,7 @@ def projection_shape_rate(lib, dev, stream):
     assert ops.device_status(lib)[0] == 0
     tf = flops_of(m, k, n, b) / (ms * 1e-3) * 1e-12
     peaks = measured_peaks()
-    return {"workload": name, "value": tf, "unit": "TFLOP/s", "ms_per_step": ms, "steps": 50,
+    return {"workload": name, "value": tf, "unit": "TFLOP/s", "ms_per_step": ms, "steps": 50, "route": ops.oft_plan(m, n, k, reconn_sz=b, lib=lib)["path"],
             "frac_of_measured_bf16_burst": tf / peaks["bf16_burst"], "frac_of_nominal_fp16": tf / NOMINAL_FP16_TFLOPS}
 
 
@@ -290,6 +293,32 @@ def run_gpu_arm(args, workload):
     total_flops = flops_of(m, k, n, b)
     value = total_flops / (ms * 1e-3) * 1e-12
 
+    # which route the library took, and for the two-pass route the duration of each pass on its own
+    plan = ops.oft_plan(m, n_loc, k, reconn_sz=b, lib=lib)
+    passes = None
+    gemm_ms = ms_local
+    if plan["path"] == "two_pass":
+        dXR = torch.empty((m, k), dtype=torch.float16, device=dev)
+
+        def timed(fn, reps):
+            for _ in range(2):
+                fn()
+            torch.cuda.synchronize()
+            t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            t0.record(stream)
+            for _ in range(reps):
+                fn()
+            t1.record(stream)
+            torch.cuda.synchronize()
+            return t0.elapsed_time(t1) / reps
+
+        rot_ms = timed(lambda: ops.rotate(m, k, dX, k, dR, k, dXR, k, stream, reconn_sz=b, lib=lib), max(args.steps, 5))
+        gemm_ms = timed(lambda: ops.gemm_tn(n_loc, m, k, dW, k, dXR, k, dY, n_loc, stream, lib=lib), args.steps)
+        passes = {"rotate_ms": rot_ms, "rotate_gbs": 4.0 * m * k / (rot_ms * 1e-3) * 1e-9, "rotate_frac_of_measured_hbm": None,
+                  "gemm_ms": gemm_ms, "gemm_tflops": 2.0 * m * n_loc * k / (gemm_ms * 1e-3) * 1e-12}
+        del dXR
+        assert ops.device_status(lib)[0] == 0
+
     # optional exchange, timed on its own
     allgather_ms = None
     if args.allgather and world > 1:
@@ -335,26 +364,34 @@ def run_gpu_arm(args, workload):
 
     if rank == 0:
         peaks = measured_peaks()
-        flops_launch = flops_of(m, k, n_loc, b)  # algorithmic FLOPs of one launch on this rank
-        achieved = flops_launch / (ms_local * 1e-3) * 1e-12
+        # dominant kernel: the fused kernel (its launch is the step), or the GEMM pass of the two-pass route
+        # (timed on its own above; algorithmic FLOPs 2 M N K, the rotation's 2 M K b belong to the other pass)
+        two = plan["path"] == "two_pass"
+        flops_launch = 2.0 * m * n_loc * k if two else flops_of(m, k, n_loc, b)
+        achieved = flops_launch / (gemm_ms * 1e-3) * 1e-12
         timed_s = ms * args.steps * 1e-3
         peak = peaks["bf16_sustained"] if timed_s >= 2.0 else peaks["bf16_burst"]
+        if passes is not None:
+            passes["rotate_frac_of_measured_hbm"] = passes["rotate_gbs"] / peaks["hbm_gbs"]
         line = {
             "metric": METRIC, "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
             "ms_per_step": ms, "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f16",
             "data": "synthetic",
             "config": {"workload": workload, "M": m, "K": k, "N": n, "b": b, "n_per_gpu": n_loc, "sharding": f"N over {world} GPU(s), X and R replicated",
                        "flops": "2MKN + 2MKb", "l2": "inputs larger than L2 (X alone exceeds 126 MB); no flush between steps",
-                       "kernel": ops.kernel_info(lib)["oft"]},
+                       "route": plan["path"], "kernel": ops.kernel_info(lib)["gemm_half_tn" if two else "oft"]},
             "roofline": {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak,
                          "peak_source": f"{peaks['source']} bf16 {'sustained' if timed_s >= 2.0 else 'burst'} (cuBLAS matmul on this pool)",
-                         "traffic": (NCU_TRAFFIC_BYTES.get(workload) if world == 1 else None), "frac_of_nominal_fp16": achieved / NOMINAL_FP16_TFLOPS,
-                         "kernel": "oft_kernel", "launch_ms": ms_local},
+                         "traffic": (NCU_TRAFFIC_BYTES.get((workload, plan["path"])) if world == 1 else None),
+                         "frac_of_nominal_fp16": achieved / NOMINAL_FP16_TFLOPS,
+                         "kernel": "gemm2_kernel (GEMM pass of the two-pass route)" if two else "oft2_kernel", "launch_ms": gemm_ms},
             "e2e": {"value": total_flops / e2e_s * 1e-12, "unit": "TFLOP/s", "h2d_bytes_per_step": int(th[0].item()),
                     "d2h_bytes_per_step": int(th[1].item()), "ms_per_step": e2e_s * 1e3, "steps": args.e2e_steps,
                     "api": "b200_oft_tn_f16_host (pinned host buffers, synchronous)", "matches_device_path": same},
-            "gpu_launches": args.steps * world, "clocks": clocks,
+            "gpu_launches": args.steps * world * plan["kernel_launches"], "clocks": clocks,
         }
+        if passes is not None:
+            line["passes"] = passes
         if allgather_ms is not None:
             line["allgather_y_ms"] = allgather_ms
         if world == 1 and workload == DEFAULT_WORKLOAD:

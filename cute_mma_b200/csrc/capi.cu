@@ -585,6 +585,45 @@ int b200_oft_tn_f16(int m, int n, int k, int group_size, int reconn_sz, const vo
   return oft_dispatch(m, n, k, group_size, reconn_sz, A, ldA, B, ldB, R, ldR, C, ldC, static_cast<cudaStream_t>(stream));
 }
 
+int b200_rotate_f16(int m, int k, int reconn_sz, const void* A, int ldA, const void* R, int ldR, void* XR, int ldX, void* stream_v) {
+  g_err.clear();
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
+  if (m < 0 || k < 0 || reconn_sz <= 0) return fail(B200_EINVAL, "bad rotate sizes (m=%d k=%d reconn_sz=%d)", m, k, reconn_sz);
+  if (k % reconn_sz != 0) return fail(B200_EINVAL, "k=%d is not a multiple of reconn_sz=%d", k, reconn_sz);
+  if (m > 0 && k > 0 && (!A || !R || !XR)) return fail(B200_EINVAL, "A, R or XR is null");
+  if (ldX < k) return fail(B200_EINVAL, "ldX=%d smaller than k=%d (XR is row-major)", ldX, k);
+  if (m == 0 || k == 0) return B200_OK;
+  DeviceState* st;
+  if (int rc = device_state(&st)) return rc;
+  switch (reconn_sz) {
+    case 8: {
+      void* rx = nullptr;
+      CUDA_TRY(cudaMallocFromPoolAsync(&rx, r8_bytes(1, k), st->pool, stream));
+      int rc = expand_r8(R, ldR, rx, 1, k, stream);
+      if (rc == B200_OK) rc = launch_xr<16>(m, k, A, ldA, rx, static_cast<int>(r8_ld(k)), XR, ldX, stream, st);
+      cudaFreeAsync(rx, stream);
+      return rc;
+    }
+    case 16: return launch_xr<16>(m, k, A, ldA, R, ldR, XR, ldX, stream, st);
+    case 32: return launch_xr<32>(m, k, A, ldA, R, ldR, XR, ldX, stream, st);
+    case 64: return launch_xr<64>(m, k, A, ldA, R, ldR, XR, ldX, stream, st);
+    case 128: return launch_xr<128>(m, k, A, ldA, R, ldR, XR, ldX, stream, st);
+    default: return fail(B200_EUNSUPPORTED, "reconn_sz=%d not compiled in (8, 16, 32, 64, 128)", reconn_sz);
+  }
+}
+
+int b200_oft_plan(int m, int n, int k, int group_size, int reconn_sz, int* path, int* kernel_launches) {
+  g_err.clear();
+  if (m <= 0 || n <= 0 || k <= 0 || group_size <= 0 || reconn_sz <= 0 || n % group_size != 0 || k % reconn_sz != 0)
+    return fail(B200_EINVAL, "bad plan arguments (m=%d n=%d k=%d group_size=%d reconn_sz=%d)", m, n, k, group_size, reconn_sz);
+  DeviceState* st;
+  if (int rc = device_state(&st)) return rc;
+  const bool two = prefer_two_pass(m, k, group_size, reconn_sz == 8 ? 16 : reconn_sz, st);
+  if (path) *path = two ? 2 : 1;
+  if (kernel_launches) *kernel_launches = (two ? 2 * (n / group_size) : 1) + (reconn_sz == 8 ? 1 : 0);
+  return B200_OK;
+}
+
 int b200_oft_tn_f16_two_pass(int m, int n, int k, int group_size, int reconn_sz, const void* A, int ldA, const void* B, int ldB,
                              const void* R, int ldR, void* C, int ldC, void* stream) {
   g_oft_path = 2;

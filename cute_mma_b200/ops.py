@@ -23,7 +23,7 @@ OK, EINVAL, EUNSUPPORTED, ECUDA, EDEVICE = 0, 1, 2, 3, 4
 
 # every symbol include/cute_mma_b200.h declares
 SYMBOLS = (
-    "b200_oft_tn_f16", "b200_oft_tn_f16_two_pass", "b200_oft_tn_f16_host", "b200_oft_tn_f16_static", "b200_transform_weight_f16", "b200_oft_tn_f16_a_rw", "b200_gemm_tn_f16", "b200_gemm_nt_f16", "b200_gemm_tn_tf32",
+    "b200_oft_tn_f16", "b200_oft_tn_f16_two_pass", "b200_rotate_f16", "b200_oft_plan", "b200_oft_tn_f16_host", "b200_oft_tn_f16_static", "b200_transform_weight_f16", "b200_oft_tn_f16_a_rw", "b200_gemm_tn_f16", "b200_gemm_nt_f16", "b200_gemm_tn_tf32",
     "b200_gemm_nt_tf32", "b200_gemm", "b200_shard_range", "b200_tile_coord", "b200_device_status", "b200_selftest_wait_timeout", "b200_wait_profile", "b200_kernel_info",
     "b200_last_error", "b200_shutdown",
 )
@@ -56,6 +56,8 @@ def load_library(path: str | None = None):
     lib.b200_oft_tn_f16.argtypes = [i, i, i, i, i, vp, i, vp, i, vp, i, vp, i, vp]
     lib.b200_oft_tn_f16_static.argtypes = [i, i, i, i, i, vp, i, vp, i, vp, i, vp, i, vp]
     lib.b200_oft_tn_f16_two_pass.argtypes = [i, i, i, i, i, vp, i, vp, i, vp, i, vp, i, vp]
+    lib.b200_rotate_f16.argtypes = [i, i, i, vp, i, vp, i, vp, i, vp]
+    lib.b200_oft_plan.argtypes = [i, i, i, i, i, ctypes.POINTER(i), ctypes.POINTER(i)]
     lib.b200_oft_tn_f16_a_rw.argtypes = [i, i, i, i, i, vp, i, vp, i, vp, i, vp, i, vp]
     lib.b200_transform_weight_f16.argtypes = [i, i, i, i, vp, i, vp, i, vp, i, vp]
     lib.b200_oft_tn_f16_host.argtypes = [i, i, i, i, i, vp, i, vp, i, vp, i, vp, i]
@@ -114,6 +116,20 @@ def oft_tn_two_pass(m, n, k, A, ldA, B, ldB, R, ldR, C, ldC, stream=None, *, gro
     lib = lib or load_library()
     gs = n if group_size is None else group_size
     _check(lib, lib.b200_oft_tn_f16_two_pass(m, n, k, gs, reconn_sz, _ptr(A), ldA, _ptr(B), ldB, _ptr(R), ldR, _ptr(C), ldC, _stream(stream)))
+
+
+def rotate(m, k, A, ldA, R, ldR, XR, ldX, stream=None, *, reconn_sz=8, lib=None) -> None:
+    """XR[m,k] = half(A . blockdiag(R^T)) for one N-group's R: the first pass of the two-pass route."""
+    lib = lib or load_library()
+    _check(lib, lib.b200_rotate_f16(m, k, reconn_sz, _ptr(A), ldA, _ptr(R), ldR, _ptr(XR), ldX, _stream(stream)))
+
+
+def oft_plan(m, n, k, *, group_size=None, reconn_sz=8, lib=None) -> dict:
+    """{'path': 'fused' | 'two_pass', 'kernel_launches': launches of the library's kernels per oft_tn call}."""
+    lib = lib or load_library()
+    path, launches = ctypes.c_int(0), ctypes.c_int(0)
+    _check(lib, lib.b200_oft_plan(m, n, k, n if group_size is None else group_size, reconn_sz, ctypes.byref(path), ctypes.byref(launches)))
+    return {"path": "two_pass" if path.value == 2 else "fused", "kernel_launches": launches.value}
 
 
 def oft_tn_static(m, n, k, A, ldA, B, ldB, R, ldR, C, ldC, stream=None, *, group_size=None, reconn_sz=8, lib=None) -> None:

@@ -41,6 +41,17 @@ int b200_oft_tn_f16(int m, int n, int k, int group_size, int reconn_sz,
                     const void* A, int ldA, const void* B, int ldB, const void* R, int ldR,
                     void* C, int ldC, void* stream);
 
+/* Rotation alone: XR[m][k] (row-major, ld = ldX, fp16) = half(A . blockdiag(R_kb^T)), R = the reconn_sz stored
+ * rows of ONE N-group (see b200_oft_tn_f16 for the stored layout), fp32 accumulation, one rounding to fp16.
+ * The first pass of b200_oft_tn_f16_two_pass; replaces the batched cublasHgemmStridedBatched that forms d_AR
+ * in the reference's cuBLAS comparator (cublas_oft.hpp:69-81). */
+int b200_rotate_f16(int m, int k, int reconn_sz, const void* A, int ldA, const void* R, int ldR,
+                    void* XR, int ldX, void* stream);
+
+/* Which route b200_oft_tn_f16 takes for this problem on the current device (*path: 1 fused kernel, 2 rotation
+ * pass + GEMM) and how many of the library's kernels one call launches.  No counterpart in the reference. */
+int b200_oft_plan(int m, int n, int k, int group_size, int reconn_sz, int* path, int* kernel_launches);
+
 /* The same product in two passes: X.R (rounded to fp16, as above) is written once to device scratch of
  * m * k * 2 bytes (stream-ordered on `stream`, from the pool the library keeps until b200_shutdown) and
  * the plain fp16 GEMM runs on it, group by group.  b200_oft_tn_f16 takes this path by itself when its
