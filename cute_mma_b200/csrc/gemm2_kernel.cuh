@@ -114,6 +114,10 @@ gemm2_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__
         for (int ks = 0; ks < k_steps; ++ks, ++it) {
           const int s = it % T::kStages;
           if (!(ok = mbar_wait(empty_bar(s), ((it / T::kStages) & 1) ^ 1, ctx, 1))) break;
+#ifdef B200_DEBUG_NO_TMA  // timing experiment only: the ring is never filled, results are garbage
+          if (rank == 0) mbar_arrive(full_bar(s));
+          continue;
+#endif
           if (rank == 0) mbar_expect_tx(full_bar(s), 2 * T::kStageBytes);  // both CTAs' bytes land on this barrier
           const uint32_t a_dst = smem_base + s * T::kStageBytes, b_dst = a_dst + T::kABytes;
           const int k0 = ks * T::kBK;
@@ -147,40 +151,61 @@ gemm2_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__
   } else if (warp == 1) {
     // ------------------------------------------------------------------ MMA issuer (leader CTA only)
     if (lane == 0 && rank == 0) {
+      // The issuing thread is on the critical path: measured with in-kernel cycle counters, every instruction
+      // it executes between two MMAs shows up as idle time of the tensor pipe (a look at the next stage's
+      // barrier whose address had to be computed: 512 -> 552 cycles per stage).  The ring is therefore walked
+      // in a loop unrolled over its stages, so that every barrier address, parity and descriptor offset is a
+      // constant plus a base register, and the tiles are flattened into one stream of K steps.
       constexpr uint32_t idesc = umma_idesc(T::kFmt, T::kAMn, T::kBMn, 2 * T::kBM, T::kBN);
       constexpr uint32_t a_adv = T::kAMn ? T::kUmmaK * 128 : 32, b_adv = T::kBMn ? T::kUmmaK * 128 : 32;
       constexpr uint32_t a_lbo = T::kAMn ? T::kBK * 128 : 16, b_lbo = T::kBMn ? T::kBK * 128 : 16;
-      uint32_t it = 0, tcount = 0;
-      bool ok = true, have_full = false;
       const uint64_t a_desc0 = umma_desc_sw128(smem_base, a_lbo, T::kA32Atom ? 512 : 1024, T::kA32Atom ? 1 : 2);
       const uint64_t b_desc0 = umma_desc_sw128(smem_base + T::kABytes, b_lbo, T::kB32Atom ? 512 : 1024, T::kB32Atom ? 1 : 2);
-      for (unsigned tile = pair; ok && tile < num_tiles; tile += num_pairs, ++tcount) {
-        const int a = tcount % T::kAccBufs;
-        if (!(ok = mbar_wait(accempty_bar(a), ((tcount / T::kAccBufs) & 1) ^ 1, ctx, 2))) break;
-        const uint32_t d_tmem = tmem_base + a * T::kBN;
-        const bool last_tile = tile + num_pairs >= num_tiles;
-        for (int ks = 0; ks < k_steps; ++ks, ++it) {
-          const int s = it % T::kStages;
-          if (!have_full && !(ok = mbar_wait(full_bar(s), (it / T::kStages) & 1, ctx, 3))) break;
+      unsigned my_tiles = 0;
+      if (pair < num_tiles) my_tiles = (num_tiles - pair + num_pairs - 1) / num_pairs;
+      const uint32_t total = my_tiles * static_cast<uint32_t>(k_steps);
+      const uint32_t full0 = full_bar(0), empty0 = empty_bar(0);
+      uint32_t phase = 0, tcount = 0, d_tmem = tmem_base;
+      int ks = 0;
+      bool ok = true, have_full = false;
+#ifdef B200_PROFILE_WAITS
+      const long long issue_c0 = clock64();
+#endif
+      for (uint32_t base = 0; ok && base < total; base += T::kStages) {
+#pragma unroll
+        for (int s = 0; s < T::kStages; ++s) {
+          if (base + s >= total) break;
+          if (ks == 0) {  // first K step of a tile: its accumulator must have been drained by the epilogue
+            const int a = tcount % T::kAccBufs;
+            if (!(ok = mbar_wait(accempty_bar(a), ((tcount / T::kAccBufs) & 1) ^ 1, ctx, 2))) break;
+            d_tmem = tmem_base + a * T::kBN;
+          }
+          if (!have_full && !(ok = mbar_wait(full0 + 8 * s, phase, ctx, 3))) break;
           tc_fence_after();
-          const uint64_t a_desc = a_desc0 + static_cast<uint64_t>(s * (T::kStageBytes >> 4));
-          const uint64_t b_desc = b_desc0 + static_cast<uint64_t>(s * (T::kStageBytes >> 4));
 #pragma unroll
           for (int kk = 0; kk < T::kBK / T::kUmmaK; ++kk) {
-            if (kk == (T::kBK / T::kUmmaK) / 2) {
-              const bool more = !(last_tile && ks + 1 == k_steps);
-              have_full = more && mbar_test_wait(full_bar((it + 1) % T::kStages), ((it + 1) / T::kStages) & 1);
-            }
+            if (kk == (T::kBK / T::kUmmaK) / 2)  // is the next stage there already?  (never waits; past the end it looks at a barrier nobody completes)
+              have_full = mbar_test_wait(full0 + 8 * ((s + 1) % T::kStages), s + 1 == T::kStages ? (phase ^ 1) : phase);
             const uint32_t acc = (ks > 0 || kk > 0) ? 1u : 0u;
-            if constexpr (T::kFmt == kFmtF16)
-              umma_f16_ss_pair(d_tmem, a_desc + ((kk * a_adv) >> 4), b_desc + ((kk * b_adv) >> 4), idesc, acc);
-            else
-              umma_tf32_ss_pair(d_tmem, a_desc + ((kk * a_adv) >> 4), b_desc + ((kk * b_adv) >> 4), idesc, acc);
+            const uint64_t a_desc = a_desc0 + static_cast<uint64_t>((s * T::kStageBytes + kk * a_adv) >> 4);
+            const uint64_t b_desc = b_desc0 + static_cast<uint64_t>((s * T::kStageBytes + kk * b_adv) >> 4);
+            if constexpr (T::kFmt == kFmtF16) umma_f16_ss_pair(d_tmem, a_desc, b_desc, idesc, acc);
+            else umma_tf32_ss_pair(d_tmem, a_desc, b_desc, idesc, acc);
           }
-          umma_commit_pair(empty_bar(s), 3);  // frees the stage in both CTAs
+          umma_commit_pair(empty0 + 8 * s, 3);  // frees the stage in both CTAs
+          if (++ks == k_steps) {
+            umma_commit_pair(accfull_bar(tcount % T::kAccBufs), 3);
+            ks = 0;
+            ++tcount;
+          }
         }
-        if (ok) umma_commit_pair(accfull_bar(a), 3);
+        phase ^= 1;
       }
+#ifdef B200_PROFILE_WAITS  // site 62: cycles the issuing thread spent from its first MMA to its last commit
+      ctx.prof_cycles[6] += static_cast<unsigned long long>(clock64() - issue_c0);
+      ctx.prof_count[6] += 1u;
+      ctx.prof_site[6] = 62;
+#endif
     }
     __syncwarp();
   } else {
@@ -197,6 +222,10 @@ gemm2_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__
       tc_fence_after();
       const int row = tm * 2 * T::kBM + rank * T::kBM + quad * 32 + lane;
       const uint32_t t_row = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + a * T::kBN;
+#ifdef B200_EXP_NO_EPI  // timing experiment: the accumulator is never read or stored
+      (void)row; (void)t_row; (void)C; (void)tm; (void)tn;
+      if (false)
+#endif
 #pragma unroll 1
       for (int c = 0; c < T::kBN / 32; ++c) {
         uint32_t v[32];
