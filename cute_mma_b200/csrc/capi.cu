@@ -307,14 +307,15 @@ int launch_oft_gt(int m, int n, int k, int group_size, const void* A, int ldA, c
 template <int kB>
 int launch_xr(int m, int k, const void* A, int ldA, const void* Rg, int ldR, void* XR, long long ldX, cudaStream_t stream, DeviceState* st) {
   using T = XrTraits<kB, 6>;
-  CUtensorMap ma, mr;
+  CUtensorMap ma, mr, mx;
   if (int rc = make_map(&ma, A, 2, k, m, ldA, T::kBK, T::kBM, "A")) return rc;
   if (int rc = make_map(&mr, Rg, 2, k, kB, ldR, T::kBK, kB, "R")) return rc;
-  XrArgs args{m, k, static_cast<__half*>(XR), ldX, st->status};
+  if (int rc = make_map(&mx, XR, 2, k, m, ldX, T::kBK, T::kBM, "XR")) return rc;  // tile stores of (128 x 64) slices
+  XrArgs args{m, k, st->status};
   const long long units = static_cast<long long>((m + T::kBM - 1) / T::kBM) * ((k + T::kUnitK - 1) / T::kUnitK);
   auto kernel = xr_kernel<T>;
   if (int rc = opt_in_smem(kernel, T::kSmemBytes)) return rc;
-  kernel<<<static_cast<int>(units < st->sm_count ? units : st->sm_count), T::kThreads, T::kSmemBytes, stream>>>(ma, mr, args);
+  kernel<<<static_cast<int>(units < st->sm_count ? units : st->sm_count), T::kThreads, T::kSmemBytes, stream>>>(ma, mr, mx, args);
   CUDA_TRY(cudaGetLastError());
   return B200_OK;
 }

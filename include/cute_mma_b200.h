@@ -43,6 +43,7 @@ int b200_oft_tn_f16(int m, int n, int k, int group_size, int reconn_sz,
 
 /* Rotation alone: XR[m][k] (row-major, ld = ldX, fp16) = half(A . blockdiag(R_kb^T)), R = the reconn_sz stored
  * rows of ONE N-group (see b200_oft_tn_f16 for the stored layout), fp32 accumulation, one rounding to fp16.
+ * A, R and XR: 16-byte aligned, leading dimensions multiples of 8 elements (TMA tile loads and stores).
  * The first pass of b200_oft_tn_f16_two_pass; replaces the batched cublasHgemmStridedBatched that forms d_AR
  * in the reference's cuBLAS comparator (cublas_oft.hpp:69-81). */
 int b200_rotate_f16(int m, int k, int reconn_sz, const void* A, int ldA, const void* R, int ldR,
