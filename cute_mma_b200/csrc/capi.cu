@@ -56,7 +56,8 @@ struct DeviceState {
   int* status = nullptr;            // 4 ints, zeroed; kernels record a timed-out wait here
   void* stage[4] = {nullptr, nullptr, nullptr, nullptr};  // staging of the host-buffer entry point
   size_t stage_bytes[4] = {0, 0, 0, 0};
-  cudaStream_t host_stream = nullptr;
+  cudaStream_t host_stream = nullptr;  // compute stream of the host-buffer entry point
+  cudaStream_t in_stream = nullptr, out_stream = nullptr;  // its host-to-device and device-to-host copy streams
   cudaMemPool_t pool = nullptr;     // stream-ordered scratch (expanded R, transformed weight); keeps its memory between calls
 };
 // workspace layout: kStatusInts ints of status, then 2 * kWaitSites 64-bit wait-profile counters
@@ -644,21 +645,60 @@ int b200_oft_tn_f16_host(int m, int n, int k, int group_size, int reconn_sz, con
   if (int rc = device_state(&st)) return rc;
   std::lock_guard<std::mutex> lock(g_host_mu);
   if (!st->host_stream) CUDA_TRY(cudaStreamCreateWithFlags(&st->host_stream, cudaStreamNonBlocking));
-  cudaStream_t s = st->host_stream;
+  if (!st->in_stream) CUDA_TRY(cudaStreamCreateWithFlags(&st->in_stream, cudaStreamNonBlocking));
+  if (!st->out_stream) CUDA_TRY(cudaStreamCreateWithFlags(&st->out_stream, cudaStreamNonBlocking));
+  cudaStream_t s = st->host_stream, s_in = st->in_stream, s_out = st->out_stream;
   const int r_rows = (n / group_size) * reconn_sz;
   const int kp = (k + 7) & ~7, np = (n + 7) & ~7;  // device copies are packed with 16-byte aligned rows
   if (int rc = stage_reserve(st, 0, static_cast<size_t>(m) * kp * 2 + 16)) return rc;
   if (int rc = stage_reserve(st, 1, static_cast<size_t>(n) * kp * 2 + 16)) return rc;
   if (int rc = stage_reserve(st, 2, static_cast<size_t>(r_rows) * kp * 2 + 16)) return rc;
   if (int rc = stage_reserve(st, 3, static_cast<size_t>(m) * np * 2 + 16)) return rc;
-  if (k > 0) {
-    CUDA_TRY(cudaMemcpy2DAsync(st->stage[0], kp * 2, A, static_cast<size_t>(ldA) * 2, static_cast<size_t>(k) * 2, m, cudaMemcpyHostToDevice, s));
-    CUDA_TRY(cudaMemcpy2DAsync(st->stage[1], kp * 2, B, static_cast<size_t>(ldB) * 2, static_cast<size_t>(k) * 2, n, cudaMemcpyHostToDevice, s));
-    CUDA_TRY(cudaMemcpy2DAsync(st->stage[2], kp * 2, R, static_cast<size_t>(ldR) * 2, static_cast<size_t>(k) * 2, r_rows, cudaMemcpyHostToDevice, s));
+  // Rows of X go up, are multiplied and come back chunk by chunk on three streams, so that the upload of chunk
+  // i + 1, the product of chunk i and the download of chunk i - 1 overlap (the link is full duplex and the
+  // download of Y is the longest leg: 3.76 GB against 1.55 GB up at M 65536, K 8192, N 28672).  W and R go up
+  // first.  Results do not depend on the chunking: a row of Y only ever sees its own row of X.
+  constexpr int kMaxChunks = 16;
+  int chunk_rows = ((m + kMaxChunks - 1) / kMaxChunks + 255) & ~255;
+  if (chunk_rows < 2048) chunk_rows = 2048;
+  const int chunks = (m + chunk_rows - 1) / chunk_rows;
+  cudaEvent_t up[kMaxChunks + 1] = {}, done[kMaxChunks] = {};
+  int rc = B200_OK;
+  auto check = [&](cudaError_t e, const char* what) {
+    if (e != cudaSuccess && rc == B200_OK) rc = fail(B200_ECUDA, "%s: %s", what, cudaGetErrorString(e));
+    return e == cudaSuccess;
+  };
+  for (int i = 0; i <= chunks && rc == B200_OK; ++i) check(cudaEventCreateWithFlags(&up[i], cudaEventDisableTiming), "cudaEventCreate");
+  for (int i = 0; i < chunks && rc == B200_OK; ++i) check(cudaEventCreateWithFlags(&done[i], cudaEventDisableTiming), "cudaEventCreate");
+  if (rc == B200_OK && k > 0) {
+    check(cudaMemcpy2DAsync(st->stage[1], kp * 2, B, static_cast<size_t>(ldB) * 2, static_cast<size_t>(k) * 2, n, cudaMemcpyHostToDevice, s_in), "copy of B");
+    check(cudaMemcpy2DAsync(st->stage[2], kp * 2, R, static_cast<size_t>(ldR) * 2, static_cast<size_t>(k) * 2, r_rows, cudaMemcpyHostToDevice, s_in), "copy of R");
   }
-  if (int rc = oft_dispatch(m, n, k, group_size, reconn_sz, st->stage[0], kp, st->stage[1], kp, st->stage[2], kp, st->stage[3], np, s)) return rc;
-  CUDA_TRY(cudaMemcpy2DAsync(C, static_cast<size_t>(ldC) * 2, st->stage[3], np * 2, static_cast<size_t>(n) * 2, m, cudaMemcpyDeviceToHost, s));
-  CUDA_TRY(cudaStreamSynchronize(s));
+  if (rc == B200_OK) check(cudaEventRecord(up[chunks], s_in), "cudaEventRecord");
+  if (rc == B200_OK) check(cudaStreamWaitEvent(s, up[chunks], 0), "cudaStreamWaitEvent");
+  for (int i = 0; i < chunks && rc == B200_OK; ++i) {
+    const int r0 = i * chunk_rows, rows = (m - r0) < chunk_rows ? (m - r0) : chunk_rows;
+    __half* dA = static_cast<__half*>(st->stage[0]) + static_cast<size_t>(r0) * kp;
+    __half* dC = static_cast<__half*>(st->stage[3]) + static_cast<size_t>(r0) * np;
+    if (k > 0)
+      check(cudaMemcpy2DAsync(dA, kp * 2, static_cast<const __half*>(A) + static_cast<size_t>(r0) * ldA, static_cast<size_t>(ldA) * 2,
+                              static_cast<size_t>(k) * 2, rows, cudaMemcpyHostToDevice, s_in), "copy of A");
+    if (rc == B200_OK) check(cudaEventRecord(up[i], s_in), "cudaEventRecord");
+    if (rc == B200_OK) check(cudaStreamWaitEvent(s, up[i], 0), "cudaStreamWaitEvent");
+    if (rc == B200_OK) rc = oft_dispatch(rows, n, k, group_size, reconn_sz, dA, kp, st->stage[1], kp, st->stage[2], kp, dC, np, s);
+    if (rc == B200_OK) check(cudaEventRecord(done[i], s), "cudaEventRecord");
+    if (rc == B200_OK) check(cudaStreamWaitEvent(s_out, done[i], 0), "cudaStreamWaitEvent");
+    if (rc == B200_OK)
+      check(cudaMemcpy2DAsync(static_cast<__half*>(C) + static_cast<size_t>(r0) * ldC, static_cast<size_t>(ldC) * 2, dC, np * 2,
+                              static_cast<size_t>(n) * 2, rows, cudaMemcpyDeviceToHost, s_out), "copy of C");
+  }
+  // everything queued is drained before the staging buffers may be reused, also after an error
+  const std::string keep = g_err;
+  cudaError_t e1 = cudaStreamSynchronize(s_in), e2 = cudaStreamSynchronize(s), e3 = cudaStreamSynchronize(s_out);
+  for (int i = 0; i <= chunks; ++i) if (up[i]) cudaEventDestroy(up[i]);
+  for (int i = 0; i < chunks; ++i) if (done[i]) cudaEventDestroy(done[i]);
+  if (rc != B200_OK) { g_err = keep; return rc; }
+  if (!check(e1, "host-to-device stream") || !check(e2, "compute stream") || !check(e3, "device-to-host stream")) return rc;
   return B200_OK;
 }
 
@@ -818,6 +858,8 @@ int b200_shutdown(void) {
     cudaFree(st.status);
     for (int i = 0; i < 4; ++i) cudaFree(st.stage[i]);
     if (st.host_stream) cudaStreamDestroy(st.host_stream);
+    if (st.in_stream) cudaStreamDestroy(st.in_stream);
+    if (st.out_stream) cudaStreamDestroy(st.out_stream);
     if (st.pool) cudaMemPoolDestroy(st.pool);
     st = DeviceState{};
   }

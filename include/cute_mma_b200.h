@@ -64,9 +64,11 @@ int b200_oft_tn_f16_two_pass(int m, int n, int k, int group_size, int reconn_sz,
                              const void* A, int ldA, const void* B, int ldB, const void* R, int ldR,
                              void* C, int ldC, void* stream);
 
-/* Same product with HOST buffers: copies A, B, R to the device, runs the kernel, copies C back and
- * synchronises before returning.  Device staging buffers are owned and reused by the library.
- * This is the call the end-to-end figure of bench.py times. */
+/* Same product with HOST buffers: copies B and R to the device, then A up, the product and C back in up to
+ * 16 row chunks on three streams (upload, product and download of successive chunks overlap), and
+ * synchronises before returning.  Pinned host memory is needed for the overlap (pageable memory works, the
+ * copies then serialise).  Device staging buffers and streams are owned and reused by the library; calls
+ * are serialised.  This is the call the end-to-end figure of bench.py times. */
 int b200_oft_tn_f16_host(int m, int n, int k, int group_size, int reconn_sz,
                          const void* A, int ldA, const void* B, int ldB, const void* R, int ldR,
                          void* C, int ldC);
