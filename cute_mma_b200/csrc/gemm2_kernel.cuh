@@ -122,7 +122,7 @@ gemm2_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__
           const uint32_t a_dst = smem_base + s * T::kStageBytes, b_dst = a_dst + T::kABytes;
           const int k0 = ks * T::kBK;
           if constexpr (!T::kAMn) {
-            tma_load_2d_pair(a_dst, &tmap_a, full_bar(s), k0, m0);
+            tma_load_2d_pair_hint(a_dst, &tmap_a, full_bar(s), k0, m0, args.hint_a);
           } else {
             if (args.a3d) {
               tma_load_3d_pair(a_dst, &tmap_a, full_bar(s), 0, k0, m0 / T::kChunk);
@@ -133,7 +133,7 @@ gemm2_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__
             }
           }
           if constexpr (!T::kBMn) {
-            tma_load_2d_pair(b_dst, &tmap_b, full_bar(s), k0, n0);
+            tma_load_2d_pair_hint(b_dst, &tmap_b, full_bar(s), k0, n0, args.hint_b);
           } else {
             if (args.b3d) {
               tma_load_3d_pair(b_dst, &tmap_b, full_bar(s), 0, k0, n0 / T::kChunk);

@@ -49,6 +49,7 @@ struct GemmArgs {
   int raster;  // 0: z-curve tile order; g > 0: bands of g tile rows
   int tile_sync;  // pair kernel: producers of all CTAs start each tile round together (status[4..5] are the counters)
   int a3d, b3d;  // MN-major operand described by a 3-D map (chunk, K, chunk index): one copy per tile instead of one per chunk
+  unsigned long long hint_a, hint_b;  // L2 eviction priority of the K-major tile loads of A and B (pair kernel)
 };
 
 template <class T>
