@@ -43,9 +43,10 @@ NCU_TRAFFIC_BYTES = {
     # fused kernel, per launch at N = 1, one-pass counters on the full workload: read 29.2 GB + write 5.7 GB
     # against 5.3 GB algorithmic (every wave of 74 tiles re-reads its panels of X and W once)
     ("oft_large_m65536_k8192_n28672_b128", "fused"): 34.94e9,
-    # two-pass route, GEMM pass (gemm2_kernel), same one-pass counters: read 28.05 GB + write 3.75 GB against
-    # 5.3 GB algorithmic; the rotation pass before it moves 1.08 + 1.02 GB, exactly its algorithmic bytes
-    ("oft_large_m65536_k8192_n28672_b128", "two_pass"): 31.80e9,
+    # two-pass route, GEMM pass (gemm2_kernel), same one-pass counters: read 17.86 GB + write 3.72 GB against
+    # 5.3 GB algorithmic (28.05 GB read before the band operand was loaded evict-last and the streaming one
+    # evict-first); the rotation pass before it moves 1.08 + 1.03 GB, its algorithmic bytes
+    ("oft_large_m65536_k8192_n28672_b128", "two_pass"): 21.58e9,
     # ncu --set full capture of the same shape (read 363 MB + write 154 MB; algorithmic 303 MB)
     ("oft_proj_m16384_k4096_n4096_b64", "fused"): 517.2e6,
 }
