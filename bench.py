@@ -219,9 +219,24 @@ def projection_shape_rate(lib, dev, stream):
     torch.cuda.synchronize()
     ms = e0.elapsed_time(e1) / 50
     assert ops.device_status(lib)[0] == 0
+    os.environ["B200_OFT_PATH"] = "1"  # the fused kernel on the same shape
+    try:
+        for _ in range(5):
+            ops.oft_tn(m, n, k, dX, k, dW, k, dR, k, dY, n, stream, reconn_sz=b, lib=lib)
+        torch.cuda.synchronize()
+        e0.record(stream)
+        for _ in range(50):
+            ops.oft_tn(m, n, k, dX, k, dW, k, dR, k, dY, n, stream, reconn_sz=b, lib=lib)
+        e1.record(stream)
+        torch.cuda.synchronize()
+        ms_fused = e0.elapsed_time(e1) / 50
+    finally:
+        del os.environ["B200_OFT_PATH"]
+    assert ops.device_status(lib)[0] == 0
     tf = flops_of(m, k, n, b) / (ms * 1e-3) * 1e-12
     peaks = measured_peaks()
     return {"workload": name, "value": tf, "unit": "TFLOP/s", "ms_per_step": ms, "steps": 50, "route": ops.oft_plan(m, n, k, reconn_sz=b, lib=lib)["path"],
+            "fused_route": {"ms_per_step": ms_fused, "value": flops_of(m, k, n, b) / (ms_fused * 1e-3) * 1e-12, "unit": "TFLOP/s"},
             "frac_of_measured_bf16_burst": tf / peaks["bf16_burst"], "frac_of_nominal_fp16": tf / NOMINAL_FP16_TFLOPS}
 
 
@@ -320,6 +335,30 @@ def run_gpu_arm(args, workload):
         del dXR
         assert ops.device_status(lib)[0] == 0
 
+    # the fused kernel (X.R never leaves the SM) on the same workload, for comparison with the route taken
+    fused = None
+    if plan["path"] == "two_pass":
+        os.environ["B200_OFT_PATH"] = "1"
+        try:
+            fsteps = max(3, min(args.steps, 5))
+            for _ in range(2):
+                step()
+            barrier()
+            f0, f1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            f0.record(stream)
+            for _ in range(fsteps):
+                step()
+            f1.record(stream)
+            barrier()
+            tf_ = torch.tensor([f0.elapsed_time(f1) / fsteps], device=dev, dtype=torch.float64)
+            if world > 1:
+                dist.all_reduce(tf_, op=dist.ReduceOp.MAX)
+            fused = {"ms_per_step": float(tf_.item()), "value": total_flops / (float(tf_.item()) * 1e-3) * 1e-12, "unit": "TFLOP/s", "steps": fsteps,
+                     "kernel": "oft2_kernel (B200_OFT_PATH=1)"}
+        finally:
+            del os.environ["B200_OFT_PATH"]
+        assert ops.device_status(lib)[0] == 0
+
     # optional exchange, timed on its own
     allgather_ms = None
     if args.allgather and world > 1:
@@ -393,6 +432,9 @@ def run_gpu_arm(args, workload):
         }
         if passes is not None:
             line["passes"] = passes
+        if fused is not None:
+            fused["frac_of_measured_bf16_burst"] = fused["value"] / peaks["bf16_burst"]
+            line["fused_route"] = fused
         if allgather_ms is not None:
             line["allgather_y_ms"] = allgather_ms
         if world == 1 and workload == DEFAULT_WORKLOAD:
