@@ -328,13 +328,19 @@ int launch_xr(int m, int k, const void* A, int ldA, const void* Rg, int ldR, voi
   return B200_OK;
 }
 
+constexpr int kNoScratch = -1000;  // internal: no device memory for X.R
+
 template <int kB>
 int oft_two_pass(int m, int n, int k, int group_size, const void* A, int ldA, const void* B, int ldB, const void* R, int ldR,
                  void* C, int ldC, cudaStream_t stream, DeviceState* st) {
   if (!st->pool) return fail(B200_EUNSUPPORTED, "the two-pass path needs the library's scratch pool");
   const long long ldx = (k + 7) & ~7;
   void* xr = nullptr;
-  CUDA_TRY(cudaMallocFromPoolAsync(&xr, static_cast<size_t>(m) * ldx * 2, st->pool, stream));  // stays in the pool until b200_shutdown
+  if (cudaError_t e = cudaMallocFromPoolAsync(&xr, static_cast<size_t>(m) * ldx * 2, st->pool, stream)) {  // stays in the pool until b200_shutdown
+    cudaGetLastError();
+    if (e == cudaErrorMemoryAllocation) return kNoScratch;  // the caller decides: fused kernel, or an error for the explicit entry point
+    return fail(B200_ECUDA, "cudaMallocFromPoolAsync: %s", cudaGetErrorString(e));
+  }
   int rc = B200_OK;
   for (int g = 0; rc == B200_OK && g < n / group_size; ++g) {  // stream order serialises the groups on the one XR buffer
     rc = launch_xr<kB>(m, k, A, ldA, static_cast<const __half*>(R) + static_cast<long long>(g) * kB * ldR, ldR, xr, ldx, stream, st);
@@ -374,7 +380,12 @@ template <int kB>
 int launch_oft(int m, int n, int k, int group_size, const void* A, int ldA, const void* B, int ldB, const void* R, int ldR,
                void* C, int ldC, cudaStream_t stream, DeviceState* st) {
   constexpr int kBN = CurrCompParams::bN;
-  if (prefer_two_pass(m, k, group_size, kB, st)) return oft_two_pass<kB>(m, n, k, group_size, A, ldA, B, ldB, R, ldR, C, ldC, stream, st);
+  if (prefer_two_pass(m, k, group_size, kB, st)) {
+    const int rc = oft_two_pass<kB>(m, n, k, group_size, A, ldA, B, ldB, R, ldR, C, ldC, stream, st);
+    if (rc != kNoScratch) return rc;
+    if (g_oft_path == 2) return fail(B200_ECUDA, "no device memory for the %lld bytes of X.R scratch", static_cast<long long>(m) * ((k + 7) & ~7) * 2);
+    // out of memory for X.R: the fused kernel needs no scratch
+  }
   if (group_size == n || group_size % kBN == 0) return launch_oft_gt<kB, 1>(m, n, k, group_size, A, ldA, B, ldB, R, ldR, C, ldC, stream, st);
   if constexpr (kOftPair && kB <= 64) {
     if (kBN % group_size == 0) {

@@ -308,6 +308,33 @@ def test_oft_large_slab_sampled(lib, cuda):
     _sampled_parity(lib, cuda, 8192, 3584, 8192, 128, "qr", 0.02, 12, seed=5)
 
 
+def test_oft_large_full_size_sampled_and_routes_agree(lib, cuda):
+    """The large configuration whole on one GPU (M 65536, K 8192, N 28672, b 128, QR blocks): sampled rows
+    against the oracle, linearity over the whole output, and the two routes of the library (rotation pass +
+    GEMM, which the cost estimate picks here, and the fused kernel) must return the same bits."""
+    import torch
+
+    m, k, n, b = 65536, 8192, 28672, 128
+    assert ops.oft_plan(m, n, k, reconn_sz=b, lib=lib)["path"] == "two_pass"
+    assert ops.oft_plan(8192, 8192, 8192, group_size=256, reconn_sz=8, lib=lib) == {"path": "fused", "kernel_launches": 2}
+    _sampled_parity(lib, cuda, m, n, k, b, "qr", 0.02, 8, seed=6)
+    g = torch.Generator(device=cuda).manual_seed(6)  # the operands _sampled_parity drew
+    dA = torch.randn((m, k), generator=g, device=cuda, dtype=torch.float32).to(torch.float16)
+    dB = (torch.randn((n, k), generator=g, device=cuda, dtype=torch.float32) * 0.02).to(torch.float16)
+    from cute_mma_b200 import inputs
+    dR = torch.from_numpy(inputs.pack_r(inputs.blocks_qr(1, k // b, b, 6))).to(cuda)
+    c_auto = torch.empty((m, n), dtype=torch.float16, device=cuda)
+    c_fused = torch.empty((m, n), dtype=torch.float16, device=cuda)
+    ops.oft_tn(m, n, k, dA, k, dB, k, dR, k, c_auto, n, reconn_sz=b, lib=lib)
+    os.environ["B200_OFT_PATH"] = "1"
+    try:
+        ops.oft_tn(m, n, k, dA, k, dB, k, dR, k, c_fused, n, reconn_sz=b, lib=lib)
+    finally:
+        del os.environ["B200_OFT_PATH"]
+    assert ops.device_status(lib)[0] == 0
+    assert torch.equal(c_auto.view(torch.int16), c_fused.view(torch.int16))
+
+
 def test_bounded_wait_reports_and_recovers(lib, cuda):
     """A wait that runs out is reported through the status record and leaves the context usable
     (no trap, no fault): the self-test waits 2 ms on a barrier nothing sets."""
