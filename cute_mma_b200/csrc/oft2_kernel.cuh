@@ -17,6 +17,9 @@
 
 namespace b200 {
 
+constexpr int oft_gcd(int a, int b) { return b == 0 ? a : oft_gcd(b, a % b); }
+constexpr int oft_lcm(int a, int b) { return a / oft_gcd(a, b) * b; }
+
 template <int kB_, int kBN_, int kS1_, int kS2_, int kGT_ = 1>
 struct Oft2Traits {
   static constexpr int kB = kB_;
@@ -50,6 +53,15 @@ struct Oft2Traits {
   static_assert(kRHalfBytes % 1024 == 0, "R half-tile must keep the next tile 1024-byte aligned");
   static_assert(kGT == 1 || (kStagesPerUnit == 1 && kGS % 16 == 0 && (kGSHalf * 128) % 1024 == 0), "several groups per tile need b <= 64 and group_size >= 16");
   static constexpr bool kFits = kSmemBytes <= 232448;
+  // Issue loops unrolled over a whole period of (ring slot, XR buffer): every barrier address, parity and
+  // descriptor offset in them is a constant plus a base register.  Used when the tile holds one N-group and
+  // the period is short; otherwise the loops that track slot and phase at run time.  Measured (cycles per 64
+  // columns of K at M 16384, K = N 4096): b 128 926 -> 883, b 32 715 -> 704, but b 64 714 -> 726 (the hand-off
+  // chain MMA1 -> conversion -> MMA2, not the issuing threads' integer work, bounds this kernel), so 64 x 64
+  // blocks keep the run-time loops.
+  static constexpr int kPeriod1 = oft_lcm(kS1, kXrBufs * kStagesPerUnit);
+  static constexpr int kPeriod2 = oft_lcm(kS2, kXrBufs * kStagesPerUnit);
+  static constexpr bool kUnrolledIssue = kGT == 1 && kB != 64 && kPeriod1 <= 24 && kPeriod2 <= 24;
 };
 
 template <class T>
@@ -174,7 +186,8 @@ oft2_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
           for (int gl = 0; gl < T::kGT; ++gl)
             tma_load_2d_pair_hint(ring2 + s * T::kS2Bytes + gl * T::kGSHalf * 128, &tmap_b, full2 + 8 * s, st * T::kBK, n0 + gl * T::kGS, args.hint_b);
         }
-      }      if (ok && args.tile_sync && done_rounds > 0) atomicAdd(args.status + 6 + rank, 1);
+      }
+      if (ok && args.tile_sync && done_rounds > 0) atomicAdd(args.status + 6 + rank, 1);
     }
     __syncwarp();
   } else if (warp == 2) {
@@ -184,50 +197,87 @@ oft2_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
       constexpr uint32_t idesc1 = umma_idesc(kFmtF16, 0, 0, 2 * T::kBM, T::kB);
       const uint64_t a_desc0 = umma_desc_sw128(ring1, 16, 1024), r_desc0 = umma_desc_sw128(ring1 + T::kABytes, 16, 1024);
       const unsigned total_stages = my_tiles * units * T::kStagesPerUnit;
-      int s = 0, xb = 0, su = 0;
-      uint32_t ph_s = 0, ph_xb = 0;
-      bool have_full = false, have_buf = false, ok = true;
-      for (unsigned j = 0; ok && j < total_stages; ++j) {
-        if (!have_full && !(ok = mbar_wait(full1 + 8 * s, ph_s, ctx, 21))) break;
-        const uint64_t a_desc = a_desc0 + static_cast<uint64_t>(s * (T::kS1Bytes >> 4));
-        const bool unit_ends = (su == T::kStagesPerUnit - 1);
-        int s_n = s + 1;
-        uint32_t ph_s_n = ph_s;
-        if (s_n == T::kS1) { s_n = 0; ph_s_n ^= 1; }
+      if constexpr (T::kUnrolledIssue) {
+        constexpr int P = T::kPeriod1, SPU = T::kStagesPerUnit, XB = T::kXrBufs;
+        uint32_t par_s = 0, par_x = 0;  // parities of ring slot 0 / XR buffer 0 at the start of the period
+        bool have_full = false, have_buf = false, ok = true;
+        for (unsigned base = 0; ok && base < total_stages; base += P) {
 #pragma unroll
-        for (int gl = 0; gl < T::kGT; ++gl) {  // one XR per N-group of the tile, all from the same stage of A
-          if (su == 0 && !have_buf && !(ok = mbar_wait(x_empty + 8 * xb, ph_xb ^ 1, ctx, 20))) break;
-          tc_fence_after();
-          const uint32_t d1 = tmem_base + T::kColXr + xb * T::kUnitK;
-          const uint64_t r_desc = r_desc0 + static_cast<uint64_t>((s * T::kS1Bytes + gl * T::kRHalfBytes) >> 4);
-          int xb_n = xb;
-          uint32_t ph_xb_n = ph_xb;
-          if (unit_ends && ++xb_n == T::kXrBufs) { xb_n = 0; ph_xb_n ^= 1; }
+          for (int j = 0; j < P; ++j) {
+            if (base + j >= total_stages) break;
+            const int sl = j % T::kS1, su = j % SPU, xb = (j / SPU) % XB;
+            const uint32_t p_full = par_s ^ ((j / T::kS1) & 1), p_x = par_x ^ (((j / SPU) / XB) & 1);
+            if (su == 0 && !have_buf && !(ok = mbar_wait(x_empty + 8 * xb, p_x ^ 1, ctx, 20))) break;
+            if (!have_full && !(ok = mbar_wait(full1 + 8 * sl, p_full, ctx, 21))) break;
+            tc_fence_after();
+            const uint32_t d1 = tmem_base + T::kColXr + xb * T::kUnitK;
+            const uint64_t a_desc = a_desc0 + static_cast<uint64_t>(sl * (T::kS1Bytes >> 4));
+            const uint64_t r_desc = r_desc0 + static_cast<uint64_t>(sl * (T::kS1Bytes >> 4));
+            const bool unit_ends = (su == SPU - 1);
+            const int jn = j + 1;  // the next stage (jn == P: slot 0 of the next period, whose base parities have flipped)
 #pragma unroll
-          for (int kk = 0; kk < T::kBK / 16; ++kk) {
-            if (kk == 2) {
-              const bool more = (j + 1 < total_stages) || (gl + 1 < T::kGT);
-              if (gl == T::kGT - 1) have_full = (j + 1 < total_stages) && mbar_test_wait(full1 + 8 * s_n, ph_s_n);
-              have_buf = more && unit_ends && mbar_test_wait(x_empty + 8 * xb_n, ph_xb_n ^ 1);
+            for (int kk = 0; kk < T::kBK / 16; ++kk) {
+              if (kk == 2) {
+                have_full = mbar_test_wait(full1 + 8 * (jn % T::kS1), par_s ^ ((jn / T::kS1) & 1));
+                have_buf = unit_ends && mbar_test_wait(x_empty + 8 * ((jn / SPU) % XB), par_x ^ (((jn / SPU) / XB) & 1) ^ 1);
+              }
+              constexpr bool small = T::kB < 64;
+              const int blk = small ? (kk * 16) / T::kB : 0;
+              const uint32_t accum = small ? ((((kk * 16) % T::kB) != 0) ? 1u : 0u) : ((su > 0 || kk > 0) ? 1u : 0u);
+              umma_f16_ss_pair(d1 + blk * T::kB, a_desc + kk * 2, r_desc + kk * 2, idesc1, accum);
             }
-            constexpr bool small = T::kB < 64;
-            const int blk = small ? (kk * 16) / T::kB : 0;
-            const uint32_t accum = small ? ((((kk * 16) % T::kB) != 0) ? 1u : 0u) : ((su > 0 || kk > 0) ? 1u : 0u);
-            umma_f16_ss_pair(d1 + blk * T::kB, a_desc + kk * 2, r_desc + kk * 2, idesc1, accum);
+            umma_commit_pair(empty1 + 8 * sl, 3);
+            if (unit_ends) umma_commit_pair(x_acc + 8 * xb, 3);  // the converters of both CTAs start on their halves
           }
-          if (unit_ends) {
-            umma_commit_pair(x_acc + 8 * xb, 3);  // the converters of both CTAs start on their halves
-            xb = xb_n;
-            ph_xb = ph_xb_n;
-          }
+          par_s ^= (P / T::kS1) & 1;
+          par_x ^= ((P / SPU) / XB) & 1;
         }
-        if (!ok) break;
-        umma_commit_pair(empty1 + 8 * s, 3);
-        s = s_n;
-        ph_s = ph_s_n;
-        su = unit_ends ? 0 : su + 1;
-      }
-    }
+      } else {
+        int s = 0, xb = 0, su = 0;
+        uint32_t ph_s = 0, ph_xb = 0;
+        bool have_full = false, have_buf = false, ok = true;
+        for (unsigned j = 0; ok && j < total_stages; ++j) {
+          if (!have_full && !(ok = mbar_wait(full1 + 8 * s, ph_s, ctx, 21))) break;
+          const uint64_t a_desc = a_desc0 + static_cast<uint64_t>(s * (T::kS1Bytes >> 4));
+          const bool unit_ends = (su == T::kStagesPerUnit - 1);
+          int s_n = s + 1;
+          uint32_t ph_s_n = ph_s;
+          if (s_n == T::kS1) { s_n = 0; ph_s_n ^= 1; }
+  #pragma unroll
+          for (int gl = 0; gl < T::kGT; ++gl) {  // one XR per N-group of the tile, all from the same stage of A
+            if (su == 0 && !have_buf && !(ok = mbar_wait(x_empty + 8 * xb, ph_xb ^ 1, ctx, 20))) break;
+            tc_fence_after();
+            const uint32_t d1 = tmem_base + T::kColXr + xb * T::kUnitK;
+            const uint64_t r_desc = r_desc0 + static_cast<uint64_t>((s * T::kS1Bytes + gl * T::kRHalfBytes) >> 4);
+            int xb_n = xb;
+            uint32_t ph_xb_n = ph_xb;
+            if (unit_ends && ++xb_n == T::kXrBufs) { xb_n = 0; ph_xb_n ^= 1; }
+  #pragma unroll
+            for (int kk = 0; kk < T::kBK / 16; ++kk) {
+              if (kk == 2) {
+                const bool more = (j + 1 < total_stages) || (gl + 1 < T::kGT);
+                if (gl == T::kGT - 1) have_full = (j + 1 < total_stages) && mbar_test_wait(full1 + 8 * s_n, ph_s_n);
+                have_buf = more && unit_ends && mbar_test_wait(x_empty + 8 * xb_n, ph_xb_n ^ 1);
+              }
+              constexpr bool small = T::kB < 64;
+              const int blk = small ? (kk * 16) / T::kB : 0;
+              const uint32_t accum = small ? ((((kk * 16) % T::kB) != 0) ? 1u : 0u) : ((su > 0 || kk > 0) ? 1u : 0u);
+              umma_f16_ss_pair(d1 + blk * T::kB, a_desc + kk * 2, r_desc + kk * 2, idesc1, accum);
+            }
+            if (unit_ends) {
+              umma_commit_pair(x_acc + 8 * xb, 3);  // the converters of both CTAs start on their halves
+              xb = xb_n;
+              ph_xb = ph_xb_n;
+            }
+          }
+          if (!ok) break;
+          umma_commit_pair(empty1 + 8 * s, 3);
+          s = s_n;
+          ph_s = ph_s_n;
+          su = unit_ends ? 0 : su + 1;
+        }
+          }
+}
     __syncwarp();
   } else if (warp == 3) {
     // -------------------------------------------------------------- issuer of MMA2 (leader CTA only)
@@ -236,58 +286,102 @@ oft2_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
       constexpr uint32_t idesc2 = umma_idesc(kFmtF16, 0, 0, 2 * T::kBM, T::kGS);
       const uint64_t b_desc0 = umma_desc_sw128(ring2, 16, 1024);
       const unsigned total_stages = my_tiles * units * T::kStagesPerUnit;
-      int s = 0, xb = 0, ku = 0, su = 0;
-      uint32_t ph_s = 0, ph_xb = 0, ph_acc = 0;
-      bool have_full = false, have_half = false, ok = true;
-      for (unsigned j = 0; ok && j < total_stages; ++j) {
-        if (su == 0 && ku == 0 && !(ok = mbar_wait(acc_empty, ph_acc ^ 1, ctx, 22))) break;
-        if (!have_full && !(ok = mbar_wait(full2 + 8 * s, ph_s, ctx, 24))) break;
-        const bool unit_ends = (su == T::kStagesPerUnit - 1);
-        int s_n = s + 1;
-        uint32_t ph_s_n = ph_s;
-        if (s_n == T::kS2) { s_n = 0; ph_s_n ^= 1; }
-        const int su_n = unit_ends ? 0 : su + 1;
+      if constexpr (T::kUnrolledIssue) {
+        constexpr int P = T::kPeriod2, SPU = T::kStagesPerUnit, XB = T::kXrBufs;
+        uint32_t par_s = 0, par_x = 0, ph_acc = 0;  // parities of ring slot 0 / XR buffer 0 at the start of the period
+        int ku = 0;
+        bool have_full = false, have_half = false, ok = true;
+        for (unsigned base = 0; ok && base < total_stages; base += P) {
 #pragma unroll
-        for (int gl = 0; gl < T::kGT; ++gl) {  // each N-group multiplies its own XR into its own columns of the accumulator
-          if (!have_half && !(ok = mbar_wait(x_half + 8 * (xb * T::kStagesPerUnit + su), ph_xb, ctx, 23))) break;
-          tc_fence_after();
-          const uint32_t a_tmem = tmem_base + T::kColXr + xb * T::kUnitK + su * (T::kBK / 2);
-          const uint64_t b_desc = b_desc0 + static_cast<uint64_t>((s * T::kS2Bytes + gl * T::kGSHalf * 128) >> 4);
-          int xb_n = xb;
-          uint32_t ph_xb_n = ph_xb;
-          if (unit_ends && ++xb_n == T::kXrBufs) { xb_n = 0; ph_xb_n ^= 1; }
+          for (int j = 0; j < P; ++j) {
+            if (base + j >= total_stages) break;
+            const int sl = j % T::kS2, su = j % SPU, xb = (j / SPU) % XB;
+            const uint32_t p_full = par_s ^ ((j / T::kS2) & 1), p_x = par_x ^ (((j / SPU) / XB) & 1);
+            // first stage of a tile: the epilogue must have drained the accumulator
+            if (su == 0 && ku == 0 && !(ok = mbar_wait(acc_empty, ph_acc ^ 1, ctx, 22))) break;
+            if (!have_half && !(ok = mbar_wait(x_half + 8 * (xb * SPU + su), p_x, ctx, 23))) break;
+            if (!have_full && !(ok = mbar_wait(full2 + 8 * sl, p_full, ctx, 24))) break;
+            tc_fence_after();
+            const uint32_t a_tmem = tmem_base + T::kColXr + xb * T::kUnitK + su * (T::kBK / 2);
+            const uint64_t b_desc = b_desc0 + static_cast<uint64_t>(sl * (T::kS2Bytes >> 4));
+            const bool unit_ends = (su == SPU - 1);
+            const int jn = j + 1;  // the next stage (jn == P: the next period, whose base parities have flipped)
 #pragma unroll
-          for (int kk = 0; kk < T::kBK / 16; ++kk) {
-            if (kk == 2) {
-              const bool more = (j + 1 < total_stages) || (gl + 1 < T::kGT);
-              if (gl == T::kGT - 1) have_full = (j + 1 < total_stages) && mbar_test_wait(full2 + 8 * s_n, ph_s_n);
-              have_half = more && mbar_test_wait(x_half + 8 * (xb_n * T::kStagesPerUnit + (T::kGT > 1 ? 0 : su_n)), ph_xb_n);
+            for (int kk = 0; kk < T::kBK / 16; ++kk) {
+              if (kk == 2) {
+                have_full = mbar_test_wait(full2 + 8 * (jn % T::kS2), par_s ^ ((jn / T::kS2) & 1));
+                have_half = mbar_test_wait(x_half + 8 * (((jn / SPU) % XB) * SPU + jn % SPU), par_x ^ (((jn / SPU) / XB) & 1));
+              }
+              const uint32_t accum = (su > 0 || kk > 0) ? 1u : (ku > 0 ? 1u : 0u);
+              umma_f16_ts_pair(tmem_base + T::kColAcc, a_tmem + kk * 8, b_desc + kk * 2, idesc2, accum);
             }
-            const uint32_t accum = (su > 0 || kk > 0) ? 1u : (ku > 0 ? 1u : 0u);
-            umma_f16_ts_pair(tmem_base + T::kColAcc + gl * T::kGS, a_tmem + kk * 8, b_desc + kk * 2, idesc2, accum);
+            umma_commit_pair(empty2 + 8 * sl, 3);
+            if (unit_ends) {
+              umma_commit_pair(x_empty + 8 * xb, 1);  // only the leader's MMA1 issuer waits for this
+              if (++ku == units) {
+                umma_commit_pair(acc_full, 3);
+                ku = 0;
+                ph_acc ^= 1;
+              }
+            }
           }
+          par_s ^= (P / T::kS2) & 1;
+          par_x ^= ((P / SPU) / XB) & 1;
+        }
+      } else {
+        int s = 0, xb = 0, ku = 0, su = 0;
+        uint32_t ph_s = 0, ph_xb = 0, ph_acc = 0;
+        bool have_full = false, have_half = false, ok = true;
+        for (unsigned j = 0; ok && j < total_stages; ++j) {
+          if (su == 0 && ku == 0 && !(ok = mbar_wait(acc_empty, ph_acc ^ 1, ctx, 22))) break;
+          if (!have_full && !(ok = mbar_wait(full2 + 8 * s, ph_s, ctx, 24))) break;
+          const bool unit_ends = (su == T::kStagesPerUnit - 1);
+          int s_n = s + 1;
+          uint32_t ph_s_n = ph_s;
+          if (s_n == T::kS2) { s_n = 0; ph_s_n ^= 1; }
+          const int su_n = unit_ends ? 0 : su + 1;
+  #pragma unroll
+          for (int gl = 0; gl < T::kGT; ++gl) {  // each N-group multiplies its own XR into its own columns of the accumulator
+            if (!have_half && !(ok = mbar_wait(x_half + 8 * (xb * T::kStagesPerUnit + su), ph_xb, ctx, 23))) break;
+            tc_fence_after();
+            const uint32_t a_tmem = tmem_base + T::kColXr + xb * T::kUnitK + su * (T::kBK / 2);
+            const uint64_t b_desc = b_desc0 + static_cast<uint64_t>((s * T::kS2Bytes + gl * T::kGSHalf * 128) >> 4);
+            int xb_n = xb;
+            uint32_t ph_xb_n = ph_xb;
+            if (unit_ends && ++xb_n == T::kXrBufs) { xb_n = 0; ph_xb_n ^= 1; }
+  #pragma unroll
+            for (int kk = 0; kk < T::kBK / 16; ++kk) {
+              if (kk == 2) {
+                const bool more = (j + 1 < total_stages) || (gl + 1 < T::kGT);
+                if (gl == T::kGT - 1) have_full = (j + 1 < total_stages) && mbar_test_wait(full2 + 8 * s_n, ph_s_n);
+                have_half = more && mbar_test_wait(x_half + 8 * (xb_n * T::kStagesPerUnit + (T::kGT > 1 ? 0 : su_n)), ph_xb_n);
+              }
+              const uint32_t accum = (su > 0 || kk > 0) ? 1u : (ku > 0 ? 1u : 0u);
+              umma_f16_ts_pair(tmem_base + T::kColAcc + gl * T::kGS, a_tmem + kk * 8, b_desc + kk * 2, idesc2, accum);
+            }
+            if (unit_ends) {
+              umma_commit_pair(x_empty + 8 * xb, 1);  // only the leader's MMA1 issuer waits for this
+              xb = xb_n;
+              ph_xb = ph_xb_n;
+            }
+          }
+          if (!ok) break;
+          umma_commit_pair(empty2 + 8 * s, 3);
+          if (unit_ends && ku + 1 == units) umma_commit_pair(acc_full, 3);
+          s = s_n;
+          ph_s = ph_s_n;
           if (unit_ends) {
-            umma_commit_pair(x_empty + 8 * xb, 1);  // only the leader's MMA1 issuer waits for this
-            xb = xb_n;
-            ph_xb = ph_xb_n;
+            su = 0;
+            if (++ku == units) {
+              ku = 0;
+              ph_acc ^= 1;
+            }
+          } else {
+            ++su;
           }
         }
-        if (!ok) break;
-        umma_commit_pair(empty2 + 8 * s, 3);
-        if (unit_ends && ku + 1 == units) umma_commit_pair(acc_full, 3);
-        s = s_n;
-        ph_s = ph_s_n;
-        if (unit_ends) {
-          su = 0;
-          if (++ku == units) {
-            ku = 0;
-            ph_acc ^= 1;
           }
-        } else {
-          ++su;
-        }
-      }
-    }
+}
     __syncwarp();
   } else if (warp >= 4 && warp < 8) {
     // -------------------------------------------------------------- converters (both CTAs, own 128 rows)
