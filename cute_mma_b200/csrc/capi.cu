@@ -308,7 +308,7 @@ int launch_oft_gt(int m, int n, int k, int group_size, const void* A, int ldA, c
 
 // ---- two-pass OFT: rotation pass + plain GEMM ---------------------------------------------------------------
 // The fused kernel recomputes X.R for every N tile of a group: per 64 columns of K a pair of SMs spends 726
-// cycles (b <= 64) or 963 cycles (b = 128) where the plain GEMM spends 570.  Writing X.R to memory once
+// cycles (b <= 64) or 880-960 cycles (b = 128) where the plain GEMM spends 530-570.  Writing X.R to memory once
 // (xr_kernel, bound by 4 bytes of traffic per element of X) and running the plain GEMM on it is cheaper as
 // soon as a group spans enough N tiles: measured at M 65536, K 8192, N 28672, b 128: 38.2 ms fused, 26 ms in
 // two passes.  Same arithmetic as the fused kernel: X.R rounded once to fp16, fp32 accumulation of the product.
@@ -369,8 +369,8 @@ bool prefer_two_pass(int m, int k, int group_size, int b, const DeviceState* st)
   // Cycles of one SM pair per (256 x 256 tile, 64 columns of K), measured with in-kernel cycle counters.
   const double units = std::ceil(m / 256.0) * std::ceil(group_size / 256.0) * std::ceil(k / 64.0);
   const double pairs = st->sm_count / 2, hz = 1.4e9;
-  const double fused = units * (b == 128 ? 963.0 : 726.0) / (pairs * hz);
-  const double two = units * 570.0 / (pairs * hz) + 4.0 * m * static_cast<double>(k) / 5.5e12 + 8e-6;
+  const double fused = units * (b == 128 ? 900.0 : 715.0) / (pairs * hz);
+  const double two = units * 545.0 / (pairs * hz) + 4.0 * m * static_cast<double>(k) / 5.5e12 + 8e-6;
   return group_size >= 256 && two < 0.93 * fused;
 }
 
