@@ -433,7 +433,7 @@ def run_gpu_arm(args, workload):
         if passes is not None:
             line["passes"] = passes
         if fused is not None:
-            fused["frac_of_measured_bf16_burst"] = fused["value"] / peaks["bf16_burst"]
+            fused["frac_of_measured_bf16_burst"] = fused["value"] / world / peaks["bf16_burst"]  # per GPU
             line["fused_route"] = fused
         if allgather_ms is not None:
             line["allgather_y_ms"] = allgather_ms
