@@ -177,6 +177,22 @@ int common_dims(int m, int n, int k, const void* A, const void* B, void* C) {
 template <class P, class = void> struct CtasOf { static constexpr int value = 1; };
 template <class P> struct CtasOf<P, decltype((void)P::ctas)> { static constexpr int value = P::ctas; };
 
+// Counters of the cross-CTA phase lock.  Each launch gets its own four, stream-ordered from the library's pool, so
+// that launches on different streams never share them; the entry point that must not allocate uses the four
+// that follow the status record in its static scratch (its calls may not overlap anyway).
+int round_counters(DeviceState* st, cudaStream_t stream, int** out) {
+  if (st->pool) {
+    CUDA_TRY(cudaMallocFromPoolAsync(reinterpret_cast<void**>(out), 4 * sizeof(int), st->pool, stream));
+  } else {
+    *out = st->status + 4;
+  }
+  CUDA_TRY(cudaMemsetAsync(*out, 0, 4 * sizeof(int), stream));
+  return B200_OK;
+}
+void release_round_counters(DeviceState* st, cudaStream_t stream, int* p) {
+  if (st->pool && p) cudaFreeAsync(p, stream);
+}
+
 template <typename TIn, typename TOut, bool kNT, class P>
 int launch_gemm(int m, int n, int k, const void* A, int ldA, const void* B, int ldB, void* C, int ldC, void* stream_v) {
   constexpr bool kPair = CtasOf<P>::value == 2;
@@ -214,7 +230,9 @@ int launch_gemm(int m, int n, int k, const void* A, int ldA, const void* B, int 
   const bool big = kPair && static_cast<long long>(n) * k * static_cast<long long>(sizeof(TIn)) > 3ll * st->l2_bytes;
   int tile_sync = big ? 1 : 0;
   if (const char* e = std::getenv("B200_GEMM_TILE_SYNC")) tile_sync = kPair ? std::atoi(e) : 0;
-  if (tile_sync) CUDA_TRY(cudaMemsetAsync(st->status + 4, 0, 4 * sizeof(int), stream));
+  int* rounds = nullptr;
+  if (tile_sync)
+    if (int rc = round_counters(st, stream, &rounds)) return rc;
   int raster = raster_for(static_cast<long long>(n) * k * sizeof(TIn), false);
   if (big && !std::getenv("B200_RASTER")) raster = 8;
   // With the bands, the band's panel of A is what later waves read again and B streams past once per band:
@@ -224,7 +242,7 @@ int launch_gemm(int m, int n, int k, const void* A, int ldA, const void* B, int 
     auto pick = [](char c) { return c == 'f' ? kL2EvictFirst : (c == 'l' ? kL2EvictLast : kL2EvictNormal); };
     if (e[0] && e[1]) { hint_a = pick(e[0]); hint_b = pick(e[1]); }
   }
-  GemmArgs args{m, n, k, C, ldC, st->status, raster, tile_sync, a3d, b3d, hint_a, hint_b};
+  GemmArgs args{m, n, k, C, ldC, st->status, raster, tile_sync, rounds, a3d, b3d, hint_a, hint_b};
   if constexpr (kPair) {
     auto kernel = gemm2_kernel<T2>;
     if (int rc = opt_in_smem(kernel, T2::kSmemBytes)) return rc;
@@ -238,7 +256,9 @@ int launch_gemm(int m, int n, int k, const void* A, int ldA, const void* B, int 
     const int grid = static_cast<int>(tiles < st->sm_count ? tiles : st->sm_count);
     kernel<<<grid, T1::kThreads, T1::kSmemBytes, stream>>>(ma, mb, args);
   }
-  CUDA_TRY(cudaGetLastError());
+  const cudaError_t launched = cudaGetLastError();
+  release_round_counters(st, stream, rounds);
+  CUDA_TRY(launched);
   return B200_OK;
 }
 
@@ -287,8 +307,10 @@ int launch_oft_gt(int m, int n, int k, int group_size, const void* A, int ldA, c
   // exceeds three times the L2 size.  B200_TILE_SYNC=0/1 overrides.
   int tile_sync = (kOftPair && static_cast<long long>(n) * k * 2 > 3ll * st->l2_bytes) ? 1 : 0;
   if (const char* e = std::getenv("B200_TILE_SYNC")) tile_sync = kOftPair ? std::atoi(e) : 0;
-  if (tile_sync) CUDA_TRY(cudaMemsetAsync(st->status + 4, 0, 4 * sizeof(int), stream));  // the round counters start at zero
-  OftArgs args{m, n, k, group_size, static_cast<__half*>(C), ldC, st->status, raster, hint_a, hint_b, tile_sync};
+  int* rounds = nullptr;
+  if (tile_sync)
+    if (int rc = round_counters(st, stream, &rounds)) return rc;  // this launch's own counters, zeroed in stream order
+  OftArgs args{m, n, k, group_size, static_cast<__half*>(C), ldC, st->status, raster, hint_a, hint_b, tile_sync, rounds};
   const long long tiles = static_cast<long long>((m + kRowsPerCta * T::kBM - 1) / (kRowsPerCta * T::kBM)) * ((n + T::kBN - 1) / T::kBN);
   if constexpr (kOftPair) {
     auto kernel = oft2_kernel<T>;
@@ -301,7 +323,9 @@ int launch_oft_gt(int m, int n, int k, int group_size, const void* A, int ldA, c
     const int grid = static_cast<int>(tiles < st->sm_count ? tiles : st->sm_count);
     kernel<<<grid, T::kThreads, T::kSmemBytes, stream>>>(ma, mr, mb, args);
   }
-  CUDA_TRY(cudaGetLastError());
+  const cudaError_t launched = cudaGetLastError();
+  release_round_counters(st, stream, rounds);
+  CUDA_TRY(launched);
   return B200_OK;
   }
 }

@@ -100,7 +100,7 @@ gemm2_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__
       unsigned done_rounds = 0, sync_target = 0;
       for (unsigned tile = pair; ok && tile < num_tiles; tile += num_pairs) {
         if (args.tile_sync && done_rounds > 0) {
-          if (!(ok = tile_round_sync(args.status + 4 + rank, sync_target, ctx, 5))) break;
+          if (!(ok = tile_round_sync(args.rounds + rank, sync_target, ctx, 5))) break;
         }
         {
           const unsigned first = tile - pair, left = num_tiles - first;
@@ -145,7 +145,7 @@ gemm2_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__
           }
         }
       }
-      if (ok && args.tile_sync && done_rounds > 0) atomicAdd(args.status + 4 + rank, 1);
+      if (ok && args.tile_sync && done_rounds > 0) atomicAdd(args.rounds + rank, 1);
     }
     __syncwarp();
   } else if (warp == 1) {

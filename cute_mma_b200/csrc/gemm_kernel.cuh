@@ -47,7 +47,8 @@ struct GemmArgs {
   long long ldC;
   int* status;
   int raster;  // 0: z-curve tile order; g > 0: bands of g tile rows
-  int tile_sync;  // pair kernel: producers of all CTAs start each tile round together (status[4..5] are the counters)
+  int tile_sync;  // pair kernel: producers of all CTAs start each tile round together
+  int* rounds;    // 4 zeroed counters of this launch's tile rounds (tile_sync only)
   int a3d, b3d;  // MN-major operand described by a 3-D map (chunk, K, chunk index): one copy per tile instead of one per chunk
   unsigned long long hint_a, hint_b;  // L2 eviction priority of the K-major tile loads of A and B (pair kernel)
 };

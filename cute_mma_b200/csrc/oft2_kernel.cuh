@@ -133,7 +133,7 @@ oft2_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
       unsigned done_rounds = 0, sync_target = 0;
       for (unsigned tile = pair; ok && tile < num_tiles; tile += num_pairs) {
         if (args.tile_sync && done_rounds > 0) {
-          if (!(ok = tile_round_sync(args.status + 4 + rank, sync_target, ctx, 12))) break;
+          if (!(ok = tile_round_sync(args.rounds + rank, sync_target, ctx, 12))) break;
         }
         {  // every pair that had a tile in this round takes part in the next rendezvous
           const unsigned first = tile - pair, left = num_tiles - first;
@@ -156,7 +156,7 @@ oft2_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
         }
       }
       // leaving after its last round, this thread still counts for the rendezvous the others make
-      if (ok && args.tile_sync && done_rounds > 0) atomicAdd(args.status + 4 + rank, 1);
+      if (ok && args.tile_sync && done_rounds > 0) atomicAdd(args.rounds + rank, 1);
     }
     __syncwarp();
   } else if (warp == 1) {
@@ -168,7 +168,7 @@ oft2_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
       unsigned done_rounds = 0, sync_target = 0;
       for (unsigned tile = pair; ok && tile < num_tiles; tile += num_pairs) {
         if (args.tile_sync && done_rounds > 0) {
-          if (!(ok = tile_round_sync(args.status + 6 + rank, sync_target, ctx, 13))) break;
+          if (!(ok = tile_round_sync(args.rounds + 2 + rank, sync_target, ctx, 13))) break;
         }
         {
           const unsigned first = tile - pair, left = num_tiles - first;
@@ -187,7 +187,7 @@ oft2_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
             tma_load_2d_pair_hint(ring2 + s * T::kS2Bytes + gl * T::kGSHalf * 128, &tmap_b, full2 + 8 * s, st * T::kBK, n0 + gl * T::kGS, args.hint_b);
         }
       }
-      if (ok && args.tile_sync && done_rounds > 0) atomicAdd(args.status + 6 + rank, 1);
+      if (ok && args.tile_sync && done_rounds > 0) atomicAdd(args.rounds + 2 + rank, 1);
     }
     __syncwarp();
   } else if (warp == 2) {

@@ -61,7 +61,8 @@ struct OftArgs {
   int* status;
   int raster;  // 0: z-curve tile order; g > 0: bands of g tile rows
   unsigned long long hint_a, hint_b;  // L2 eviction priority of the A and B tile loads (pair kernel)
-  int tile_sync;  // pair kernel: producers of all CTAs start each tile round together (status[4..7] are the counters)
+  int tile_sync;  // pair kernel: producers of all CTAs start each tile round together
+  int* rounds;    // 4 zeroed counters of this launch's tile rounds (tile_sync only)
 };
 
 template <class T>
