@@ -151,6 +151,29 @@ def test_oft_path_choice_is_invisible(lib, cuda):
     assert truth_ok(auto, truth)[0] == 0
 
 
+@pytest.mark.parametrize("m,k,b,ldx", [(200, 192, 64, 192), (136, 96, 32, 104), (384, 512, 128, 512), (72, 264, 8, 264), (1000, 320, 16, 328)])
+def test_rotate_matches_blockwise_product(lib, cuda, m, k, b, ldx):
+    """b200_rotate_f16 alone: XR[:, kb*b:(kb+1)*b] = half(A[:, kb*b:(kb+1)*b] . Rstore_kb^T) with fp32 accumulation
+    (summation order free: one fp16 ulp allowed), ragged M and K edges clipped, padding of XR untouched."""
+    import torch
+
+    A, R, _ = make_oft_case(m, 8, k, b, seed=17, kind="qr")
+    dA, dR = torch.from_numpy(A).to(cuda), torch.from_numpy(R).to(cuda)
+    dX = torch.full((m + 1, ldx), -7.0, dtype=torch.float16, device=cuda)
+    ops.rotate(m, k, dA, k, dR, k, dX, ldx, reconn_sz=b, lib=lib)
+    assert ops.device_status(lib)[0] == 0
+    out = dX.cpu().numpy()
+    assert np.all(out[m, :] == np.float16(-7.0)) and np.all(out[:m, k:] == np.float16(-7.0))
+    ref = np.empty((m, k), dtype=np.float64)
+    for kb in range(k // b):
+        ref[:, kb * b:(kb + 1) * b] = A[:, kb * b:(kb + 1) * b].astype(np.float64) @ R[:, kb * b:(kb + 1) * b].astype(np.float64).T
+    got = out[:m, :k].astype(np.float64)
+    assert np.all(np.abs(got - ref) <= 2.0 ** -10 * (np.abs(ref) + 2.0 ** -4)), float(np.abs(got - ref).max())
+    with pytest.raises(ops.Error) as e:  # rows of XR must start on 16-byte boundaries (tile stores)
+        ops.rotate(m, k, dA, k, dR, k, dX, ldx + 1, reconn_sz=b, lib=lib)
+    assert e.value.code == ops.EINVAL
+
+
 def test_oft_group_size_limits(lib, cuda):
     """Groups that neither divide the N tile nor are a multiple of it, and 128 x 128 blocks with several groups
     per tile, are refused with a message instead of computed wrongly."""
