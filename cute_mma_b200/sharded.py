@@ -50,3 +50,98 @@ def all_gather_c(c_local, world: int | None = None):
     out = torch.empty((world * m, n_loc), dtype=c_local.dtype, device=c_local.device)  # concatenation along dim 0
     dist.all_gather_into_tensor(out, c_local.contiguous())
     return out.view(world, m, n_loc)
+
+
+def row_slice(m: int, world: int, rank: int) -> tuple[int, int]:
+    """Rows of X that rank uploads in HostSlabRunner: equal slices of ceil(m / world) rows (the last ones may be
+    short or empty), so that the all-gather of the slices is one contiguous collective."""
+    per = (m + world - 1) // world
+    r0 = min(m, rank * per)
+    return r0, min(m, r0 + per)
+
+
+class HostSlabRunner:
+    """End-to-end N-sharded product from HOST buffers on the ranks of one node.
+
+    Every rank needs all of X, but X crosses the host link only once per node: rank r uploads rows
+    row_slice(m, world, r) of X from its (pinned) host buffer, and the slices are all-gathered over NVLink
+    (torch.distributed, NCCL on GPUs) while each rank's slab of W^T and R go up on a second stream.  Then the
+    rank's slab product runs (ops.oft_tn on the device buffers) and its [m][n_loc] slab of Y comes back to
+    host memory in row chunks whose downloads overlap the next chunk's product.  Device buffers are allocated
+    once per runner.  ``compute`` / ``device`` exist so that the data movement can be exercised on CPU ranks over
+    gloo with the oracle standing in for the kernel."""
+
+    def __init__(self, m, n_total, k, n0, n1, *, group_size=None, reconn_sz=8, world=None, rank=None, device=None, compute=None,
+                 lib=None, chunks=8):
+        import torch
+        import torch.distributed as dist
+
+        self.torch, self.dist = torch, dist
+        self.world = world if world is not None else dist.get_world_size()
+        self.rank = rank if rank is not None else dist.get_rank()
+        self.m, self.n_total, self.k, self.n0, self.n1 = m, n_total, k, n0, n1
+        self.n_loc = n1 - n0
+        gs = n_total if group_size is None else group_size
+        self.gs_loc = self.n_loc if gs >= n_total else gs
+        self.b = reconn_sz
+        self.r_rows = max(1, self.n_loc // self.gs_loc) * reconn_sz
+        self.device = torch.device(device if device is not None else "cuda")
+        self.compute, self.lib = compute, lib
+        self.per = (m + self.world - 1) // self.world
+        f16 = torch.float16
+        self.dX = torch.empty((self.per * self.world, k), dtype=f16, device=self.device)  # padded to equal slices
+        self.dW = torch.empty((self.n_loc, k), dtype=f16, device=self.device)
+        self.dR = torch.empty((self.r_rows, k), dtype=f16, device=self.device)
+        self.dY = torch.empty((m, self.n_loc), dtype=f16, device=self.device)
+        self.cuda = self.device.type == "cuda"
+        if self.cuda:
+            self.s_in, self.s_out = torch.cuda.Stream(self.device), torch.cuda.Stream(self.device)
+        self.chunk_rows = max(256, ((m + chunks - 1) // chunks + 255) // 256 * 256)
+
+    def bytes_per_step(self):
+        """(host-to-device, device-to-host) bytes this rank moves per call."""
+        r0, r1 = row_slice(self.m, self.world, self.rank)
+        return ((r1 - r0) * self.k + self.n_loc * self.k + self.r_rows * self.k) * 2, self.m * self.n_loc * 2
+
+    def __call__(self, hX_rows, hW_slab, hR_slab, hY_slab):
+        """hX_rows: this rank's rows row_slice(m, world, rank) of X [rows][k]; hW_slab [n_loc][k]; hR_slab
+        [r_rows][k]; hY_slab [m][n_loc] (written).  Host tensors, pinned for asynchronous copies.  Returns when
+        hY_slab is complete."""
+        torch, dist = self.torch, self.dist
+        r0, r1 = row_slice(self.m, self.world, self.rank)
+        mine = self.dX[self.rank * self.per: self.rank * self.per + self.per]
+        if self.cuda:
+            main = torch.cuda.current_stream(self.device)
+            self.s_in.wait_stream(main)
+            with torch.cuda.stream(self.s_in):  # W and R go up beside the slice of X and the all-gather
+                self.dW.copy_(hW_slab, non_blocking=True)
+                self.dR.copy_(hR_slab, non_blocking=True)
+            if r1 > r0:
+                mine[: r1 - r0].copy_(hX_rows, non_blocking=True)
+        else:
+            self.dW.copy_(hW_slab)
+            self.dR.copy_(hR_slab)
+            if r1 > r0:
+                mine[: r1 - r0].copy_(hX_rows)
+        if self.world > 1:
+            # in place on NCCL (rank r's input is slice r of the output); a copy of the slice where the backend may not alias
+            dist.all_gather_into_tensor(self.dX, mine if self.cuda else mine.clone())
+        if self.cuda:
+            main.wait_stream(self.s_in)
+        fn = self.compute or ops.oft_tn
+        kwargs = dict(group_size=self.gs_loc, reconn_sz=self.b)
+        if self.compute is None:
+            kwargs["lib"] = self.lib
+        for c0 in range(0, self.m, self.chunk_rows):
+            rows = min(self.chunk_rows, self.m - c0)
+            stream = torch.cuda.current_stream(self.device).cuda_stream if self.cuda else None
+            fn(rows, self.n_loc, self.k, self.dX[c0:], self.k, self.dW, self.k, self.dR, self.k, self.dY[c0:], self.n_loc, stream, **kwargs)
+            if self.cuda:
+                self.s_out.wait_stream(main)
+                with torch.cuda.stream(self.s_out):
+                    hY_slab[c0: c0 + rows].copy_(self.dY[c0: c0 + rows], non_blocking=True)
+            else:
+                hY_slab[c0: c0 + rows].copy_(self.dY[c0: c0 + rows])
+        if self.cuda:
+            self.s_out.synchronize()
+            main.synchronize()

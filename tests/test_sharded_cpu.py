@@ -74,3 +74,69 @@ def test_two_rank_sharded_product_matches_unsharded(n, gs, b):
     results.sort()
     assert [r[1] for r in results] == [(0, n // 2), (n // 2, n)]
     assert all(r[2] and r[3] for r in results), results
+
+
+def _host_runner_worker(rank, world, port, m, n, gs, b, q):
+    sys.path.insert(0, ROOT)
+    sys.path.insert(0, os.path.join(ROOT, "tests"))
+    import torch
+    import torch.distributed as dist
+
+    from _util import make_oft_case
+    from cute_mma_b200 import ops, sharded
+    from oracle import oracle
+
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        k = 128
+        A, R, B = make_oft_case(m, n, k, b, gs, seed=2)
+        n0, n1 = sharded.my_slab(n, gs, lib=ops.load_library())
+        calls = []
+
+        def compute(m_, n_loc, k_, A_, ldA, B_, ldB, R_, ldR, C_, ldC, stream, group_size, reconn_sz):
+            calls.append(m_)
+            out = oracle.cpu_oft_tn(A_[:m_].numpy().view(np.float16), R_.numpy().view(np.float16), B_.numpy().view(np.float16),
+                                    m_, group_size, n_loc // group_size, k_, reconn_sz)
+            C_[:m_] = torch.from_numpy(out)
+
+        runner = sharded.HostSlabRunner(m, n, k, n0, n1, group_size=gs, reconn_sz=b, device="cpu", compute=compute, chunks=2)
+        r0, r1 = sharded.row_slice(m, world, rank)
+        G_first = n0 // gs if gs < n else 0
+        R_slab = R[G_first * b: G_first * b + runner.r_rows]
+        hY = torch.zeros((m, n1 - n0), dtype=torch.float16)
+        runner(torch.from_numpy(A[r0:r1]), torch.from_numpy(B[n0:n1]), torch.from_numpy(R_slab), hY)  # this rank only supplies ITS rows of X
+        full = oracle.cpu_oft_tn(A, R, B, m, gs, n // gs, k, b)
+        ok = np.array_equal(hY.numpy().view(np.uint16), full[:, n0:n1].view(np.uint16))
+        h2d, d2h = runner.bytes_per_step()
+        q.put((rank, bool(ok), (r0, r1), len(calls), h2d, d2h))
+    except Exception as e:
+        q.put((rank, repr(e), None, 0, 0, 0))
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("m,n,gs,b", [(512, 512, 512, 32), (300, 512, 256, 16)])
+def test_two_rank_host_runner_uploads_x_once_and_matches(m, n, gs, b):
+    """HostSlabRunner over gloo: each rank supplies only its rows of X, the all-gather rebuilds X on every rank
+    (also when M is not a multiple of the world size), the chunked slab product equals the unsharded oracle."""
+    import torch.multiprocessing as mp
+
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_host_runner_worker, args=(r, 2, port, m, n, gs, b, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    results = [q.get(timeout=90) for _ in procs]
+    for p in procs:
+        p.join(timeout=60)
+        assert p.exitcode == 0
+    results.sort()
+    assert all(r[1] is True for r in results), results
+    assert [r[2] for r in results] == [(0, (m + 1) // 2), ((m + 1) // 2, m)]
+    assert all(r[3] == 2 for r in results)  # two row chunks per rank
+    r_rows_total = (n // gs) * b if gs < n else 2 * b  # one group: both ranks hold the whole R
+    assert sum(r[4] for r in results) == (m * 128 + n * 128 + r_rows_total * 128) * 2  # X crosses the host link once
+    assert sum(r[5] for r in results) == m * n * 2
