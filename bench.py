@@ -188,7 +188,7 @@ def run_reference_arm(args, workload):
             "config": {"workload": workload, "note": "ms_per_step extrapolates the sampled rate to the full problem"},
             "cpu_baseline": {"value": value, "unit": "TFLOP/s", "cores": info["cores"], "kind": info["kind"], "sample": info["sample"]},
             "e2e": {"value": value, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}, "gpu_launches": 0}
-    print(json.dumps(line), flush=True)
+    emit(line)
 
 
 # --------------------------------------------------------------------------------------- GPU arm
@@ -257,8 +257,6 @@ def run_gpu_arm(args, workload):
     dev = torch.device("cuda", local_rank)
     if world > 1:
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
-        # rank 0 prints one JSON line on stdout: NCCL's version banner and any debug output go to stderr
-        os.environ.setdefault("NCCL_DEBUG_FILE", "/dev/stderr")
         dist.init_process_group("nccl", device_id=dev)
     lib = ops.load_library()  # raises if the CUDA library is missing: there is no fallback
 
@@ -456,13 +454,33 @@ def run_gpu_arm(args, workload):
             cb = cpu_reference_rate(m, k, n, b, kind, 12.0)
             cb.pop("seconds", None)
             line["cpu_baseline"] = cb
-        print(json.dumps(line), flush=True)
+        emit(line)
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()
 
 
+_RESULT_FD = None
+
+
+def emit(line):
+    """The one JSON line of the run, written to the process's original stdout."""
+    data = (json.dumps(line) + "\n").encode()
+    if _RESULT_FD is None:
+        sys.stdout.write(data.decode())
+        sys.stdout.flush()
+    else:
+        os.write(_RESULT_FD, data)
+
+
 def main():
+    # stdout carries exactly one JSON line.  Libraries that write to file descriptor 1 on their own (NCCL prints its
+    # version banner there whatever NCCL_DEBUG_FILE says) are sent to stderr: fd 1 is pointed at fd 2 for the whole
+    # run and the result goes to a duplicate of the original stdout.
+    global _RESULT_FD
+    sys.stdout.flush()
+    _RESULT_FD = os.dup(1)
+    os.dup2(2, 1)
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=10)
