@@ -766,6 +766,37 @@ int b200_gemm(char transA, char transB, int is_float, int m, int n, int k, const
   return fail(B200_EUNSUPPORTED, "gemm('%c','%c'): only ('T','N') and ('N','T') exist, as in the reference", transA, transB);
 }
 
+int b200_gemm_rowmajor(char transA, char transB, int is_float, int m, int n, int k, const void* A, int ldA, const void* B, int ldB,
+                       void* C, int ldC, void* stream) {
+  // Row-major C (m x n, rows ldC apart) is the column-major n x m result of the same product with the operands
+  // exchanged; both layouts keep their meaning under the exchange (K-contiguous stays K-contiguous).
+  if (m > 0 && n > 0 && ldC < n) {
+    g_err.clear();
+    return fail(B200_EINVAL, "ldC=%d smaller than n=%d (C is row-major)", ldC, n);
+  }
+  return b200_gemm(transA, transB, is_float, n, m, k, B, ldB, A, ldA, C, ldC, stream);
+}
+
+int b200_peer_copy_async(void* dst, int dst_device, const void* src, int src_device, size_t bytes, void* stream) {
+  g_err.clear();
+  if (bytes == 0) return B200_OK;
+  if (!dst || !src) return fail(B200_EINVAL, "null pointer in peer copy");
+  if (dst_device != src_device) {  // direct copies over NVLink need peer access from the device that issues them
+    int cur = 0, can = 0;
+    CUDA_TRY(cudaGetDevice(&cur));
+    CUDA_TRY(cudaDeviceCanAccessPeer(&can, src_device, dst_device));
+    if (can) {
+      if (cur != src_device) CUDA_TRY(cudaSetDevice(src_device));
+      const cudaError_t e = cudaDeviceEnablePeerAccess(dst_device, 0);
+      if (cur != src_device) cudaSetDevice(cur);
+      if (e != cudaSuccess && e != cudaErrorPeerAccessAlreadyEnabled) return fail(B200_ECUDA, "cudaDeviceEnablePeerAccess: %s", cudaGetErrorString(e));
+      cudaGetLastError();
+    }
+  }
+  CUDA_TRY(cudaMemcpyPeerAsync(dst, dst_device, src, src_device, bytes, static_cast<cudaStream_t>(stream)));
+  return B200_OK;
+}
+
 int b200_shard_range(int n, int group_size, int world, int rank, int* n_begin, int* n_end) {
   g_err.clear();
   if (n < 0 || group_size <= 0 || world <= 0 || rank < 0 || rank >= world || !n_begin || !n_end)

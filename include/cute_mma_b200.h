@@ -126,6 +126,17 @@ int b200_gemm_nt_tf32(int m, int n, int k, const void* A, int ldA, const void* B
 int b200_gemm(char transA, char transB, int is_float, int m, int n, int k,
               const void* A, int ldA, const void* B, int ldB, void* C, int ldC, void* stream);
 
+/* The same products with C row-major: C(i,j) at C[i*ldC + j], ldC >= n.  The reference's kernels only write
+ * column-major C (gemm_tc.hpp:12-14, SURVEY "row-major C for gemm_*" is listed as an adjacent variant); the
+ * rotation + GEMM route of the OFT product uses this form internally. */
+int b200_gemm_rowmajor(char transA, char transB, int is_float, int m, int n, int k,
+                       const void* A, int ldA, const void* B, int ldB, void* C, int ldC, void* stream);
+
+/* Device-to-device copy between two GPUs of this process' view (dst may be memory of another process mapped
+ * through CUDA IPC), asynchronous on `stream` of the current device: a copy-engine transfer over NVLink, with
+ * peer access enabled on first use.  Used by the overlapped all-gather of Y; no counterpart in the reference. */
+int b200_peer_copy_async(void* dst, int dst_device, const void* src, int src_device, size_t bytes, void* stream);
+
 /* Column range [n_begin, n_end) of B (rows of the stored [n][k] matrix) and of C owned by `rank` when
  * the product is sharded along N over `world` GPUs, A and R replicated.  The reference has no
  * multi-GPU path; the partition follows its group structure (cpu_oft.hpp:52-93: columns of one

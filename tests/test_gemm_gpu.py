@@ -112,6 +112,29 @@ def test_gemm_dispatcher_and_errors(lib, cuda):
     assert e.value.code == ops.EINVAL
 
 
+@pytest.mark.parametrize("layout,dtype", [("TN", "half"), ("NT", "half"), ("TN", "float"), ("NT", "float")])
+def test_gemm_rowmajor_is_the_transpose_of_colmajor(lib, cuda, layout, dtype):
+    """b200_gemm_rowmajor writes C[i][j] where b200_gemm writes C[i + j*ldC]: same numbers, bit for bit
+    (the same MMAs accumulate each element in the same K order), padding of C untouched."""
+    import torch
+
+    m, n, k = 200, 328, 96
+    A, B, ldA, ldB, _, _ = make_operands(layout, dtype, m, n, k, seed=6)
+    tdt = torch.float16 if dtype == "half" else torch.float32
+    dA, dB = torch.from_numpy(A).to(cuda), torch.from_numpy(B).to(cuda)
+    c_col = torch.empty((n, m), dtype=tdt, device=cuda)
+    c_row = torch.full((m, n + 8), -7.0, dtype=tdt, device=cuda)
+    ta, tb = ("T", "N") if layout == "TN" else ("N", "T")
+    ops.gemm(ta, tb, m, n, k, dA, ldA, dB, ldB, c_col, m, dtype=dtype, lib=lib)
+    ops.gemm_rowmajor(ta, tb, m, n, k, dA, ldA, dB, ldB, c_row, n + 8, dtype=dtype, lib=lib)
+    assert ops.device_status(lib)[0] == 0
+    assert torch.equal(c_row[:, :n], c_col.t())
+    assert bool((c_row[:, n:] == -7.0).all())
+    with pytest.raises(ops.Error) as e:
+        ops.gemm_rowmajor(ta, tb, m, n, k, dA, ldA, dB, ldB, c_row, n - 8, dtype=dtype, lib=lib)
+    assert e.value.code == ops.EINVAL
+
+
 def _sampled(lib, cuda, layout, dtype, m, n, k, seed, dist):
     import torch
 
