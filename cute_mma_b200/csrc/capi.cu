@@ -11,6 +11,7 @@
 #include <mutex>
 #include <string>
 #include <type_traits>
+#include <unordered_map>
 
 #include <cuda.h>
 #include <cuda_fp16.h>
@@ -157,11 +158,22 @@ int make_map_chunks(CUtensorMap* map, const void* base, int elem_bytes, long lon
   return r == CUDA_SUCCESS ? B200_OK : B200_EUNSUPPORTED;
 }
 
+std::mutex g_optin_mu;
+std::unordered_map<const void*, unsigned long long> g_optin;  // kernel -> bit per device ordinal that has opted in (cleared by b200_shutdown)
+
 template <class Kernel>
 int opt_in_smem(Kernel kernel, int bytes) {
   // The reference never raises the dynamic shared-memory limit and so cannot launch any tile
   // configuration above 48 KB; every kernel here needs the opt-in.
+  // (once per kernel and device: the attribute belongs to the device's context)
+  int dev = 0;
+  CUDA_TRY(cudaGetDevice(&dev));
+  const void* key = reinterpret_cast<const void*>(kernel);
+  std::lock_guard<std::mutex> lock(g_optin_mu);
+  unsigned long long& bits = g_optin[key];
+  if (dev >= 0 && dev < 64 && ((bits >> dev) & 1ull)) return B200_OK;
   CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes));
+  if (dev >= 0 && dev < 64) bits |= 1ull << dev;
   return B200_OK;
 }
 
@@ -921,6 +933,10 @@ const char* b200_last_error(void) { return g_err.c_str(); }
 
 int b200_shutdown(void) {
   g_err.clear();
+  {
+    std::lock_guard<std::mutex> lock(g_optin_mu);
+    g_optin.clear();
+  }
   std::lock_guard<std::mutex> lock(g_mu);
   int cur = 0;
   cudaGetDevice(&cur);
