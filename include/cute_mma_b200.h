@@ -127,8 +127,7 @@ int b200_gemm(char transA, char transB, int is_float, int m, int n, int k,
               const void* A, int ldA, const void* B, int ldB, void* C, int ldC, void* stream);
 
 /* The same products with C row-major: C(i,j) at C[i*ldC + j], ldC >= n.  The reference's kernels only write
- * column-major C (gemm_tc.hpp:12-14, SURVEY "row-major C for gemm_*" is listed as an adjacent variant); the
- * rotation + GEMM route of the OFT product uses this form internally. */
+ * column-major C (gemm_tc.hpp:12-14); the rotation + GEMM route of the OFT product uses this form internally. */
 int b200_gemm_rowmajor(char transA, char transB, int is_float, int m, int n, int k,
                        const void* A, int ldA, const void* B, int ldB, void* C, int ldC, void* stream);
 
