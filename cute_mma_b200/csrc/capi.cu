@@ -206,7 +206,8 @@ void release_round_counters(DeviceState* st, cudaStream_t stream, int* p) {
 }
 
 template <typename TIn, typename TOut, bool kNT, class P>
-int launch_gemm(int m, int n, int k, const void* A, int ldA, const void* B, int ldB, void* C, int ldC, void* stream_v) {
+int launch_gemm(int m, int n, int k, const void* A, int ldA, const void* B, int ldB, void* C, int ldC, void* stream_v,
+                int k2 = 0, const void* A2 = nullptr, int ldA2 = 0, const void* B2 = nullptr, int ldB2 = 0) {
   constexpr bool kPair = CtasOf<P>::value == 2;
   using T1 = GemmTraits<TIn, TOut, kNT, kNT, P::bN, kPair ? 4 : P::bP>;
   using T2 = Gemm2Traits<TIn, TOut, kNT, kNT, P::bN, kPair ? P::bP : 6>;
@@ -216,6 +217,9 @@ int launch_gemm(int m, int n, int k, const void* A, int ldA, const void* B, int 
   if (ldC < m) return fail(B200_EINVAL, "ldC=%d smaller than m=%d (C is column-major)", ldC, m);
   cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
   if (m == 0 || n == 0) return B200_OK;
+  if (k2 < 0 || (k2 > 0 && (!A2 || !B2))) return fail(B200_EINVAL, "bad second operand pair (k2=%d)", k2);
+  if (k2 > 0 && (kNT || !kPair)) return fail(B200_EUNSUPPORTED, "a second operand pair needs K-contiguous operands and the CTA-pair kernel (ctas = 2)");
+  if (k == 0 && k2 > 0) return launch_gemm<TIn, TOut, kNT, P>(m, n, k2, A2, ldA2, B2, ldB2, C, ldC, stream_v);
   if (k == 0) {
     CUDA_TRY(cudaMemset2DAsync(C, static_cast<size_t>(ldC) * sizeof(TOut), 0, static_cast<size_t>(m) * sizeof(TOut), n, stream));
     return B200_OK;
@@ -254,13 +258,18 @@ int launch_gemm(int m, int n, int k, const void* A, int ldA, const void* B, int 
     auto pick = [](char c) { return c == 'f' ? kL2EvictFirst : (c == 'l' ? kL2EvictLast : kL2EvictNormal); };
     if (e[0] && e[1]) { hint_a = pick(e[0]); hint_b = pick(e[1]); }
   }
-  GemmArgs args{m, n, k, C, ldC, st->status, raster, tile_sync, rounds, a3d, b3d, hint_a, hint_b};
+  GemmArgs args{m, n, k, C, ldC, st->status, raster, tile_sync, rounds, a3d, b3d, hint_a, hint_b, k2};
   if constexpr (kPair) {
+    CUtensorMap ma2 = ma, mb2 = mb;  // never read when k2 == 0
+    if (k2 > 0) {
+      if (int rc = make_map(&ma2, A2, sizeof(TIn), k2, m, ldA2, T1::kBK, T1::kBM, "A2")) return rc;
+      if (int rc = make_map(&mb2, B2, sizeof(TIn), k2, n, ldB2, T1::kBK, kBoxN, "B2")) return rc;
+    }
     auto kernel = gemm2_kernel<T2>;
     if (int rc = opt_in_smem(kernel, T2::kSmemBytes)) return rc;
     const long long tiles = static_cast<long long>((m + 2 * T2::kBM - 1) / (2 * T2::kBM)) * ((n + T2::kBN - 1) / T2::kBN);
     const int pairs = static_cast<int>(tiles < st->sm_count / 2 ? tiles : st->sm_count / 2);
-    kernel<<<2 * pairs, T2::kThreads, T2::kSmemBytes, stream>>>(ma, mb, args);  // cluster dimension (2,1,1) is part of the kernel
+    kernel<<<2 * pairs, T2::kThreads, T2::kSmemBytes, stream>>>(ma, mb, ma2, mb2, args);  // cluster dimension (2,1,1) is part of the kernel
   } else {
     auto kernel = gemm_kernel<T1>;
     if (int rc = opt_in_smem(kernel, T1::kSmemBytes)) return rc;
@@ -759,6 +768,36 @@ int b200_oft_tn_f16_host(int m, int n, int k, int group_size, int reconn_sz, con
 int b200_gemm_tn_f16(int m, int n, int k, const void* A, int ldA, const void* B, int ldB, void* C, int ldC, void* stream) {
   return launch_gemm<__half, __half, false, Params<half, half, MMA_T, MMA_N>>(m, n, k, A, ldA, B, ldB, C, ldC, stream);
 }
+int b200_gemm_tn_f16_acc2(int m, int n, int k, const void* A, int ldA, const void* B, int ldB, int k2, const void* A2, int ldA2,
+                          const void* B2, int ldB2, void* C, int ldC, void* stream) {
+  return launch_gemm<__half, __half, false, Params<half, half, MMA_T, MMA_N>>(m, n, k, A, ldA, B, ldB, C, ldC, stream, k2, A2, ldA2, B2, ldB2);
+}
+
+int b200_lora_tn_f16(int m, int n, int k, int r, const void* X, int ldX, const void* W, int ldW, const void* L1, int ldL1,
+                     const void* L2, int ldL2, void* C, int ldC, void* stream_v) {
+  g_err.clear();
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
+  if (int rc = common_dims(m, n, k, X, W, C)) return rc;
+  if (r < 0 || (r > 0 && m > 0 && n > 0 && k > 0 && (!L1 || !L2))) return fail(B200_EINVAL, "bad low-rank factors (r=%d)", r);
+  if (ldC < n) return fail(B200_EINVAL, "ldC=%d smaller than n=%d (C is row-major)", ldC, n);
+  if (m == 0 || n == 0) return B200_OK;
+  if (r == 0 || k == 0) return b200_gemm_tn_f16(n, m, k, W, ldW, X, ldX, C, ldC, stream_v);  // no adapter: the plain product, row-major
+  DeviceState* st;
+  if (int rc = device_state(&st)) return rc;
+  const int ldt = (r + 7) & ~7;
+  void* t = nullptr;
+  CUDA_TRY(cudaMallocFromPoolAsync(&t, static_cast<size_t>(m) * ldt * 2, st->pool, stream));
+  // T[m][r] (row-major) = X . L1^T: the column-major r x m result of gemm_tn(L1, X); rounded to fp16 like the
+  // reference's intermediate (playgrounds/lora.cu:44-49)
+  int rc = b200_gemm_tn_f16(r, m, k, L1, ldL1, X, ldX, t, ldt, stream_v);
+  // C[m][n] (row-major) = column-major n x m result of  W . X^T + L2 . T^T  in one pass over both operand pairs
+  if (rc == B200_OK) rc = b200_gemm_tn_f16_acc2(n, m, k, W, ldW, X, ldX, r, L2, ldL2, t, ldt, C, ldC, stream_v);
+  const std::string keep = g_err;
+  cudaFreeAsync(t, stream);
+  g_err = keep;
+  return rc;
+}
+
 int b200_gemm_nt_f16(int m, int n, int k, const void* A, int ldA, const void* B, int ldB, void* C, int ldC, void* stream) {
   return launch_gemm<__half, __half, true, Params<half, half, MMA_N, MMA_T>>(m, n, k, A, ldA, B, ldB, C, ldC, stream);
 }

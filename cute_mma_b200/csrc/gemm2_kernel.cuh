@@ -49,7 +49,8 @@ struct Gemm2Traits {
 
 template <class T>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(T::kThreads, 1)
-gemm2_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b, const GemmArgs args) {
+gemm2_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+             const __grid_constant__ CUtensorMap tmap_a2, const __grid_constant__ CUtensorMap tmap_b2, const GemmArgs args) {
   using TOut = typename T::TOut;
   extern __shared__ uint8_t smem_raw[];
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -71,7 +72,9 @@ gemm2_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__
   const unsigned pair = blockIdx.x >> 1, num_pairs = gridDim.x >> 1;
   const unsigned tiles_m = (args.m + 2 * T::kBM - 1) / (2 * T::kBM), tiles_n = (args.n + T::kBN - 1) / T::kBN;
   const unsigned num_tiles = tiles_m * tiles_n;
-  const int k_steps = (args.k + T::kBK - 1) / T::kBK;
+  // C = A.B^T + A2.B2^T: the K steps of the second pair simply follow those of the first in every tile's stream
+  const int k_steps1 = (args.k + T::kBK - 1) / T::kBK;
+  const int k_steps = k_steps1 + (args.k2 + T::kBK - 1) / T::kBK;
 
   if (threadIdx.x == 0) {
     *abort_flag = 0;
@@ -81,6 +84,7 @@ gemm2_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__
     fence_proxy_async_smem();
     prefetch_tmap(&tmap_a);
     prefetch_tmap(&tmap_b);
+    if (args.k2 > 0) { prefetch_tmap(&tmap_a2); prefetch_tmap(&tmap_b2); }
   }
   if (warp == 1) {
     tmem_alloc_pair(smem_u32(tmem_slot), T::kTmemCols);
@@ -120,9 +124,10 @@ gemm2_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__
 #endif
           if (rank == 0) mbar_expect_tx(full_bar(s), 2 * T::kStageBytes);  // both CTAs' bytes land on this barrier
           const uint32_t a_dst = smem_base + s * T::kStageBytes, b_dst = a_dst + T::kABytes;
-          const int k0 = ks * T::kBK;
+          const bool second = ks >= k_steps1;
+          const int k0 = (second ? ks - k_steps1 : ks) * T::kBK;
           if constexpr (!T::kAMn) {
-            tma_load_2d_pair_hint(a_dst, &tmap_a, full_bar(s), k0, m0, args.hint_a);
+            tma_load_2d_pair_hint(a_dst, second ? &tmap_a2 : &tmap_a, full_bar(s), k0, m0, args.hint_a);
           } else {
             if (args.a3d) {
               tma_load_3d_pair(a_dst, &tmap_a, full_bar(s), 0, k0, m0 / T::kChunk);
@@ -133,7 +138,7 @@ gemm2_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__
             }
           }
           if constexpr (!T::kBMn) {
-            tma_load_2d_pair_hint(b_dst, &tmap_b, full_bar(s), k0, n0, args.hint_b);
+            tma_load_2d_pair_hint(b_dst, second ? &tmap_b2 : &tmap_b, full_bar(s), k0, n0, args.hint_b);
           } else {
             if (args.b3d) {
               tma_load_3d_pair(b_dst, &tmap_b, full_bar(s), 0, k0, n0 / T::kChunk);

@@ -51,6 +51,7 @@ struct GemmArgs {
   int* rounds;    // 4 zeroed counters of this launch's tile rounds (tile_sync only)
   int a3d, b3d;  // MN-major operand described by a 3-D map (chunk, K, chunk index): one copy per tile instead of one per chunk
   unsigned long long hint_a, hint_b;  // L2 eviction priority of the K-major tile loads of A and B (pair kernel)
+  int k2;  // pair kernel, K-major operands: columns of a second operand pair (A2, B2) accumulated into the same C; 0 = none
 };
 
 template <class T>

@@ -24,7 +24,7 @@ OK, EINVAL, EUNSUPPORTED, ECUDA, EDEVICE = 0, 1, 2, 3, 4
 # every symbol include/cute_mma_b200.h declares
 SYMBOLS = (
     "b200_oft_tn_f16", "b200_oft_tn_f16_two_pass", "b200_rotate_f16", "b200_oft_plan", "b200_oft_tn_f16_host", "b200_oft_tn_f16_static", "b200_transform_weight_f16", "b200_oft_tn_f16_a_rw", "b200_gemm_tn_f16", "b200_gemm_nt_f16", "b200_gemm_tn_tf32",
-    "b200_gemm_nt_tf32", "b200_gemm", "b200_gemm_rowmajor", "b200_peer_copy_async", "b200_shard_range", "b200_tile_coord", "b200_device_status", "b200_selftest_wait_timeout", "b200_wait_profile", "b200_kernel_info",
+    "b200_gemm_nt_tf32", "b200_gemm", "b200_gemm_tn_f16_acc2", "b200_lora_tn_f16", "b200_gemm_rowmajor", "b200_peer_copy_async", "b200_shard_range", "b200_tile_coord", "b200_device_status", "b200_selftest_wait_timeout", "b200_wait_profile", "b200_kernel_info",
     "b200_last_error", "b200_shutdown",
 )
 
@@ -64,6 +64,8 @@ def load_library(path: str | None = None):
     for name in ("b200_gemm_tn_f16", "b200_gemm_nt_f16", "b200_gemm_tn_tf32", "b200_gemm_nt_tf32"):
         getattr(lib, name).argtypes = [i, i, i, vp, i, vp, i, vp, i, vp]
     lib.b200_gemm.argtypes = [c, c, i, i, i, i, vp, i, vp, i, vp, i, vp]
+    lib.b200_gemm_tn_f16_acc2.argtypes = [i, i, i, vp, i, vp, i, i, vp, i, vp, i, vp, i, vp]
+    lib.b200_lora_tn_f16.argtypes = [i, i, i, i, vp, i, vp, i, vp, i, vp, i, vp, i, vp]
     lib.b200_gemm_rowmajor.argtypes = [c, c, i, i, i, i, vp, i, vp, i, vp, i, vp]
     lib.b200_peer_copy_async.argtypes = [vp, i, vp, i, ctypes.c_size_t, vp]
     lib.b200_shard_range.argtypes = [i, i, i, i, ctypes.POINTER(i), ctypes.POINTER(i)]
@@ -182,6 +184,18 @@ def gemm(transA, transB, m, n, k, A, ldA, B, ldB, C, ldC, stream=None, *, dtype=
     lib = lib or load_library()
     _check(lib, lib.b200_gemm(transA.encode(), transB.encode(), 0 if dtype == "half" else 1, m, n, k, _ptr(A), ldA,
                               _ptr(B), ldB, _ptr(C), ldC, _stream(stream)))
+
+
+def gemm_tn_acc2(m, n, k, A, ldA, B, ldB, k2, A2, ldA2, B2, ldB2, C, ldC, stream=None, *, lib=None) -> None:
+    """C (column-major m x n) = A . B^T + A2 . B2^T, fp16, one pass."""
+    lib = lib or load_library()
+    _check(lib, lib.b200_gemm_tn_f16_acc2(m, n, k, _ptr(A), ldA, _ptr(B), ldB, k2, _ptr(A2), ldA2, _ptr(B2), ldB2, _ptr(C), ldC, _stream(stream)))
+
+
+def lora_tn(m, n, k, r, X, ldX, W, ldW, L1, ldL1, L2, ldL2, C, ldC, stream=None, *, lib=None) -> None:
+    """C[m][n] = X . W^T + (X . L1^T) . L2^T (row-major C), the LoRA-equivalent of oft_tn."""
+    lib = lib or load_library()
+    _check(lib, lib.b200_lora_tn_f16(m, n, k, r, _ptr(X), ldX, _ptr(W), ldW, _ptr(L1), ldL1, _ptr(L2), ldL2, _ptr(C), ldC, _stream(stream)))
 
 
 def gemm_rowmajor(transA, transB, m, n, k, A, ldA, B, ldB, C, ldC, stream=None, *, dtype="half", lib=None) -> None:

@@ -120,6 +120,19 @@ int b200_gemm_nt_f16(int m, int n, int k, const void* A, int ldA, const void* B,
 int b200_gemm_tn_tf32(int m, int n, int k, const void* A, int ldA, const void* B, int ldB, void* C, int ldC, void* stream);
 int b200_gemm_nt_tf32(int m, int n, int k, const void* A, int ldA, const void* B, int ldB, void* C, int ldC, void* stream);
 
+/* C = A . B^T + A2 . B2^T in one pass (tn layouts, fp16, C column-major): the K steps of the second operand pair
+ * (k2 columns) follow those of the first in every tile's accumulation.  CTA-pair build only.  No counterpart
+ * in the reference, whose accumulate-into-C epilogue is stubbed out (axpby, gemm_tc.hpp:241). */
+int b200_gemm_tn_f16_acc2(int m, int n, int k, const void* A, int ldA, const void* B, int ldB,
+                          int k2, const void* A2, int ldA2, const void* B2, int ldB2, void* C, int ldC, void* stream);
+
+/* LoRA-equivalent product, the comparator of playgrounds/lora.cu:33-64 (three cublasHgemm calls there):
+ *   C[m][n] (row-major, ldC) = X . W^T + (X . L1^T) . L2^T,   X [m][k], W [n][k], L1 [r][k], L2 [n][r], all fp16,
+ * as one small GEMM for T = X . L1^T (rounded to fp16, m * r * 2 bytes of stream-ordered scratch from the
+ * library's pool) and one b200_gemm_tn_f16_acc2 over (W, X) and (L2, T) with fp32 accumulation of both terms. */
+int b200_lora_tn_f16(int m, int n, int k, int r, const void* X, int ldX, const void* W, int ldW,
+                     const void* L1, int ldL1, const void* L2, int ldL2, void* C, int ldC, void* stream);
+
 /* Dispatcher of gemm(char transA, char transB, ...) (gemm_sm80_tc.cu:393-418): ('T','N') -> tn,
  * ('N','T') -> nt; lower-case letters select the same kernels (the reference's *_test variants are
  * an alternative shared-memory path of the same operator).  is_float: 0 = half/half, 1 = float/float. */

@@ -135,6 +135,49 @@ def test_gemm_rowmajor_is_the_transpose_of_colmajor(lib, cuda, layout, dtype):
     assert e.value.code == ops.EINVAL
 
 
+@pytest.mark.parametrize("m,n,k,k2", [(200, 328, 192, 64), (384, 512, 136, 16), (128, 256, 64, 200), (256, 256, 0, 72)])
+def test_gemm_second_operand_pair(lib, cuda, m, n, k, k2):
+    """C = A.B^T + A2.B2^T in one pass equals the fp64 sum of the two products within the fp16 GEMM tolerance,
+    including a ragged last K step of either pair and k = 0."""
+    import torch
+
+    rng = np.random.default_rng(12)
+    A, B = rng.uniform(-1, 1, (m, max(k, 8))).astype(np.float16), rng.uniform(-1, 1, (n, max(k, 8))).astype(np.float16)
+    A2, B2 = rng.uniform(-1, 1, (m, k2)).astype(np.float16), rng.uniform(-1, 1, (n, k2)).astype(np.float16)
+    dA, dB, dA2, dB2 = (torch.from_numpy(x).to(cuda) for x in (A, B, A2, B2))
+    dC = torch.empty((n, m), dtype=torch.float16, device=cuda)
+    ops.gemm_tn_acc2(m, n, k, dA, A.shape[1], dB, B.shape[1], k2, dA2, k2, dB2, k2, dC, m, lib=lib)
+    assert ops.device_status(lib)[0] == 0
+    ref = A[:, :k].astype(np.float64) @ B[:, :k].astype(np.float64).T + A2.astype(np.float64) @ B2.astype(np.float64).T
+    got = dC.cpu().numpy().T
+    bad, worst = oft_ok(got, ref)
+    assert bad == 0, (bad, worst)
+    assert np.all(np.abs(got.astype(np.float64) - ref) <= 2e-3 * (np.abs(ref) + 1))
+
+
+@pytest.mark.parametrize("m,n,k,r", [(256, 512, 256, 16), (200, 328, 192, 64), (1024, 1024, 512, 8), (128, 256, 128, 0)])
+def test_lora_matches_three_gemm_reference(lib, cuda, m, n, k, r):
+    """b200_lora_tn_f16 against the arithmetic of the reference's comparator (playgrounds/lora.cu:33-64) done in
+    fp64, with the intermediate X.L1^T rounded to fp16 as there."""
+    import torch
+
+    rng = np.random.default_rng(13)
+    X = rng.normal(0, 1, (m, k)).astype(np.float16)
+    W = rng.normal(0, 0.05, (n, k)).astype(np.float16)
+    L1 = rng.normal(0, 0.05, (max(r, 1), k)).astype(np.float16)
+    L2 = rng.normal(0, 0.05, (n, max(r, 8))).astype(np.float16)  # ld a multiple of 8 elements
+    dX, dW, dL1, dL2 = (torch.from_numpy(x).to(cuda) for x in (X, W, L1, L2))
+    dC = torch.full((m + 1, n), -7.0, dtype=torch.float16, device=cuda)
+    ops.lora_tn(m, n, k, r, dX, k, dW, k, dL1, k, dL2, L2.shape[1], dC, n, lib=lib)
+    assert ops.device_status(lib)[0] == 0
+    T = (X.astype(np.float64) @ L1[:r].astype(np.float64).T).astype(np.float16).astype(np.float64) if r else np.zeros((m, 0))
+    ref = X.astype(np.float64) @ W.astype(np.float64).T + T @ L2[:, :r].astype(np.float64).T
+    out = dC.cpu().numpy()
+    assert np.all(out[m] == np.float16(-7.0))
+    got = out[:m].astype(np.float64)
+    assert np.all(np.abs(got - ref) <= 2e-3 * (np.abs(ref) + 1)), float(np.abs(got - ref).max())
+
+
 def _sampled(lib, cuda, layout, dtype, m, n, k, seed, dist):
     import torch
 
