@@ -408,7 +408,7 @@ bool prefer_two_pass(int m, int k, int group_size, int b, const DeviceState* st)
   int path = g_oft_path;
   if (path == 0)
     if (const char* e = std::getenv("B200_OFT_PATH")) path = std::atoi(e);
-  if (!st->pool || !kOftPair) return false;  // no scratch to put X.R in (static-scratch entry point) / single-CTA build
+  if (!st->pool) return false;  // no scratch to put X.R in (the entry point with static scratch)
   if (path == 1) return false;
   if (path == 2) return true;
   // Cycles of one SM pair per (256 x 256 tile, 64 columns of K), measured with in-kernel cycle counters.

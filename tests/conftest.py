@@ -28,3 +28,11 @@ def cuda():
     assert torch.cuda.is_available(), "GPU tests need a CUDA device"
     torch.cuda.set_device(0)
     return torch.device("cuda:0")
+
+
+@pytest.fixture(scope="session")
+def pair_build(lib):
+    """True when the library was built with CTA pairs (ctas = 2, the default); a few features exist only there."""
+    from cute_mma_b200 import ops
+
+    return ops.kernel_info(lib)["oft"]["ctas"] == 2

@@ -136,7 +136,9 @@ def test_gemm_rowmajor_is_the_transpose_of_colmajor(lib, cuda, layout, dtype):
 
 
 @pytest.mark.parametrize("m,n,k,k2", [(200, 328, 192, 64), (384, 512, 136, 16), (128, 256, 64, 200), (256, 256, 0, 72)])
-def test_gemm_second_operand_pair(lib, cuda, m, n, k, k2):
+def test_gemm_second_operand_pair(lib, cuda, pair_build, m, n, k, k2):
+    if not pair_build:
+        pytest.skip("the second operand pair is a feature of the CTA-pair kernel")
     """C = A.B^T + A2.B2^T in one pass equals the fp64 sum of the two products within the fp16 GEMM tolerance,
     including a ragged last K step of either pair and k = 0."""
     import torch
@@ -156,7 +158,9 @@ def test_gemm_second_operand_pair(lib, cuda, m, n, k, k2):
 
 
 @pytest.mark.parametrize("m,n,k,r", [(256, 512, 256, 16), (200, 328, 192, 64), (1024, 1024, 512, 8), (128, 256, 128, 0)])
-def test_lora_matches_three_gemm_reference(lib, cuda, m, n, k, r):
+def test_lora_matches_three_gemm_reference(lib, cuda, pair_build, m, n, k, r):
+    if not pair_build and r > 0:
+        pytest.skip("the second operand pair is a feature of the CTA-pair kernel")
     """b200_lora_tn_f16 against the arithmetic of the reference's comparator (playgrounds/lora.cu:33-64) done in
     fp64, with the intermediate X.L1^T rounded to fp16 as there."""
     import torch
