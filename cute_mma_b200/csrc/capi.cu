@@ -205,12 +205,42 @@ void release_round_counters(DeviceState* st, cudaStream_t stream, int* p) {
   if (st->pool && p) cudaFreeAsync(p, stream);
 }
 
+template <typename TIn, typename TOut, bool kNT, class P, int kBN>
+int launch_gemm_bn(int m, int n, int k, const void* A, int ldA, const void* B, int ldB, void* C, int ldC, void* stream_v,
+                   int k2, const void* A2, int ldA2, const void* B2, int ldB2);
+
+// The tile is bM x bN of the configuration, except that the pair kernel also exists with half the N extent for
+// problems of at most half a wave of full-width tiles, where twice as many SM pairs get work.  A half-width tile
+// takes 0.8 of the time of a full one (measured at M = N = K = 4096, TF32: 512 half-width tiles in 7 waves
+// 0.286 ms, 256 full-width tiles in 4 waves 0.203 ms), so it never pays for evening out the last wave of a
+// larger problem.
 template <typename TIn, typename TOut, bool kNT, class P>
 int launch_gemm(int m, int n, int k, const void* A, int ldA, const void* B, int ldB, void* C, int ldC, void* stream_v,
                 int k2 = 0, const void* A2 = nullptr, int ldA2 = 0, const void* B2 = nullptr, int ldB2 = 0) {
   constexpr bool kPair = CtasOf<P>::value == 2;
-  using T1 = GemmTraits<TIn, TOut, kNT, kNT, P::bN, kPair ? 4 : P::bP>;
-  using T2 = Gemm2Traits<TIn, TOut, kNT, kNT, P::bN, kPair ? P::bP : 6>;
+  if constexpr (kPair && P::bN == 256) {
+    int narrow = 0;
+    if (const char* e = std::getenv("B200_GEMM_BN")) {
+      narrow = std::atoi(e) == 128;
+    } else if (m > 0 && n > 0) {
+      int dev = 0, sms = 148;
+      if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+      const long long pairs = sms / 2 > 0 ? sms / 2 : 1;
+      const long long t_wide = static_cast<long long>((m + 255) / 256) * ((n + 255) / 256), t_narrow = static_cast<long long>((m + 255) / 256) * ((n + 127) / 128);
+      const double wide = static_cast<double>((t_wide + pairs - 1) / pairs), half = 0.8 * static_cast<double>((t_narrow + pairs - 1) / pairs);
+      narrow = half < 0.97 * wide;
+    }
+    if (narrow) return launch_gemm_bn<TIn, TOut, kNT, P, 128>(m, n, k, A, ldA, B, ldB, C, ldC, stream_v, k2, A2, ldA2, B2, ldB2);
+  }
+  return launch_gemm_bn<TIn, TOut, kNT, P, P::bN>(m, n, k, A, ldA, B, ldB, C, ldC, stream_v, k2, A2, ldA2, B2, ldB2);
+}
+
+template <typename TIn, typename TOut, bool kNT, class P, int kBN>
+int launch_gemm_bn(int m, int n, int k, const void* A, int ldA, const void* B, int ldB, void* C, int ldC, void* stream_v,
+                   int k2, const void* A2, int ldA2, const void* B2, int ldB2) {
+  constexpr bool kPair = CtasOf<P>::value == 2;
+  using T1 = GemmTraits<TIn, TOut, kNT, kNT, kBN, kPair ? 4 : P::bP>;
+  using T2 = Gemm2Traits<TIn, TOut, kNT, kNT, kBN, kPair ? P::bP : 6>;
   static_assert(P::bM == T1::kBM && P::bK == T1::kBK, "gemm_config.hpp: bM must be 128 and bK one 128-byte row");
   g_err.clear();
   if (int rc = common_dims(m, n, k, A, B, C)) return rc;
@@ -219,7 +249,7 @@ int launch_gemm(int m, int n, int k, const void* A, int ldA, const void* B, int 
   if (m == 0 || n == 0) return B200_OK;
   if (k2 < 0 || (k2 > 0 && (!A2 || !B2))) return fail(B200_EINVAL, "bad second operand pair (k2=%d)", k2);
   if (k2 > 0 && (kNT || !kPair)) return fail(B200_EUNSUPPORTED, "a second operand pair needs K-contiguous operands and the CTA-pair kernel (ctas = 2)");
-  if (k == 0 && k2 > 0) return launch_gemm<TIn, TOut, kNT, P>(m, n, k2, A2, ldA2, B2, ldB2, C, ldC, stream_v);
+  if (k == 0 && k2 > 0) return launch_gemm_bn<TIn, TOut, kNT, P, kBN>(m, n, k2, A2, ldA2, B2, ldB2, C, ldC, stream_v, 0, nullptr, 0, nullptr, 0);
   if (k == 0) {
     CUDA_TRY(cudaMemset2DAsync(C, static_cast<size_t>(ldC) * sizeof(TOut), 0, static_cast<size_t>(m) * sizeof(TOut), n, stream));
     return B200_OK;
