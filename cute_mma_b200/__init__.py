@@ -11,9 +11,18 @@ from .ops import (  # noqa: F401
     gemm_tn,
     library_path,
     load_library,
+    gemm_rowmajor,
+    gemm_tn_acc2,
+    kernel_info,
+    lora_tn,
+    oft_plan,
     oft_tn,
+    oft_tn_a_rw,
     oft_tn_host,
+    oft_tn_static,
+    oft_tn_two_pass,
+    rotate,
     shard_range,
     tile_coord,
-    kernel_info,
+    transform_weight,
 )
