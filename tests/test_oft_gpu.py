@@ -362,6 +362,29 @@ def test_oft_large_full_size_sampled_and_routes_agree(lib, cuda):
     assert torch.equal(c_auto.view(torch.int16), c_fused.view(torch.int16))
 
 
+@pytest.mark.parametrize("m,n,k,b,gs,pad", [(200, 328, 192, 64, None, 0), (5000, 512, 256, 32, None, 8), (4200, 512, 128, 8, 256, 0)])
+def test_host_buffer_entry_point_matches_device_path(lib, cuda, m, n, k, b, gs, pad):
+    """b200_oft_tn_f16_host (pageable numpy buffers here; several row chunks when M exceeds 2048, the chunks'
+    uploads, products and downloads on three streams) returns the bits of the device entry point, with padded
+    host leading dimensions and with the padding of C untouched."""
+    A, R, B = make_oft_case(m, n, k, b, gs, seed=41)
+    dev = run_oft(lib, cuda, A, R, B, m, n, k, b, gs)
+
+    def padded(x):
+        out = np.full((x.shape[0], x.shape[1] + pad), np.float16(3.0))
+        out[:, : x.shape[1]] = x
+        return np.ascontiguousarray(out.astype(np.float16))
+
+    hA, hB, hR = padded(A), padded(B), padded(R)
+    hC = np.full((m, n + pad), np.float16(-7.0), dtype=np.float16)
+    ops.oft_tn_host(m, n, k, hA, k + pad, hB, k + pad, hR, k + pad, hC, n + pad, group_size=gs, reconn_sz=b, lib=lib)
+    assert ops.device_status(lib)[0] == 0
+    assert np.array_equal(hC[:, :n].view(np.uint16), dev.view(np.uint16))
+    assert np.all(hC[:, n:] == np.float16(-7.0))
+    if m <= 512:
+        assert oft_ok(hC[:, :n], oracle_full(A, R, B, m, n, k, b, gs))[0] == 0
+
+
 def test_bounded_wait_reports_and_recovers(lib, cuda):
     """A wait that runs out is reported through the status record and leaves the context usable
     (no trap, no fault): the self-test waits 2 ms on a barrier nothing sets."""
