@@ -209,29 +209,12 @@ template <typename TIn, typename TOut, bool kNT, class P, int kBN>
 int launch_gemm_bn(int m, int n, int k, const void* A, int ldA, const void* B, int ldB, void* C, int ldC, void* stream_v,
                    int k2, const void* A2, int ldA2, const void* B2, int ldB2);
 
-// The tile is bM x bN of the configuration, except that the pair kernel also exists with half the N extent for
-// problems of at most half a wave of full-width tiles, where twice as many SM pairs get work.  A half-width tile
-// takes 0.8 of the time of a full one (measured at M = N = K = 4096, TF32: 512 half-width tiles in 7 waves
-// 0.286 ms, 256 full-width tiles in 4 waves 0.203 ms), so it never pays for evening out the last wave of a
-// larger problem.
+// (A pair kernel with half the N extent was tried for evening out the last wave of tiles and for small problems:
+// a half-width tile takes 0.8 of the time of a full one, M = N = K = 4096 TF32 0.286 ms against 0.203 ms, so it
+// never pays; the tiles of a short last wave are split along K instead, see below.)
 template <typename TIn, typename TOut, bool kNT, class P>
 int launch_gemm(int m, int n, int k, const void* A, int ldA, const void* B, int ldB, void* C, int ldC, void* stream_v,
                 int k2 = 0, const void* A2 = nullptr, int ldA2 = 0, const void* B2 = nullptr, int ldB2 = 0) {
-  constexpr bool kPair = CtasOf<P>::value == 2;
-  if constexpr (kPair && P::bN == 256) {
-    int narrow = 0;
-    if (const char* e = std::getenv("B200_GEMM_BN")) {
-      narrow = std::atoi(e) == 128;
-    } else if (m > 0 && n > 0) {
-      int dev = 0, sms = 148;
-      if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-      const long long pairs = sms / 2 > 0 ? sms / 2 : 1;
-      const long long t_wide = static_cast<long long>((m + 255) / 256) * ((n + 255) / 256), t_narrow = static_cast<long long>((m + 255) / 256) * ((n + 127) / 128);
-      const double wide = static_cast<double>((t_wide + pairs - 1) / pairs), half = 0.8 * static_cast<double>((t_narrow + pairs - 1) / pairs);
-      narrow = half < 0.97 * wide;
-    }
-    if (narrow) return launch_gemm_bn<TIn, TOut, kNT, P, 128>(m, n, k, A, ldA, B, ldB, C, ldC, stream_v, k2, A2, ldA2, B2, ldB2);
-  }
   return launch_gemm_bn<TIn, TOut, kNT, P, P::bN>(m, n, k, A, ldA, B, ldB, C, ldC, stream_v, k2, A2, ldA2, B2, ldB2);
 }
 
@@ -288,16 +271,56 @@ int launch_gemm_bn(int m, int n, int k, const void* A, int ldA, const void* B, i
     auto pick = [](char c) { return c == 'f' ? kL2EvictFirst : (c == 'l' ? kL2EvictLast : kL2EvictNormal); };
     if (e[0] && e[1]) { hint_a = pick(e[0]); hint_b = pick(e[1]); }
   }
-  GemmArgs args{m, n, k, C, ldC, st->status, raster, tile_sync, rounds, a3d, b3d, hint_a, hint_b, k2};
+  GemmArgs args{m, n, k, C, ldC, st->status, raster, tile_sync, rounds, a3d, b3d, hint_a, hint_b, k2, 0u, 1, nullptr, nullptr};
   if constexpr (kPair) {
     CUtensorMap ma2 = ma, mb2 = mb;  // never read when k2 == 0
     if (k2 > 0) {
       if (int rc = make_map(&ma2, A2, sizeof(TIn), k2, m, ldA2, T1::kBK, T1::kBM, "A2")) return rc;
       if (int rc = make_map(&mb2, B2, sizeof(TIn), k2, n, ldB2, T1::kBK, kBoxN, "B2")) return rc;
     }
+    const long long tiles = static_cast<long long>((m + 2 * T2::kBM - 1) / (2 * T2::kBM)) * ((n + T2::kBN - 1) / T2::kBN);
+    // Split along K for problems of at most half a wave of tiles.  With P SM pairs and T <= P / 2 tiles, every
+    // tile is cut into s = P / T pieces along K (at most 4, at least 8 K steps each) that run on otherwise idle
+    // pairs and are summed by whichever piece of a tile finishes last (fp32 partial tiles in pool scratch, summed
+    // in piece order: deterministic; no CTA waits for another).  Measured: M = N = 1024, K = 8192 fp16 49 -> 37 us.
+    // Evening out the last wave of a larger problem the same way gained nothing (M = N = K = 4096 TF32: 0.2020
+    // against 0.2031 ms; the reduction and the shorter K pipelines eat the saved half wave), so only problems
+    // without a full wave are split.  B200_GEMM_SPLIT=0 disables it.
+    const long long all_pairs = st->sm_count / 2;
+    const long long full_waves = tiles / all_pairs, rest = tiles % all_pairs;
+    const long long k_steps_all = (k + T2::kBK - 1) / T2::kBK + (k2 + T2::kBK - 1) / T2::kBK;
+    long long parts = (rest > 0 && rest * 2 <= all_pairs && full_waves == 0 && !big && st->pool) ? all_pairs / rest : 1;
+    if (parts > 4) parts = 4;
+    if (parts > k_steps_all / 8) parts = k_steps_all / 8;
+    if (const char* e = std::getenv("B200_GEMM_SPLIT")) {
+      if (std::atoi(e) == 0) parts = 1;
+    }
+    if (parts >= 2) {
+      void* scratch = nullptr;
+      const size_t tile_floats = static_cast<size_t>(T2::kBM) * T2::kBN;
+      const size_t count_bytes = (static_cast<size_t>(rest) * 2 * sizeof(int) + 255) & ~static_cast<size_t>(255);
+      const size_t bytes = count_bytes + static_cast<size_t>(rest) * parts * 2 * tile_floats * sizeof(float);
+      if (cudaMallocFromPoolAsync(&scratch, bytes, st->pool, stream) == cudaSuccess) {
+        CUDA_TRY(cudaMemsetAsync(scratch, 0, count_bytes, stream));
+        args.split_first = static_cast<unsigned>(tiles - rest);
+        args.split_parts = static_cast<int>(parts);
+        args.split_count = static_cast<int*>(scratch);
+        args.split_scratch = reinterpret_cast<float*>(static_cast<unsigned char*>(scratch) + count_bytes);
+        auto kernel = gemm2_kernel<T2, true>;
+        if (int rc = opt_in_smem(kernel, T2::kSmemBytes)) return rc;
+        const long long items = tiles - rest + rest * parts;
+        const int pairs = static_cast<int>(items < all_pairs ? items : all_pairs);
+        kernel<<<2 * pairs, T2::kThreads, T2::kSmemBytes, stream>>>(ma, mb, ma2, mb2, args);
+        const cudaError_t launched = cudaGetLastError();
+        cudaFreeAsync(scratch, stream);
+        release_round_counters(st, stream, rounds);
+        CUDA_TRY(launched);
+        return B200_OK;
+      }
+      cudaGetLastError();  // no scratch: the plain schedule
+    }
     auto kernel = gemm2_kernel<T2>;
     if (int rc = opt_in_smem(kernel, T2::kSmemBytes)) return rc;
-    const long long tiles = static_cast<long long>((m + 2 * T2::kBM - 1) / (2 * T2::kBM)) * ((n + T2::kBN - 1) / T2::kBN);
     const int pairs = static_cast<int>(tiles < st->sm_count / 2 ? tiles : st->sm_count / 2);
     kernel<<<2 * pairs, T2::kThreads, T2::kSmemBytes, stream>>>(ma, mb, ma2, mb2, args);  // cluster dimension (2,1,1) is part of the kernel
   } else {

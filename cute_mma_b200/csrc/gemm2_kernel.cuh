@@ -47,7 +47,7 @@ struct Gemm2Traits {
   static_assert(kSmemBytes <= 232448, "shared memory ring too large");
 };
 
-template <class T>
+template <class T, bool kSplit = false>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(T::kThreads, 1)
 gemm2_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
              const __grid_constant__ CUtensorMap tmap_a2, const __grid_constant__ CUtensorMap tmap_b2, const GemmArgs args) {
@@ -75,6 +75,17 @@ gemm2_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__
   // C = A.B^T + A2.B2^T: the K steps of the second pair simply follow those of the first in every tile's stream
   const int k_steps1 = (args.k + T::kBK - 1) / T::kBK;
   const int k_steps = k_steps1 + (args.k2 + T::kBK - 1) / T::kBK;
+  // Work items.  Without the split an item is a tile over all K steps.  With it, the tiles from args.split_first
+  // on (all of them for a problem smaller than half a wave) are cut into args.split_parts pieces along K so that
+  // idle SM pairs share them; the pieces meet in the epilogue (no CTA ever waits for another one).
+  const unsigned num_items = kSplit ? args.split_first + (num_tiles - args.split_first) * args.split_parts : num_tiles;
+  auto item_tile = [&](unsigned item) -> unsigned {
+    if (!kSplit || item < args.split_first) return item;
+    return args.split_first + (item - args.split_first) / args.split_parts;
+  };
+  auto item_part = [&](unsigned item) -> int { return (!kSplit || item < args.split_first) ? 0 : static_cast<int>((item - args.split_first) % args.split_parts); };
+  auto item_ks0 = [&](unsigned item) -> int { return (!kSplit || item < args.split_first) ? 0 : item_part(item) * k_steps / args.split_parts; };
+  auto item_ks1 = [&](unsigned item) -> int { return (!kSplit || item < args.split_first) ? k_steps : (item_part(item) + 1) * k_steps / args.split_parts; };
 
   if (threadIdx.x == 0) {
     *abort_flag = 0;
@@ -102,7 +113,8 @@ gemm2_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__
       uint32_t it = 0;
       bool ok = true;
       unsigned done_rounds = 0, sync_target = 0;
-      for (unsigned tile = pair; ok && tile < num_tiles; tile += num_pairs) {
+      for (unsigned item = pair; ok && item < num_items; item += num_pairs) {
+        const unsigned tile = item_tile(item);
         if (args.tile_sync && done_rounds > 0) {
           if (!(ok = tile_round_sync(args.rounds + rank, sync_target, ctx, 5))) break;
         }
@@ -115,7 +127,7 @@ gemm2_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__
         tile_coord_r(args.raster, tiles_m, tiles_n, tile, tm, tn);
         const int m0 = tm * 2 * T::kBM + rank * T::kBM;      // this CTA's rows of A and C
         const int n0 = tn * T::kBN + rank * T::kBNHalf;      // this CTA's half of the B tile
-        for (int ks = 0; ks < k_steps; ++ks, ++it) {
+        for (int ks = item_ks0(item), ks_end = item_ks1(item); ks < ks_end; ++ks, ++it) {
           const int s = it % T::kStages;
           if (!(ok = mbar_wait(empty_bar(s), ((it / T::kStages) & 1) ^ 1, ctx, 1))) break;
 #ifdef B200_DEBUG_NO_TMA  // timing experiment only: the ring is never filled, results are garbage
@@ -167,8 +179,13 @@ gemm2_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__
       const uint64_t a_desc0 = umma_desc_sw128(smem_base, a_lbo, T::kA32Atom ? 512 : 1024, T::kA32Atom ? 1 : 2);
       const uint64_t b_desc0 = umma_desc_sw128(smem_base + T::kABytes, b_lbo, T::kB32Atom ? 512 : 1024, T::kB32Atom ? 1 : 2);
       unsigned my_tiles = 0;
-      if (pair < num_tiles) my_tiles = (num_tiles - pair + num_pairs - 1) / num_pairs;
-      const uint32_t total = my_tiles * static_cast<uint32_t>(k_steps);
+      if (pair < num_items) my_tiles = (num_items - pair + num_pairs - 1) / num_pairs;
+      uint32_t total = my_tiles * static_cast<uint32_t>(k_steps);
+      int steps_this = k_steps;  // K steps of the item being multiplied
+      if constexpr (kSplit) {
+        total = 0;
+        for (unsigned item = pair; item < num_items; item += num_pairs) total += static_cast<uint32_t>(item_ks1(item) - item_ks0(item));
+      }
       const uint32_t full0 = full_bar(0), empty0 = empty_bar(0);
       uint32_t phase = 0, tcount = 0, d_tmem = tmem_base;
       int ks = 0;
@@ -184,6 +201,10 @@ gemm2_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__
             const int a = tcount % T::kAccBufs;
             if (!(ok = mbar_wait(accempty_bar(a), ((tcount / T::kAccBufs) & 1) ^ 1, ctx, 2))) break;
             d_tmem = tmem_base + a * T::kBN;
+            if constexpr (kSplit) {
+              const unsigned item = pair + tcount * num_pairs;
+              steps_this = item_ks1(item) - item_ks0(item);
+            }
           }
           if (!have_full && !(ok = mbar_wait(full0 + 8 * s, phase, ctx, 3))) break;
           tc_fence_after();
@@ -198,7 +219,7 @@ gemm2_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__
             else umma_tf32_ss_pair(d_tmem, a_desc, b_desc, idesc, acc);
           }
           umma_commit_pair(empty0 + 8 * s, 3);  // frees the stage in both CTAs
-          if (++ks == k_steps) {
+          if (++ks == (kSplit ? steps_this : k_steps)) {
             umma_commit_pair(accfull_bar(tcount % T::kAccBufs), 3);
             ks = 0;
             ++tcount;
@@ -219,7 +240,8 @@ gemm2_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__
     uint32_t tcount = 0;
     bool ok = true;
     TOut* __restrict__ C = reinterpret_cast<TOut*>(args.C);
-    for (unsigned tile = pair; ok && tile < num_tiles; tile += num_pairs, ++tcount) {
+    for (unsigned item = pair; ok && item < num_items; item += num_pairs, ++tcount) {
+      const unsigned tile = item_tile(item);
       unsigned tm, tn;
       tile_coord_r(args.raster, tiles_m, tiles_n, tile, tm, tn);
       const int a = tcount % T::kAccBufs;
@@ -227,6 +249,69 @@ gemm2_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__
       tc_fence_after();
       const int row = tm * 2 * T::kBM + rank * T::kBM + quad * 32 + lane;
       const uint32_t t_row = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + a * T::kBN;
+      if constexpr (kSplit) {
+        if (item >= args.split_first) {
+          // A piece of a split tile: park the fp32 partial tile (groups of four columns per row, so a thread moves
+          // 16 bytes and a warp 512 contiguous bytes), count this CTA's arrival, and if it is the last of the tile's
+          // pieces add all of them up in piece order (every run gives the same bits whoever comes last) and write C.
+          const unsigned sidx = tile - args.split_first;
+          const int part = item_part(item), parts = args.split_parts;  // parts <= 4
+          const int r_in_cta = quad * 32 + lane;
+          constexpr size_t kTileFloats = static_cast<size_t>(T::kBM) * T::kBN;
+          float4* mine = reinterpret_cast<float4*>(args.split_scratch + ((static_cast<size_t>(sidx) * parts + part) * 2 + rank) * kTileFloats);
+#pragma unroll 1
+          for (int c = 0; c < T::kBN / 32; ++c) {
+            uint32_t v[32];
+            tmem_ld_x32(t_row + c * 32, v);
+            tmem_wait_ld();
+#pragma unroll
+            for (int g = 0; g < 8; ++g)
+              mine[(c * 8 + g) * T::kBM + r_in_cta] = make_float4(__uint_as_float(v[4 * g]), __uint_as_float(v[4 * g + 1]),
+                                                                  __uint_as_float(v[4 * g + 2]), __uint_as_float(v[4 * g + 3]));
+          }
+          tc_fence_before();
+          mbar_arrive_cluster(mapa_shared(accempty_bar(a), 0));  // the accumulator is free again
+          __threadfence();
+          named_barrier_sync(1, 128);
+          volatile int* arrivals = reinterpret_cast<volatile int*>(tmem_slot + 2);
+          if (warp == 2 && lane == 0) *arrivals = atomicAdd(args.split_count + sidx * 2 + rank, 1);
+          named_barrier_sync(1, 128);
+          const bool last = (*arrivals == parts - 1);
+          named_barrier_sync(1, 128);  // everyone has read the count before the next item may overwrite it
+          if (last) {
+            __threadfence();
+            const float4* base = reinterpret_cast<const float4*>(args.split_scratch + (static_cast<size_t>(sidx) * parts * 2 + rank) * kTileFloats);
+            constexpr size_t kPartStride = 2 * kTileFloats / 4;  // float4s between two pieces of one CTA's half tile
+            if (row < args.m) {
+#pragma unroll 1
+              for (int g0 = 0; g0 < T::kBN / 4; g0 += 8) {  // 8 column groups x up to 4 pieces: 32 independent 16-byte loads
+                float4 x[4][8];
+#pragma unroll
+                for (int q = 0; q < 4; ++q)
+#pragma unroll
+                  for (int g = 0; g < 8; ++g)
+                    x[q][g] = (q < parts) ? __ldcg(base + q * kPartStride + (g0 + g) * T::kBM + r_in_cta) : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+                for (int g = 0; g < 8; ++g) {
+                  float4 sum = x[0][g];
+#pragma unroll
+                  for (int q = 1; q < 4; ++q) { sum.x += x[q][g].x; sum.y += x[q][g].y; sum.z += x[q][g].z; sum.w += x[q][g].w; }
+                  const float o[4] = {sum.x, sum.y, sum.z, sum.w};
+#pragma unroll
+                  for (int e = 0; e < 4; ++e) {
+                    const int gcol = tn * T::kBN + (g0 + g) * 4 + e;
+                    if (gcol < args.n) {
+                      if constexpr (sizeof(TOut) == 2) C[row + static_cast<long long>(gcol) * args.ldC] = __float2half_rn(o[e]);
+                      else C[row + static_cast<long long>(gcol) * args.ldC] = o[e];
+                    }
+                  }
+                }
+              }
+            }
+          }
+          continue;
+        }
+      }
 #ifdef B200_EXP_NO_EPI  // timing experiment: the accumulator is never read or stored
       (void)row; (void)t_row; (void)C; (void)tm; (void)tn;
       if (false)

@@ -52,6 +52,12 @@ struct GemmArgs {
   int a3d, b3d;  // MN-major operand described by a 3-D map (chunk, K, chunk index): one copy per tile instead of one per chunk
   unsigned long long hint_a, hint_b;  // L2 eviction priority of the K-major tile loads of A and B (pair kernel)
   int k2;  // pair kernel, K-major operands: columns of a second operand pair (A2, B2) accumulated into the same C; 0 = none
+  // pair kernel, split instance: tiles from split_first on are cut into split_parts pieces along K; every piece
+  // leaves its fp32 partial tile in split_scratch and the last piece of a tile to finish (split_count) sums them
+  unsigned split_first;
+  int split_parts;
+  float* split_scratch;
+  int* split_count;
 };
 
 template <class T>
