@@ -189,6 +189,25 @@ int common_dims(int m, int n, int k, const void* A, const void* B, void* C) {
 template <class P, class = void> struct CtasOf { static constexpr int value = 1; };
 template <class P> struct CtasOf<P, decltype((void)P::ctas)> { static constexpr int value = P::ctas; };
 
+// Launch of a phase-locked persistent kernel.  Its CTAs wait for one another between tile rounds, which is only
+// safe when all of them are resident at once; a cooperative launch makes the device start them together (or not
+// at all) even when other work holds some SMs.  If the cooperative launch is refused the caller launches again
+// without the phase lock.
+template <class Kernel, class... Args>
+cudaError_t launch_cooperative(Kernel kernel, int grid, int threads, int smem, cudaStream_t stream, Args... args) {
+  cudaLaunchConfig_t cfg{};
+  cfg.gridDim = dim3(static_cast<unsigned>(grid));
+  cfg.blockDim = dim3(static_cast<unsigned>(threads));
+  cfg.dynamicSmemBytes = static_cast<size_t>(smem);
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeCooperative;
+  attr[0].val.cooperative = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, kernel, args...);
+}
+
 // Counters of the cross-CTA phase lock.  Each launch gets its own four, stream-ordered from the library's pool, so
 // that launches on different streams never share them; the entry point that must not allocate uses the four
 // that follow the status record in its static scratch (its calls may not overlap anyway).
@@ -322,7 +341,15 @@ int launch_gemm_bn(int m, int n, int k, const void* A, int ldA, const void* B, i
     auto kernel = gemm2_kernel<T2>;
     if (int rc = opt_in_smem(kernel, T2::kSmemBytes)) return rc;
     const int pairs = static_cast<int>(tiles < st->sm_count / 2 ? tiles : st->sm_count / 2);
-    kernel<<<2 * pairs, T2::kThreads, T2::kSmemBytes, stream>>>(ma, mb, ma2, mb2, args);  // cluster dimension (2,1,1) is part of the kernel
+    bool launched_coop = false;
+    if (args.tile_sync) {
+      launched_coop = launch_cooperative(kernel, 2 * pairs, T2::kThreads, T2::kSmemBytes, stream, ma, mb, ma2, mb2, args) == cudaSuccess;
+      if (!launched_coop) {
+        cudaGetLastError();
+        args.tile_sync = 0;
+      }
+    }
+    if (!launched_coop) kernel<<<2 * pairs, T2::kThreads, T2::kSmemBytes, stream>>>(ma, mb, ma2, mb2, args);  // cluster dimension (2,1,1) is part of the kernel
   } else {
     auto kernel = gemm_kernel<T1>;
     if (int rc = opt_in_smem(kernel, T1::kSmemBytes)) return rc;
@@ -390,7 +417,15 @@ int launch_oft_gt(int m, int n, int k, int group_size, const void* A, int ldA, c
     auto kernel = oft2_kernel<T>;
     if (int rc = opt_in_smem(kernel, T::kSmemBytes)) return rc;
     const int pairs = static_cast<int>(tiles < st->sm_count / 2 ? tiles : st->sm_count / 2);
-    kernel<<<2 * pairs, T::kThreads, T::kSmemBytes, stream>>>(ma, mr, mb, args);  // cluster dimension (2,1,1) is part of the kernel
+    bool launched_coop = false;
+    if (args.tile_sync) {
+      launched_coop = launch_cooperative(kernel, 2 * pairs, T::kThreads, T::kSmemBytes, stream, ma, mr, mb, args) == cudaSuccess;
+      if (!launched_coop) {
+        cudaGetLastError();
+        args.tile_sync = 0;
+      }
+    }
+    if (!launched_coop) kernel<<<2 * pairs, T::kThreads, T::kSmemBytes, stream>>>(ma, mr, mb, args);  // cluster dimension (2,1,1) is part of the kernel
   } else {
     auto kernel = oft_kernel<T>;
     if (int rc = opt_in_smem(kernel, T::kSmemBytes)) return rc;
