@@ -807,8 +807,8 @@ int b200_oft_tn_f16_host(int m, int n, int k, int group_size, int reconn_sz, con
   if (int rc = stage_reserve(st, 3, static_cast<size_t>(m) * np * 2 + 16)) return rc;
   // Rows of X go up, are multiplied and come back chunk by chunk on three streams, so that the upload of chunk
   // i + 1, the product of chunk i and the download of chunk i - 1 overlap (the link is full duplex and the
-  // download of Y is the longest leg: 3.76 GB against 1.55 GB up at M 65536, K 8192, N 28672).  W and R go up
-  // first.  Results do not depend on the chunking: a row of Y only ever sees its own row of X.
+  // download of Y is the longest leg: 3.76 GB against 1.55 GB up at M 65536, K 8192, N 28672).  Results do not
+  // depend on the chunking: an element of Y only ever sees its own row of X and its own column of W.
   constexpr int kMaxChunks = 16;
   int chunk_rows = ((m + kMaxChunks - 1) / kMaxChunks + 255) & ~255;
   if (chunk_rows < 2048) chunk_rows = 2048;
@@ -821,21 +821,61 @@ int b200_oft_tn_f16_host(int m, int n, int k, int group_size, int reconn_sz, con
   };
   for (int i = 0; i <= chunks && rc == B200_OK; ++i) check(cudaEventCreateWithFlags(&up[i], cudaEventDisableTiming), "cudaEventCreate");
   for (int i = 0; i < chunks && rc == B200_OK; ++i) check(cudaEventCreateWithFlags(&done[i], cudaEventDisableTiming), "cudaEventCreate");
-  if (rc == B200_OK && k > 0) {
-    check(cudaMemcpy2DAsync(st->stage[1], kp * 2, B, static_cast<size_t>(ldB) * 2, static_cast<size_t>(k) * 2, n, cudaMemcpyHostToDevice, s_in), "copy of B");
+  // The first row chunk does not wait for all of W: with one N-group, W goes up in kPieces column pieces behind
+  // the first rows of X, and that chunk's product and download run piece by piece, so the download of Y (the
+  // longest leg) starts after a quarter of W instead of all of it.
+  constexpr int kPieces = 4;
+  const bool piecewise = chunks > 1 && k > 0 && group_size == n && n % (kPieces * 256) == 0;
+  cudaEvent_t w_up[kPieces] = {}, w_done[kPieces] = {};
+  if (piecewise)
+    for (int j = 0; j < kPieces && rc == B200_OK; ++j) {
+      check(cudaEventCreateWithFlags(&w_up[j], cudaEventDisableTiming), "cudaEventCreate");
+      if (rc == B200_OK) check(cudaEventCreateWithFlags(&w_done[j], cudaEventDisableTiming), "cudaEventCreate");
+    }
+  auto upload_rows = [&](int i) {
+    const int r0 = i * chunk_rows, rows = (m - r0) < chunk_rows ? (m - r0) : chunk_rows;
+    if (k > 0)
+      check(cudaMemcpy2DAsync(static_cast<__half*>(st->stage[0]) + static_cast<size_t>(r0) * kp, kp * 2,
+                              static_cast<const __half*>(A) + static_cast<size_t>(r0) * ldA, static_cast<size_t>(ldA) * 2,
+                              static_cast<size_t>(k) * 2, rows, cudaMemcpyHostToDevice, s_in), "copy of A");
+    if (rc == B200_OK) check(cudaEventRecord(up[i], s_in), "cudaEventRecord");
+  };
+  if (rc == B200_OK && k > 0)
     check(cudaMemcpy2DAsync(st->stage[2], kp * 2, R, static_cast<size_t>(ldR) * 2, static_cast<size_t>(k) * 2, r_rows, cudaMemcpyHostToDevice, s_in), "copy of R");
+  if (piecewise && rc == B200_OK) upload_rows(0);
+  if (rc == B200_OK && k > 0) {
+    const int pieces = piecewise ? kPieces : 1, n_piece = n / pieces;
+    for (int j = 0; j < pieces && rc == B200_OK; ++j) {
+      check(cudaMemcpy2DAsync(static_cast<__half*>(st->stage[1]) + static_cast<size_t>(j) * n_piece * kp, kp * 2,
+                              static_cast<const __half*>(B) + static_cast<size_t>(j) * n_piece * ldB, static_cast<size_t>(ldB) * 2,
+                              static_cast<size_t>(k) * 2, n_piece, cudaMemcpyHostToDevice, s_in), "copy of B");
+      if (piecewise && rc == B200_OK) check(cudaEventRecord(w_up[j], s_in), "cudaEventRecord");
+    }
   }
   if (rc == B200_OK) check(cudaEventRecord(up[chunks], s_in), "cudaEventRecord");
-  if (rc == B200_OK) check(cudaStreamWaitEvent(s, up[chunks], 0), "cudaStreamWaitEvent");
   for (int i = 0; i < chunks && rc == B200_OK; ++i) {
     const int r0 = i * chunk_rows, rows = (m - r0) < chunk_rows ? (m - r0) : chunk_rows;
     __half* dA = static_cast<__half*>(st->stage[0]) + static_cast<size_t>(r0) * kp;
     __half* dC = static_cast<__half*>(st->stage[3]) + static_cast<size_t>(r0) * np;
-    if (k > 0)
-      check(cudaMemcpy2DAsync(dA, kp * 2, static_cast<const __half*>(A) + static_cast<size_t>(r0) * ldA, static_cast<size_t>(ldA) * 2,
-                              static_cast<size_t>(k) * 2, rows, cudaMemcpyHostToDevice, s_in), "copy of A");
-    if (rc == B200_OK) check(cudaEventRecord(up[i], s_in), "cudaEventRecord");
+    if (!(piecewise && i == 0)) upload_rows(i);
     if (rc == B200_OK) check(cudaStreamWaitEvent(s, up[i], 0), "cudaStreamWaitEvent");
+    if (piecewise && i == 0) {
+      const int n_piece = n / kPieces;
+      for (int j = 0; j < kPieces && rc == B200_OK; ++j) {
+        check(cudaStreamWaitEvent(s, w_up[j], 0), "cudaStreamWaitEvent");
+        if (rc == B200_OK)
+          rc = oft_dispatch(rows, n_piece, k, n_piece, reconn_sz, dA, kp, static_cast<__half*>(st->stage[1]) + static_cast<size_t>(j) * n_piece * kp, kp,
+                            st->stage[2], kp, dC + static_cast<size_t>(j) * n_piece, np, s);
+        if (rc == B200_OK) check(cudaEventRecord(w_done[j], s), "cudaEventRecord");
+        if (rc == B200_OK) check(cudaStreamWaitEvent(s_out, w_done[j], 0), "cudaStreamWaitEvent");
+        if (rc == B200_OK)
+          check(cudaMemcpy2DAsync(static_cast<__half*>(C) + static_cast<size_t>(r0) * ldC + static_cast<size_t>(j) * n_piece, static_cast<size_t>(ldC) * 2,
+                                  dC + static_cast<size_t>(j) * n_piece, np * 2, static_cast<size_t>(n_piece) * 2, rows, cudaMemcpyDeviceToHost, s_out),
+                "copy of C");
+      }
+      continue;
+    }
+    if (rc == B200_OK) check(cudaStreamWaitEvent(s, up[chunks], 0), "cudaStreamWaitEvent");  // all of W and R
     if (rc == B200_OK) rc = oft_dispatch(rows, n, k, group_size, reconn_sz, dA, kp, st->stage[1], kp, st->stage[2], kp, dC, np, s);
     if (rc == B200_OK) check(cudaEventRecord(done[i], s), "cudaEventRecord");
     if (rc == B200_OK) check(cudaStreamWaitEvent(s_out, done[i], 0), "cudaStreamWaitEvent");
@@ -848,6 +888,7 @@ int b200_oft_tn_f16_host(int m, int n, int k, int group_size, int reconn_sz, con
   cudaError_t e1 = cudaStreamSynchronize(s_in), e2 = cudaStreamSynchronize(s), e3 = cudaStreamSynchronize(s_out);
   for (int i = 0; i <= chunks; ++i) if (up[i]) cudaEventDestroy(up[i]);
   for (int i = 0; i < chunks; ++i) if (done[i]) cudaEventDestroy(done[i]);
+  for (int j = 0; j < kPieces; ++j) { if (w_up[j]) cudaEventDestroy(w_up[j]); if (w_done[j]) cudaEventDestroy(w_done[j]); }
   if (rc != B200_OK) { g_err = keep; return rc; }
   if (!check(e1, "host-to-device stream") || !check(e2, "compute stream") || !check(e3, "device-to-host stream")) return rc;
   return B200_OK;

@@ -362,10 +362,10 @@ def test_oft_large_full_size_sampled_and_routes_agree(lib, cuda):
     assert torch.equal(c_auto.view(torch.int16), c_fused.view(torch.int16))
 
 
-@pytest.mark.parametrize("m,n,k,b,gs,pad", [(200, 328, 192, 64, None, 0), (5000, 512, 256, 32, None, 8), (4200, 512, 128, 8, 256, 0)])
+@pytest.mark.parametrize("m,n,k,b,gs,pad", [(200, 328, 192, 64, None, 0), (5000, 512, 256, 32, None, 8), (4200, 512, 128, 8, 256, 0), (4300, 1024, 128, 16, None, 8)])
 def test_host_buffer_entry_point_matches_device_path(lib, cuda, m, n, k, b, gs, pad):
     """b200_oft_tn_f16_host (pageable numpy buffers here; several row chunks when M exceeds 2048, the chunks'
-    uploads, products and downloads on three streams) returns the bits of the device entry point, with padded
+    uploads, products and downloads on three streams, the first chunk piecewise over N when N is a multiple of 1024) returns the bits of the device entry point, with padded
     host leading dimensions and with the padding of C untouched."""
     A, R, B = make_oft_case(m, n, k, b, gs, seed=41)
     dev = run_oft(lib, cuda, A, R, B, m, n, k, b, gs)
