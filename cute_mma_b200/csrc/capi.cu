@@ -294,8 +294,12 @@ int launch_gemm_bn(int m, int n, int k, const void* A, int ldA, const void* B, i
   if constexpr (kPair) {
     CUtensorMap ma2 = ma, mb2 = mb;  // never read when k2 == 0
     if (k2 > 0) {
-      if (int rc = make_map(&ma2, A2, sizeof(TIn), k2, m, ldA2, T1::kBK, T1::kBM, "A2")) return rc;
-      if (int rc = make_map(&mb2, B2, sizeof(TIn), k2, n, ldB2, T1::kBK, kBoxN, "B2")) return rc;
+      int rc = make_map(&ma2, A2, sizeof(TIn), k2, m, ldA2, T1::kBK, T1::kBM, "A2");
+      if (rc == B200_OK) rc = make_map(&mb2, B2, sizeof(TIn), k2, n, ldB2, T1::kBK, kBoxN, "B2");
+      if (rc != B200_OK) {
+        release_round_counters(st, stream, rounds);
+        return rc;
+      }
     }
     const long long tiles = static_cast<long long>((m + 2 * T2::kBM - 1) / (2 * T2::kBM)) * ((n + T2::kBN - 1) / T2::kBN);
     // Split along K for problems of at most half a wave of tiles.  With P SM pairs and T <= P / 2 tiles, every
@@ -326,7 +330,11 @@ int launch_gemm_bn(int m, int n, int k, const void* A, int ldA, const void* B, i
         args.split_count = static_cast<int*>(scratch);
         args.split_scratch = reinterpret_cast<float*>(static_cast<unsigned char*>(scratch) + count_bytes);
         auto kernel = gemm2_kernel<T2, true>;
-        if (int rc = opt_in_smem(kernel, T2::kSmemBytes)) return rc;
+        if (int rc = opt_in_smem(kernel, T2::kSmemBytes)) {
+          cudaFreeAsync(scratch, stream);
+          release_round_counters(st, stream, rounds);
+          return rc;
+        }
         const long long items = tiles - rest + rest * parts;
         const int pairs = static_cast<int>(items < all_pairs ? items : all_pairs);
         kernel<<<2 * pairs, T2::kThreads, T2::kSmemBytes, stream>>>(ma, mb, ma2, mb2, args);
