@@ -182,6 +182,31 @@ def test_lora_matches_three_gemm_reference(lib, cuda, pair_build, m, n, k, r):
     assert np.all(np.abs(got - ref) <= 2e-3 * (np.abs(ref) + 1)), float(np.abs(got - ref).max())
 
 
+def test_phase_locked_gemms_on_two_streams(lib, cuda, pair_build):
+    """Two GEMMs large enough for the cross-CTA phase lock (operand beyond three times L2), launched on two streams
+    without a synchronisation between them: each launch has its own round counters and is started cooperatively,
+    so both finish, report no timed-out wait and return the bits of a launch that ran alone."""
+    import torch
+
+    if not pair_build:
+        pytest.skip("the phase lock is a feature of the CTA-pair kernels")
+    m, n, k = 512, 26624, 8192   # B: 26624 x 8192 fp16 = 416 MB
+    g = torch.Generator(device=cuda).manual_seed(77)
+    dA = (torch.rand((m, k), generator=g, device=cuda) * 2 - 1).to(torch.float16)
+    dB = (torch.rand((n, k), generator=g, device=cuda) * 2 - 1).to(torch.float16)
+    alone = torch.empty((n, m), dtype=torch.float16, device=cuda)
+    ops.gemm_tn(m, n, k, dA, k, dB, k, alone, m, lib=lib)
+    torch.cuda.synchronize()
+    s1, s2 = torch.cuda.Stream(), torch.cuda.Stream()
+    c1, c2 = torch.empty_like(alone), torch.empty_like(alone)
+    for _ in range(3):
+        ops.gemm_tn(m, n, k, dA, k, dB, k, c1, m, s1.cuda_stream, lib=lib)
+        ops.gemm_tn(m, n, k, dA, k, dB, k, c2, m, s2.cuda_stream, lib=lib)
+    torch.cuda.synchronize()
+    assert ops.device_status(lib)[0] == 0
+    assert torch.equal(c1, alone) and torch.equal(c2, alone)
+
+
 def _sampled(lib, cuda, layout, dtype, m, n, k, seed, dist):
     import torch
 
