@@ -274,8 +274,11 @@ int launch_gemm_bn(int m, int n, int k, const void* A, int ldA, const void* B, i
   }
   // Cross-CTA phase lock of the tile rounds and banded tile order (see launch_oft) when the operand that spans
   // N is far larger than L2.  Measured at M 28672, N 65536, K 8192 (fp16): 34.2 ms with neither, 30.0 ms with
-  // bands of 8 tile rows, 25.7 ms with both.  At 8192^3 (128 MB operand) both cost a few per cent, so they stay off.
-  const bool big = kPair && static_cast<long long>(n) * k * static_cast<long long>(sizeof(TIn)) > 3ll * st->l2_bytes;
+  // bands of 8 tile rows, 25.7 ms with both (before the L2 eviction priorities below were added).
+  // The same three measures already pay when the two operands together exceed one and a half times L2 (one-pass
+  // ncu counters, unthrottled launches): 8192^3 fp16 721 -> 689 us and 1.37 -> 0.85 GB of DRAM reads; M 8192,
+  // N 4096, K 8192 354 -> 346 us; 4096 x 16384 x 4096 and below: no difference, so they stay on the z-curve.
+  const bool big = kPair && (static_cast<long long>(m) + n) * k * static_cast<long long>(sizeof(TIn)) > 3ll * st->l2_bytes / 2;
   int tile_sync = big ? 1 : 0;
   if (const char* e = std::getenv("B200_GEMM_TILE_SYNC")) tile_sync = kPair ? std::atoi(e) : 0;
   int* rounds = nullptr;
