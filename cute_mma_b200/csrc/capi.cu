@@ -131,13 +131,11 @@ int make_map(CUtensorMap* map, const void* base, int elem_bytes, long long inner
 }
 
 // Tile order of a launch.  B200_RASTER (integer) overrides it for experiments.
-int raster_for(long long b_bytes, bool oft) {
+int raster_for(long long operand_bytes, bool oft) {
   if (const char* e = std::getenv("B200_RASTER")) return std::atoi(e);
-  // Measured on the GPU: the two orders cost the same cycles, but when B is larger than what L2 keeps
-  // beside the A panels, bands of 8 tile rows move less data, draw less power and so run at a higher
-  // clock under the power cap (OFT slab M 65536, N 3584, K 8192: 668 -> 748 TFLOP/s).  The plain GEMM
-  // at 8192^3 showed no gain and keeps the z-curve.
-  return (oft && b_bytes > (40ll << 20)) ? 8 : 0;
+  // Bands of 8 tile rows for the fused kernel once the operands no longer sit in L2 beside each other (see
+  // launch_oft_gt); the plain GEMM chooses its order in launch_gemm_bn.
+  return (oft && operand_bytes > (40ll << 20)) ? 8 : 0;
 }
 
 // 3-D map over an MN-major matrix [outer = K rows][inner = MN contiguous], inner a multiple of `chunk`:
@@ -402,22 +400,29 @@ int launch_oft_gt(int m, int n, int k, int group_size, const void* A, int ldA, c
   if (int rc = make_map(&ma, A, 2, k, m, ldA, T::kBK, T::kBM, "A")) return rc;
   if (int rc = make_map(&mr, R, 2, k, static_cast<long long>(n_groups) * kB, ldR, T::kBK, kB / kRowsPerCta, "R")) return rc;
   if (int rc = make_map(&mb, B, 2, k, n, ldB, T::kBK, T::kBN / kRowsPerCta / kGT, "B")) return rc;  // one copy per N-group of the tile
-  const int raster = raster_for(static_cast<long long>(n) * k * 2, true);
-  // L2 eviction priorities of the A and B loads.  Keeping the band's rows of A (evict_last) and streaming B
-  // (evict_first) was measured at the large workload: 10 % less DRAM traffic but no gain in time, so both
-  // stay at normal priority.
-  unsigned long long hint_a = kL2EvictNormal, hint_b = kL2EvictNormal;
+  // Tile order, L2 eviction priorities and the cross-CTA phase lock (pair kernel), chosen by the size of the two
+  // operands together, (M + N) K fp16:
+  //  * above 40 MB: bands of 8 tile rows instead of the z-curve (unthrottled launches under ncu, projection shape
+  //    M 16384, K = N 4096, b 64: 438 -> 427 us, DRAM reads 372 -> 344 MB);
+  //  * above 1.5 x L2 also the phase lock (without it the CTAs drift apart by up to a tile time, the panels that
+  //    concurrently running tiles share fall out of L2 before the second reader arrives, and DRAM traffic grew
+  //    to 17x the algorithmic bytes at M 65536, N 28672, K 8192: 650-730 -> 795-820 TFLOP/s with the lock) and
+  //    evict-last for the band's rows of A, evict-first for B, which streams past it.  M = N = K = 8192, group
+  //    256, b 8: 847 us with the bands alone, 835 with the lock, 828 with lock and priorities (DRAM reads
+  //    1.26 -> 1.00 GB); priorities without the lock double the traffic (2.5 GB).  The priorities only when B
+  //    itself exceeds L2: M 65536, N 28672, K 8192, b 128 27.85 -> 27.45 ms and 29.2 -> 22.5 GB of reads, but with
+  //    N 3584 (B 59 MB, resident in L2 anyway) 3.551 -> 3.583 ms.
+  // B200_RASTER, B200_TILE_SYNC and B200_L2_HINTS override each of them.
+  const long long operand_bytes = (static_cast<long long>(m) + n) * k * 2;
+  const bool big = kOftPair && operand_bytes > 3ll * st->l2_bytes / 2;
+  const int raster = raster_for(operand_bytes, true);
+  const bool streams = big && static_cast<long long>(n) * k * 2 > st->l2_bytes;  // B does not fit L2: it streams past the band
+  unsigned long long hint_a = streams ? kL2EvictLast : kL2EvictNormal, hint_b = streams ? kL2EvictFirst : kL2EvictNormal;
   if (const char* e = std::getenv("B200_L2_HINTS")) {  // experiments: two letters out of n/f/l for A and B
     auto pick = [](char c) { return c == 'f' ? kL2EvictFirst : (c == 'l' ? kL2EvictLast : kL2EvictNormal); };
     if (e[0] && e[1]) { hint_a = pick(e[0]); hint_b = pick(e[1]); }
   }
-  // Cross-CTA phase lock of the tile rounds (pair kernel).  Without it the CTAs drift apart by up to a tile
-  // time (~80 us measured), the panels of A and B that concurrently running tiles share fall out of L2
-  // before the second reader arrives, and DRAM traffic grows to 17x the algorithmic bytes at M 65536,
-  // N 28672, K 8192.  Measured there: 5 % more cycles, 20 % less time (the saved DRAM power buys clock
-  // under the power cap).  It costs 5-9 % where B fits L2 a few times over, so it is on only when B
-  // exceeds three times the L2 size.  B200_TILE_SYNC=0/1 overrides.
-  int tile_sync = (kOftPair && static_cast<long long>(n) * k * 2 > 3ll * st->l2_bytes) ? 1 : 0;
+  int tile_sync = big ? 1 : 0;
   if (const char* e = std::getenv("B200_TILE_SYNC")) tile_sync = kOftPair ? std::atoi(e) : 0;
   int* rounds = nullptr;
   if (tile_sync)
