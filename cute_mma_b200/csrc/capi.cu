@@ -3,6 +3,7 @@
 // buffers of the host-buffer entry point).  Takes over the role of the reference's host launchers
 // oft_tn (cute_oft_coop_pc.cu:505-577) and gemm_tn / gemm_nt / gemm (gemm_sm80_tc.cu:95-228, 393-418),
 // with the checks the reference leaves out (shape, alignment, shared-memory opt-in).
+#include <atomic>
 #include <cmath>
 #include <cstdarg>
 #include <cstdio>
@@ -25,6 +26,7 @@
 #include "oft_kernel.cuh"
 #include "oft2_kernel.cuh"
 #include "xr_kernel.cuh"
+#include "oft3_kernel.cuh"
 
 namespace {
 
@@ -41,6 +43,40 @@ int fail(int code, const char* fmt, ...) {
   g_err = buf;
   return code;
 }
+
+// ---- launch options ----------------------------------------------------------------------------------
+// Overrides of the launch heuristics, for experiments and tests.  -1 (or 0 for the route) means "let the
+// library choose".  The B200_* environment variables of the same meaning are read ONCE, at the first use
+// of any option in the process, as initial values; after that only b200_set_option changes them, so
+// nothing on the launch path reads the environment.
+enum OptionId { kOptOftRoute, kOptRaster, kOptTileSync, kOptL2Hints, kOptGemmTileSync, kOptGemmL2Hints, kOptGemmSplit, kOptMaps3d, kOptCount };
+struct OptionDef { const char* name; const char* env; int initial; };
+constexpr OptionDef kOptionDefs[kOptCount] = {
+    {"oft_route", "B200_OFT_PATH", 0},            // 0 choose, 1 X.R in tensor memory per tile, 2 two passes, 3 X.R shared through the L2 ring
+    {"raster", "B200_RASTER", -1},                // tile order: 0 z-curve, g > 0 bands of g tile rows
+    {"tile_sync", "B200_TILE_SYNC", -1},          // cross-CTA phase lock of the fused kernels
+    {"l2_hints", "B200_L2_HINTS", -1},            // 10 * a + b, a / b = 0 normal, 1 evict-first, 2 evict-last for the A / B loads
+    {"gemm_tile_sync", "B200_GEMM_TILE_SYNC", -1},
+    {"gemm_l2_hints", "B200_GEMM_L2_HINTS", -1},
+    {"gemm_split", "B200_GEMM_SPLIT", -1},        // 0: never split small problems along K
+    {"maps_3d", "B200_MAPS_3D", -1},              // 0: one 2-D copy per 128-byte chunk of an MN-major tile
+};
+std::atomic<int> g_opt[kOptCount];
+std::once_flag g_opt_once;
+void options_init() {
+  std::call_once(g_opt_once, [] {
+    for (int i = 0; i < kOptCount; ++i) {
+      int v = kOptionDefs[i].initial;
+      if (const char* e = std::getenv(kOptionDefs[i].env)) v = std::atoi(e);
+      g_opt[i].store(v);
+    }
+  });
+}
+int opt(OptionId id) {
+  options_init();
+  return g_opt[id].load(std::memory_order_relaxed);
+}
+unsigned long long hint_word(int code) { return code == 1 ? b200::kL2EvictFirst : (code == 2 ? b200::kL2EvictLast : b200::kL2EvictNormal); }
 
 #define CUDA_TRY(call)                                                                       \
   do {                                                                                       \
@@ -72,6 +108,24 @@ using EncodeFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, voi
                               const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
                               CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
 EncodeFn g_encode = nullptr;
+std::mutex g_encode_mu;  // the allocating and the non-allocating set-up paths both look the entry point up
+
+int resolve_encode() {
+  std::lock_guard<std::mutex> lock(g_encode_mu);
+  if (g_encode) return B200_OK;
+  void* fn = nullptr;
+  cudaDriverEntryPointQueryResult q;
+  if (cudaError_t e = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &q)) {
+    g_err = std::string("cudaGetDriverEntryPoint failed: ") + cudaGetErrorString(e);
+    return B200_ECUDA;
+  }
+  if (q != cudaDriverEntryPointSuccess || !fn) {
+    g_err = "cuTensorMapEncodeTiled not available from the driver";
+    return B200_ECUDA;
+  }
+  g_encode = reinterpret_cast<EncodeFn>(fn);
+  return B200_OK;
+}
 
 int device_state(DeviceState** out) {
   int dev = 0;
@@ -99,13 +153,7 @@ int device_state(DeviceState** out) {
     CUDA_TRY(cudaMemPoolCreate(&st.pool, &props));
     unsigned long long keep = ~0ull;
     CUDA_TRY(cudaMemPoolSetAttribute(st.pool, cudaMemPoolAttrReleaseThreshold, &keep));
-    if (!g_encode) {
-      void* fn = nullptr;
-      cudaDriverEntryPointQueryResult q;
-      CUDA_TRY(cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &q));
-      if (q != cudaDriverEntryPointSuccess || !fn) return fail(B200_ECUDA, "cuTensorMapEncodeTiled not available from the driver");
-      g_encode = reinterpret_cast<EncodeFn>(fn);
-    }
+    if (int rc = resolve_encode()) return rc;
     st.ready = true;
   }
   *out = &st;
@@ -130,9 +178,9 @@ int make_map(CUtensorMap* map, const void* base, int elem_bytes, long long inner
   return B200_OK;
 }
 
-// Tile order of a launch.  B200_RASTER (integer) overrides it for experiments.
+// Tile order of a launch.  The "raster" option overrides it for experiments.
 int raster_for(long long operand_bytes, bool oft) {
-  if (const char* e = std::getenv("B200_RASTER")) return std::atoi(e);
+  if (opt(kOptRaster) >= 0) return opt(kOptRaster);
   // Bands of 8 tile rows for the fused kernel once the operands no longer sit in L2 beside each other (see
   // launch_oft_gt); the plain GEMM chooses its order in launch_gemm_bn.
   return (oft && operand_bytes > (40ll << 20)) ? 8 : 0;
@@ -263,8 +311,8 @@ int launch_gemm_bn(int m, int n, int k, const void* A, int ldA, const void* B, i
     if (int rc = make_map(&ma, A, sizeof(TIn), k, m, ldA, T1::kBK, T1::kBM, "A")) return rc;
     if (int rc = make_map(&mb, B, sizeof(TIn), k, n, ldB, T1::kBK, kBoxN, "B")) return rc;
   } else {     // M / N contiguous: all 128-byte column chunks of a tile with one 3-D copy when the extent is
-               // a whole number of chunks (B200_NO_3D_MAPS=1 keeps the per-chunk 2-D copies), else one copy per chunk
-    const bool try3d = std::getenv("B200_NO_3D_MAPS") == nullptr;
+               // a whole number of chunks (option maps_3d = 0 keeps the per-chunk 2-D copies), else one copy per chunk
+    const bool try3d = opt(kOptMaps3d) != 0;
     if (try3d && make_map_chunks(&ma, A, sizeof(TIn), m, k, ldA, T1::kChunk, T1::kBK, T1::kBM / T1::kChunk, T1::kA32Atom) == B200_OK) a3d = 1;
     else if (int rc = make_map(&ma, A, sizeof(TIn), m, k, ldA, T1::kChunk, T1::kBK, "A", T1::kA32Atom)) return rc;
     if (try3d && make_map_chunks(&mb, B, sizeof(TIn), n, k, ldB, T1::kChunk, T1::kBK, kBoxN / T1::kChunk, T1::kB32Atom) == B200_OK) b3d = 1;
@@ -278,19 +326,16 @@ int launch_gemm_bn(int m, int n, int k, const void* A, int ldA, const void* B, i
   // N 4096, K 8192 354 -> 346 us; 4096 x 16384 x 4096 and below: no difference, so they stay on the z-curve.
   const bool big = kPair && (static_cast<long long>(m) + n) * k * static_cast<long long>(sizeof(TIn)) > 3ll * st->l2_bytes / 2;
   int tile_sync = big ? 1 : 0;
-  if (const char* e = std::getenv("B200_GEMM_TILE_SYNC")) tile_sync = kPair ? std::atoi(e) : 0;
+  if (opt(kOptGemmTileSync) >= 0) tile_sync = kPair ? opt(kOptGemmTileSync) : 0;
   int* rounds = nullptr;
   if (tile_sync)
     if (int rc = round_counters(st, stream, &rounds)) return rc;
   int raster = raster_for(static_cast<long long>(n) * k * sizeof(TIn), false);
-  if (big && !std::getenv("B200_RASTER")) raster = 8;
+  if (big && opt(kOptRaster) < 0) raster = 8;
   // With the bands, the band's panel of A is what later waves read again and B streams past once per band:
   // A is loaded evict-last, B evict-first.  Same shape: DRAM reads 26.2 -> 17.6 GB per launch, 23.9 -> 22.4 ms.
   unsigned long long hint_a = big ? kL2EvictLast : kL2EvictNormal, hint_b = big ? kL2EvictFirst : kL2EvictNormal;
-  if (const char* e = std::getenv("B200_GEMM_L2_HINTS")) {  // experiments: two letters out of n/f/l for A and B
-    auto pick = [](char c) { return c == 'f' ? kL2EvictFirst : (c == 'l' ? kL2EvictLast : kL2EvictNormal); };
-    if (e[0] && e[1]) { hint_a = pick(e[0]); hint_b = pick(e[1]); }
-  }
+  if (const int h = opt(kOptGemmL2Hints); h >= 0) { hint_a = hint_word(h / 10); hint_b = hint_word(h % 10); }
   GemmArgs args{m, n, k, C, ldC, st->status, raster, tile_sync, rounds, a3d, b3d, hint_a, hint_b, k2, 0u, 1, nullptr, nullptr};
   if constexpr (kPair) {
     CUtensorMap ma2 = ma, mb2 = mb;  // never read when k2 == 0
@@ -309,16 +354,14 @@ int launch_gemm_bn(int m, int n, int k, const void* A, int ldA, const void* B, i
     // in piece order: deterministic; no CTA waits for another).  Measured: M = N = 1024, K = 8192 fp16 49 -> 37 us.
     // Evening out the last wave of a larger problem the same way gained nothing (M = N = K = 4096 TF32: 0.2020
     // against 0.2031 ms; the reduction and the shorter K pipelines eat the saved half wave), so only problems
-    // without a full wave are split.  B200_GEMM_SPLIT=0 disables it.
+    // without a full wave are split.  Option gemm_split = 0 disables it.
     const long long all_pairs = st->sm_count / 2;
     const long long full_waves = tiles / all_pairs, rest = tiles % all_pairs;
     const long long k_steps_all = (k + T2::kBK - 1) / T2::kBK + (k2 + T2::kBK - 1) / T2::kBK;
     long long parts = (rest > 0 && rest * 2 <= all_pairs && full_waves == 0 && !big && st->pool) ? all_pairs / rest : 1;
     if (parts > 4) parts = 4;
     if (parts > k_steps_all / 8) parts = k_steps_all / 8;
-    if (const char* e = std::getenv("B200_GEMM_SPLIT")) {
-      if (std::atoi(e) == 0) parts = 1;
-    }
+    if (opt(kOptGemmSplit) == 0) parts = 1;
     if (parts >= 2) {
       void* scratch = nullptr;
       const size_t tile_floats = static_cast<size_t>(T2::kBM) * T2::kBN;
@@ -412,18 +455,15 @@ int launch_oft_gt(int m, int n, int k, int group_size, const void* A, int ldA, c
   //    1.26 -> 1.00 GB); priorities without the lock double the traffic (2.5 GB).  The priorities only when B
   //    itself exceeds L2: M 65536, N 28672, K 8192, b 128 27.85 -> 27.45 ms and 29.2 -> 22.5 GB of reads, but with
   //    N 3584 (B 59 MB, resident in L2 anyway) 3.551 -> 3.583 ms.
-  // B200_RASTER, B200_TILE_SYNC and B200_L2_HINTS override each of them.
+  // The options raster, tile_sync and l2_hints override each of them.
   const long long operand_bytes = (static_cast<long long>(m) + n) * k * 2;
   const bool big = kOftPair && operand_bytes > 3ll * st->l2_bytes / 2;
   const int raster = raster_for(operand_bytes, true);
   const bool streams = big && static_cast<long long>(n) * k * 2 > st->l2_bytes;  // B does not fit L2: it streams past the band
   unsigned long long hint_a = streams ? kL2EvictLast : kL2EvictNormal, hint_b = streams ? kL2EvictFirst : kL2EvictNormal;
-  if (const char* e = std::getenv("B200_L2_HINTS")) {  // experiments: two letters out of n/f/l for A and B
-    auto pick = [](char c) { return c == 'f' ? kL2EvictFirst : (c == 'l' ? kL2EvictLast : kL2EvictNormal); };
-    if (e[0] && e[1]) { hint_a = pick(e[0]); hint_b = pick(e[1]); }
-  }
+  if (const int h = opt(kOptL2Hints); h >= 0) { hint_a = hint_word(h / 10); hint_b = hint_word(h % 10); }
   int tile_sync = big ? 1 : 0;
-  if (const char* e = std::getenv("B200_TILE_SYNC")) tile_sync = kOftPair ? std::atoi(e) : 0;
+  if (opt(kOptTileSync) >= 0) tile_sync = kOftPair ? opt(kOptTileSync) : 0;
   int* rounds = nullptr;
   if (tile_sync)
     if (int rc = round_counters(st, stream, &rounds)) return rc;  // this launch's own counters, zeroed in stream order
@@ -504,23 +544,91 @@ int oft_two_pass(int m, int n, int k, int group_size, const void* A, int ldA, co
   return rc;
 }
 
-// 0: choose by the cost estimate below, 1: fused kernel, 2: two passes.  Set by b200_oft_tn_f16_two_pass for its
-// own call and by B200_OFT_PATH for experiments.
+// ---- fused OFT with X.R shared through an L2-resident ring (oft3_kernel) ------------------------------------
+// One launch per N-group (each group has its own R, so its own X.R).  Scratch, stream-ordered from the library's
+// pool: the ring of row blocks of X.R (2 bands of 8 row blocks of 256 rows, or all row blocks if fewer) and the
+// zeroed ready / done / round counters of this launch.  The kernel's CTAs wait for one another, so it is only
+// ever launched cooperatively (all CTAs resident); kNoRing tells the caller to take another route.
+constexpr int kNoRing = -1001;
+
+template <int kB>
+int launch_oft3(int m, int n, int k, const void* A, int ldA, const void* B, int ldB, const void* Rg, int ldR, void* C, int ldC,
+                cudaStream_t stream, DeviceState* st) {
+  using T = Oft3Traits<kB, 2, 5>;
+  if (!st->pool) return kNoRing;
+  const int tiles_m = (m + 2 * T::kBM - 1) / (2 * T::kBM), tiles_n = (n + T::kBN - 1) / T::kBN;
+  const int raster = opt(kOptRaster) > 0 ? opt(kOptRaster) : 8;
+  const int slots = tiles_m <= 2 * raster ? tiles_m : 2 * raster;
+  const long long ldx = (static_cast<long long>(k) + 63) & ~63ll;
+  const size_t counter_bytes = ((static_cast<size_t>(3) * tiles_m + 4) * sizeof(int) + 1023) & ~static_cast<size_t>(1023);
+  const size_t ring_bytes = static_cast<size_t>(slots) * 2 * T::kBM * ldx * 2;
+  unsigned char* scratch = nullptr;
+  if (cudaError_t e = cudaMallocFromPoolAsync(reinterpret_cast<void**>(&scratch), counter_bytes + ring_bytes, st->pool, stream)) {
+    cudaGetLastError();
+    if (e == cudaErrorMemoryAllocation) return kNoRing;
+    return fail(B200_ECUDA, "cudaMallocFromPoolAsync: %s", cudaGetErrorString(e));
+  }
+  auto finish = [&](int rc) {
+    const std::string keep = g_err;
+    cudaFreeAsync(scratch, stream);
+    g_err = keep;
+    return rc;
+  };
+  if (cudaError_t e = cudaMemsetAsync(scratch, 0, counter_bytes, stream)) return finish(fail(B200_ECUDA, "cudaMemsetAsync: %s", cudaGetErrorString(e)));
+  int* counters = reinterpret_cast<int*>(scratch);
+  void* ring = scratch + counter_bytes;
+  CUtensorMap mx, mr, mxr, mb;
+  if (int rc = make_map(&mx, A, 2, k, m, ldA, T::kBK, T::kBM, "A")) return finish(rc);
+  if (int rc = make_map(&mr, Rg, 2, k, kB, ldR, T::kBK, kB / 2, "R")) return finish(rc);
+  if (int rc = make_map(&mxr, ring, 2, ldx, static_cast<long long>(slots) * 2 * T::kBM, ldx, T::kBK, T::kBM, "XR ring")) return finish(rc);
+  if (int rc = make_map(&mb, B, 2, k, n, ldB, T::kBK, T::kBNHalf, "B")) return finish(rc);
+  // Phase lock and eviction priorities as for the plain pair GEMM (launch_gemm_bn): the band's rows of X.R are what
+  // the tiles of a band share, W streams past them once per band, X is read once.
+  const long long operand_bytes = (static_cast<long long>(m) + n) * k * 2;
+  const bool big = operand_bytes > 3ll * st->l2_bytes / 2;
+  const bool streams = big && static_cast<long long>(n) * k * 2 > st->l2_bytes;
+  unsigned long long hint_a = streams ? kL2EvictLast : kL2EvictNormal, hint_b = streams ? kL2EvictFirst : kL2EvictNormal;
+  if (const int h = opt(kOptL2Hints); h >= 0) { hint_a = hint_word(h / 10); hint_b = hint_word(h % 10); }
+  int tile_sync = big ? 1 : 0;
+  if (opt(kOptTileSync) >= 0) tile_sync = opt(kOptTileSync);
+  Oft3Args args{m, n, k, static_cast<__half*>(C), ldC, st->status, raster, big ? kL2EvictFirst : kL2EvictNormal, hint_a, hint_b,
+                tile_sync, counters + 3 * tiles_m, slots, counters, counters + 2 * tiles_m};
+  auto kernel = oft3_kernel<T>;
+  if (int rc = opt_in_smem(kernel, T::kSmemBytes)) return finish(rc);
+  const long long tiles = static_cast<long long>(tiles_m) * tiles_n;
+  const int pairs = static_cast<int>(tiles < st->sm_count / 2 ? tiles : st->sm_count / 2);
+  if (launch_cooperative(kernel, 2 * pairs, T::kThreads, T::kSmemBytes, stream, mx, mr, mxr, mb, args) != cudaSuccess) {
+    cudaGetLastError();
+    return finish(kNoRing);
+  }
+  return finish(B200_OK);
+}
+
+template <int kB>
+int oft_ring(int m, int n, int k, int group_size, const void* A, int ldA, const void* B, int ldB, const void* R, int ldR,
+             void* C, int ldC, cudaStream_t stream, DeviceState* st) {
+  int rc = B200_OK;
+  for (int g = 0; rc == B200_OK && g < n / group_size; ++g)  // stream order serialises the groups
+    rc = launch_oft3<kB>(m, group_size, k, A, ldA, static_cast<const __half*>(B) + static_cast<long long>(g) * group_size * ldB, ldB,
+                         static_cast<const __half*>(R) + static_cast<long long>(g) * kB * ldR, ldR,
+                         static_cast<__half*>(C) + static_cast<long long>(g) * group_size, ldC, stream, st);
+  return rc;
+}
+
+// Routes of the AR_W product.  1: oft2_kernel, X.R kept in tensor memory and formed again for every N tile (no
+// scratch; the only route for groups narrower than the N tile).  2: rotation pass + plain GEMM.  3: oft3_kernel,
+// one X.R per row block shared by all N tiles of the group through the L2 ring.  0 = choose: the ring kernel as
+// soon as a group spans two N tiles (its rotation work is 1 / tiles_n of route 1's, and unlike route 2 it neither
+// writes X.R to HBM nor serialises the rotation in front of the product), else route 1.
+// Set by b200_oft_tn_f16_two_pass for its own call and by the option "oft_route".
 thread_local int g_oft_path = 0;
 
-bool prefer_two_pass(int m, int k, int group_size, int b, const DeviceState* st) {
-  int path = g_oft_path;
-  if (path == 0)
-    if (const char* e = std::getenv("B200_OFT_PATH")) path = std::atoi(e);
-  if (!st->pool) return false;  // no scratch to put X.R in (the entry point with static scratch)
-  if (path == 1) return false;
-  if (path == 2) return true;
-  // Cycles of one SM pair per (256 x 256 tile, 64 columns of K), measured with in-kernel cycle counters.
-  const double units = std::ceil(m / 256.0) * std::ceil(group_size / 256.0) * std::ceil(k / 64.0);
-  const double pairs = st->sm_count / 2, hz = 1.4e9;
-  const double fused = units * (b == 128 ? 900.0 : 715.0) / (pairs * hz);
-  const double two = units * 545.0 / (pairs * hz) + 4.0 * m * static_cast<double>(k) / 5.5e12 + 8e-6;
-  return group_size >= 256 && two < 0.93 * fused;
+int choose_route(int group_size, const DeviceState* st) {
+  int path = g_oft_path != 0 ? g_oft_path : opt(kOptOftRoute);
+  const bool can_share = kOftPair && st->pool != nullptr;  // routes 2 and 3 need scratch from the pool
+  if (path == 2 || path == 3) return can_share ? path : 1;
+  if (path == 1) return 1;
+  return (can_share && group_size >= 2 * static_cast<int>(CurrCompParams::bN)) ? 3 : 1;
 }
 
 // group_size == n or a multiple of the N tile: one R per tile.  group_size a divisor of the N tile (the
@@ -529,11 +637,19 @@ template <int kB>
 int launch_oft(int m, int n, int k, int group_size, const void* A, int ldA, const void* B, int ldB, const void* R, int ldR,
                void* C, int ldC, cudaStream_t stream, DeviceState* st) {
   constexpr int kBN = CurrCompParams::bN;
-  if (prefer_two_pass(m, k, group_size, kB, st)) {
+  const int route = choose_route(group_size, st);
+  if (route == 2) {
     const int rc = oft_two_pass<kB>(m, n, k, group_size, A, ldA, B, ldB, R, ldR, C, ldC, stream, st);
     if (rc != kNoScratch) return rc;
     if (g_oft_path == 2) return fail(B200_ECUDA, "no device memory for the %lld bytes of X.R scratch", static_cast<long long>(m) * ((k + 7) & ~7) * 2);
-    // out of memory for X.R: the fused kernel needs no scratch
+    // out of memory for X.R: the kernel that keeps X.R in tensor memory needs no scratch
+  }
+  if constexpr (kOftPair) {
+    if (route == 3 && (group_size == n || group_size % kBN == 0)) {
+      const int rc = oft_ring<kB>(m, n, k, group_size, A, ldA, B, ldB, R, ldR, C, ldC, stream, st);
+      if (rc != kNoRing) return rc;
+      // no scratch, or the cooperative launch was refused: fall through to the kernel that needs neither
+    }
   }
   if (group_size == n || group_size % kBN == 0) return launch_oft_gt<kB, 1>(m, n, k, group_size, A, ldA, B, ldB, R, ldR, C, ldC, stream, st);
   if constexpr (kOftPair && kB <= 64) {
@@ -701,6 +817,7 @@ static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBy
 struct StaticScratchState {
   bool ready = false;
   int sm_count = 0;
+  long long l2_bytes = 126ll << 20;
   void* scratch = nullptr;  // device address of g_static_scratch on this device
 };
 StaticScratchState g_static[kMaxDevices];
@@ -709,14 +826,20 @@ std::mutex g_static_mu;
 // Device scratch one fused-OFT launch needs beyond its inputs and outputs: the status record of the
 // bounded waits followed by the wait-profile words (the same layout the allocated workspace has).
 // reconn_sz = 8 adds the expanded copy of R (see expand_r8_kernel) at kStaticRxOffset.
+#ifdef B200_PROFILE_WAITS
+constexpr size_t kStaticRecordBytes = kWorkspaceBytes;  // the kernels of this build also write their wait-profile words
 constexpr size_t kStaticRxOffset = 36 * 1024;
-static_assert(kWorkspaceBytes <= kStaticRxOffset, "status record and profile words must fit below the expanded R");
+#else
+constexpr size_t kStaticRecordBytes = 256;              // status record (4 ints) and round counters (4 ints)
+constexpr size_t kStaticRxOffset = 256;
+#endif
+static_assert(kStaticRecordBytes <= kStaticRxOffset && kStatusInts * sizeof(int) <= kStaticRecordBytes, "the record must fit below the expanded R");
 size_t oft_scratch_bytes(int n_groups, int k, int reconn_sz) {
-  return reconn_sz == 8 ? kStaticRxOffset + r8_bytes(n_groups, k) : kWorkspaceBytes;
+  return reconn_sz == 8 ? kStaticRxOffset + r8_bytes(n_groups, k) : kStaticRecordBytes;
 }
 
 // Once per device, with that device current.  Calls nothing that allocates device memory.
-int static_scratch_state(StaticScratchState** out) {
+int static_scratch_state(StaticScratchState** out, cudaStream_t stream) {
   int dev = 0;
   CUDA_TRY(cudaGetDevice(&dev));
   if (dev < 0 || dev >= kMaxDevices) return fail(B200_EINVAL, "device ordinal %d out of range", dev);
@@ -730,14 +853,13 @@ int static_scratch_state(StaticScratchState** out) {
     void* ptr = nullptr;
     CUDA_TRY(cudaGetSymbolAddress(&ptr, g_static_scratch));
     if (!ptr) return fail(B200_ECUDA, "cudaGetSymbolAddress returned a null address for the static scratch");
-    CUDA_TRY(cudaMemset(ptr, 0, kWorkspaceBytes));  // the status record must start at zero
-    if (!g_encode) {
-      void* fn = nullptr;
-      cudaDriverEntryPointQueryResult q;
-      CUDA_TRY(cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &q));
-      if (q != cudaDriverEntryPointSuccess || !fn) return fail(B200_ECUDA, "cuTensorMapEncodeTiled not available from the driver");
-      g_encode = reinterpret_cast<EncodeFn>(fn);
-    }
+    int l2 = 0;
+    CUDA_TRY(cudaDeviceGetAttribute(&l2, cudaDevAttrL2CacheSize, dev));
+    st.l2_bytes = l2 > 0 ? l2 : (126ll << 20);
+    // the status record must start at zero: cleared on the first caller's stream, ahead of its kernel; later
+    // calls on other streams are ordered after this one by the rule that calls may not overlap
+    CUDA_TRY(cudaMemsetAsync(ptr, 0, kStaticRecordBytes, stream));
+    if (int rc = resolve_encode()) return rc;
     st.scratch = ptr;
     st.ready = true;
   }
@@ -787,9 +909,10 @@ int b200_oft_plan(int m, int n, int k, int group_size, int reconn_sz, int* path,
     return fail(B200_EINVAL, "bad plan arguments (m=%d n=%d k=%d group_size=%d reconn_sz=%d)", m, n, k, group_size, reconn_sz);
   DeviceState* st;
   if (int rc = device_state(&st)) return rc;
-  const bool two = prefer_two_pass(m, k, group_size, reconn_sz == 8 ? 16 : reconn_sz, st);
-  if (path) *path = two ? 2 : 1;
-  if (kernel_launches) *kernel_launches = (two ? 2 * (n / group_size) : 1) + (reconn_sz == 8 ? 1 : 0);
+  const int route = choose_route(group_size, st);
+  if (path) *path = route;
+  const int groups = n / group_size;
+  if (kernel_launches) *kernel_launches = (route == 2 ? 2 * groups : (route == 3 ? groups : 1)) + (reconn_sz == 8 ? 1 : 0);
   return B200_OK;
 }
 
@@ -1034,6 +1157,21 @@ int b200_device_status(int out[4]) {
   return B200_OK;
 }
 
+int b200_static_status(int out[4]) {
+  g_err.clear();
+  StaticScratchState* ss;
+  if (int rc = static_scratch_state(&ss, nullptr)) return rc;
+  CUDA_TRY(cudaDeviceSynchronize());
+  int host[4] = {0, 0, 0, 0};
+  CUDA_TRY(cudaMemcpy(host, ss->scratch, sizeof host, cudaMemcpyDeviceToHost));
+  if (out) std::memcpy(out, host, sizeof host);
+  if (host[0] != 0) {
+    CUDA_TRY(cudaMemset(ss->scratch, 0, sizeof host));
+    return fail(B200_EDEVICE, "a bounded wait ran out in CTA %d at wait site %d (parity %d)", host[1], host[2], host[3]);
+  }
+  return B200_OK;
+}
+
 int b200_transform_weight_f16(int n, int k, int group_size, int reconn_sz, const void* B, int ldB, const void* R, int ldR,
                               void* Bt, int ldBt, void* stream) {
   g_err.clear();
@@ -1115,6 +1253,28 @@ const char* b200_kernel_info(void) {
 
 const char* b200_last_error(void) { return g_err.c_str(); }
 
+int b200_set_option(const char* name, int value) {
+  g_err.clear();
+  options_init();
+  for (int i = 0; name && i < kOptCount; ++i)
+    if (std::strcmp(name, kOptionDefs[i].name) == 0) {
+      g_opt[i].store(value);
+      return B200_OK;
+    }
+  return fail(B200_EINVAL, "unknown option '%s'", name ? name : "(null)");
+}
+
+int b200_get_option(const char* name, int* value) {
+  g_err.clear();
+  options_init();
+  for (int i = 0; name && value && i < kOptCount; ++i)
+    if (std::strcmp(name, kOptionDefs[i].name) == 0) {
+      *value = g_opt[i].load();
+      return B200_OK;
+    }
+  return fail(B200_EINVAL, "unknown option '%s'", name ? name : "(null)");
+}
+
 int b200_shutdown(void) {
   g_err.clear();
   {
@@ -1160,12 +1320,13 @@ int b200_oft_tn_f16_static(int m, int n, int k, int group_size, int reconn_sz, c
     return B200_OK;
   }
   StaticScratchState* ss;
-  if (int rc = static_scratch_state(&ss)) return rc;
-  // Every call shares the one array, which still holds what the last call left there.  The status
-  // record is the part that must start at zero; clear it in stream order ahead of the kernel.
-  CUDA_TRY(cudaMemsetAsync(ss->scratch, 0, kStatusInts * sizeof(int), stream));
-  DeviceState view;  // what the launcher reads: SM count and where the kernel's scratch is
+  if (int rc = static_scratch_state(&ss, stream)) return rc;
+  // Every call shares the one array, which still holds what the last call left there.  The record of a
+  // bounded wait that ran out (words 0..3) stays until b200_static_status reads it; the round counters
+  // that follow are zeroed by the launcher when a launch uses them.
+  DeviceState view;  // what the launcher reads: SM count, L2 size and where the kernel's scratch is
   view.sm_count = ss->sm_count;
+  view.l2_bytes = ss->l2_bytes;
   view.status = static_cast<int*>(ss->scratch);
   if (reconn_sz == 8) {
     void* rx = static_cast<unsigned char*>(ss->scratch) + kStaticRxOffset;

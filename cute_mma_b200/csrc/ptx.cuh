@@ -179,6 +179,41 @@ __device__ __forceinline__ bool tile_round_sync(int* counter, unsigned target, c
   return true;
 }
 
+// Counters in global memory that CTAs of one co-resident persistent kernel publish progress through.
+// The data they guard moves through the async proxy (TMA stores and loads), so both sides put a proxy fence
+// between the copies and the counter access.
+__device__ __forceinline__ void fence_proxy_async_all() { asm volatile("fence.proxy.async;" ::: "memory"); }
+__device__ __forceinline__ int ld_acquire_gpu(const int* p) {
+  int v;
+  asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+// Publishes whatever the calling thread wrote (or saw complete) before: release, then one relaxed add.
+__device__ __forceinline__ void flag_signal(int* counter) {
+  fence_proxy_async_all();
+  __threadfence();
+  atomicAdd(counter, 1);
+}
+// Bounded wait until *counter >= target.  False when this CTA is aborting (this wait or another one ran out).
+__device__ __forceinline__ bool flag_wait_ge(const int* counter, int target, const WaitCtx& ctx, int site) {
+  if (ld_acquire_gpu(counter) < target) {
+    const unsigned long long t0 = globaltimer_ns();
+    int it = 0;
+    while (ld_acquire_gpu(counter) < target) {
+      if ((++it & 15) == 0) {
+        if (*ctx.abort_flag) return false;
+        if (globaltimer_ns() - t0 > ctx.limit_ns) {
+          report_timeout(ctx, site, static_cast<uint32_t>(target));
+          return false;
+        }
+      }
+      __nanosleep(100);
+    }
+  }
+  fence_proxy_async_all();
+  return true;
+}
+
 // Whole-warp form for roles whose next instruction is warp-collective (tcgen05.ld / st / wait):
 // every lane gets the same answer, so the warp stays converged when a wait gives up.
 __device__ __forceinline__ bool mbar_wait_warp(uint32_t bar, uint32_t parity, const WaitCtx& ctx, int site) {

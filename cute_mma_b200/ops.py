@@ -25,7 +25,7 @@ OK, EINVAL, EUNSUPPORTED, ECUDA, EDEVICE = 0, 1, 2, 3, 4
 SYMBOLS = (
     "b200_oft_tn_f16", "b200_oft_tn_f16_two_pass", "b200_rotate_f16", "b200_oft_plan", "b200_oft_tn_f16_host", "b200_oft_tn_f16_static", "b200_transform_weight_f16", "b200_oft_tn_f16_a_rw", "b200_gemm_tn_f16", "b200_gemm_nt_f16", "b200_gemm_tn_tf32",
     "b200_gemm_nt_tf32", "b200_gemm", "b200_gemm_tn_f16_acc2", "b200_lora_tn_f16", "b200_gemm_rowmajor", "b200_peer_copy_async", "b200_shard_range", "b200_tile_coord", "b200_device_status", "b200_selftest_wait_timeout", "b200_wait_profile", "b200_kernel_info",
-    "b200_last_error", "b200_shutdown",
+    "b200_last_error", "b200_shutdown", "b200_static_status", "b200_set_option", "b200_get_option",
 )
 
 
@@ -73,6 +73,9 @@ def load_library(path: str | None = None):
     lib.b200_device_status.argtypes = [ctypes.POINTER(ctypes.c_int)]
     lib.b200_selftest_wait_timeout.argtypes = [ctypes.c_uint, ctypes.POINTER(ctypes.c_int)]
     lib.b200_wait_profile.argtypes = [ctypes.POINTER(ctypes.c_ulonglong), i]
+    lib.b200_static_status.argtypes = [ctypes.POINTER(ctypes.c_int)]
+    lib.b200_set_option.argtypes = [ctypes.c_char_p, i]
+    lib.b200_get_option.argtypes = [ctypes.c_char_p, ctypes.POINTER(i)]
     lib.b200_kernel_info.restype = ctypes.c_char_p
     lib.b200_last_error.restype = ctypes.c_char_p
     for name in SYMBOLS:
@@ -128,12 +131,56 @@ def rotate(m, k, A, ldA, R, ldR, XR, ldX, stream=None, *, reconn_sz=8, lib=None)
     _check(lib, lib.b200_rotate_f16(m, k, reconn_sz, _ptr(A), ldA, _ptr(R), ldR, _ptr(XR), ldX, _stream(stream)))
 
 
+ROUTES = {1: "fused_tmem", 2: "two_pass", 3: "fused_ring"}
+
+
 def oft_plan(m, n, k, *, group_size=None, reconn_sz=8, lib=None) -> dict:
-    """{'path': 'fused' | 'two_pass', 'kernel_launches': launches of the library's kernels per oft_tn call}."""
+    """{'path': 'fused_tmem' | 'two_pass' | 'fused_ring', 'kernel_launches': launches of the library's kernels per
+    oft_tn call}: fused_tmem keeps X.R in tensor memory per N tile, fused_ring shares one X.R per row block
+    among the N tiles of a group through an L2-resident ring, two_pass writes X.R to memory first."""
     lib = lib or load_library()
     path, launches = ctypes.c_int(0), ctypes.c_int(0)
     _check(lib, lib.b200_oft_plan(m, n, k, n if group_size is None else group_size, reconn_sz, ctypes.byref(path), ctypes.byref(launches)))
-    return {"path": "two_pass" if path.value == 2 else "fused", "kernel_launches": launches.value}
+    return {"path": ROUTES[path.value], "kernel_launches": launches.value}
+
+
+def set_option(name: str, value: int, lib=None) -> None:
+    """Process-wide override of a launch heuristic (see b200_set_option in the header)."""
+    lib = lib or load_library()
+    _check(lib, lib.b200_set_option(name.encode(), int(value)))
+
+
+def get_option(name: str, lib=None) -> int:
+    lib = lib or load_library()
+    v = ctypes.c_int(0)
+    _check(lib, lib.b200_get_option(name.encode(), ctypes.byref(v)))
+    return v.value
+
+
+class option:
+    """``with ops.option("oft_route", 1): ...`` sets an option for the block and restores the old value."""
+
+    def __init__(self, name: str, value: int, lib=None):
+        self.name, self.value, self.lib = name, value, lib
+
+    def __enter__(self):
+        self.old = get_option(self.name, self.lib)
+        set_option(self.name, self.value, self.lib)
+        return self
+
+    def __exit__(self, *exc):
+        set_option(self.name, self.old, self.lib)
+        return False
+
+
+def static_status(lib=None, raise_on_error: bool = True):
+    """The status record of oft_tn_static's scratch array (b200_static_status): synchronises, reads, clears."""
+    lib = lib or load_library()
+    out = (ctypes.c_int * 4)()
+    rc = lib.b200_static_status(out)
+    if rc != OK and raise_on_error:
+        raise Error(rc, lib.b200_last_error().decode())
+    return list(out)
 
 
 def oft_tn_static(m, n, k, A, ldA, B, ldB, R, ldR, C, ldC, stream=None, *, group_size=None, reconn_sz=8, lib=None) -> None:

@@ -49,15 +49,17 @@ int b200_oft_tn_f16(int m, int n, int k, int group_size, int reconn_sz,
 int b200_rotate_f16(int m, int k, int reconn_sz, const void* A, int ldA, const void* R, int ldR,
                     void* XR, int ldX, void* stream);
 
-/* Which route b200_oft_tn_f16 takes for this problem on the current device (*path: 1 fused kernel, 2 rotation
- * pass + GEMM) and how many of the library's kernels one call launches.  No counterpart in the reference. */
+/* Which route b200_oft_tn_f16 takes for this problem on the current device and how many of the library's
+ * kernels one call launches.  *path: 1 fused kernel that keeps X.R in tensor memory and forms it per N tile
+ * (groups of one N tile or less), 2 rotation pass + GEMM (only when asked for), 3 fused kernel in which one
+ * X.R per row block serves all N tiles of its group through a ring of row blocks that stays in L2 (groups of
+ * two N tiles or more).  No counterpart in the reference. */
 int b200_oft_plan(int m, int n, int k, int group_size, int reconn_sz, int* path, int* kernel_launches);
 
 /* The same product in two passes: X.R (rounded to fp16, as above) is written once to device scratch of
  * m * k * 2 bytes (stream-ordered on `stream`, from the pool the library keeps until b200_shutdown) and
- * the plain fp16 GEMM runs on it, group by group.  b200_oft_tn_f16 takes this path by itself when its
- * cost estimate says so (a group that spans many N tiles; B200_OFT_PATH=1 keeps it on the fused kernel);
- * this entry point always does.  Counterpart in the reference: cublas_oft(..., RW_mode = false), the AR_W
+ * the plain fp16 GEMM runs on it, group by group.  b200_oft_tn_f16 takes this path only when the
+ * option "oft_route" is 2 (see b200_set_option); this entry point always does.  Counterpart in the reference: cublas_oft(..., RW_mode = false), the AR_W
  * order with a batched cuBLAS GEMM for X.R and one cublasHgemm per group (cublas_oft.hpp:66-91); its own
  * kernel never lets X.R leave the thread block (cute_oft_coop_pc.cu:19-186). */
 int b200_oft_tn_f16_two_pass(int m, int n, int k, int group_size, int reconn_sz,
@@ -78,20 +80,24 @@ int b200_oft_tn_f16_host(int m, int n, int k, int group_size, int reconn_sz,
  * cudaMalloc fails; others run this call on a path where the device-wide synchronisation that cudaMalloc
  * implies is not acceptable.  b200_oft_tn_f16 creates a small per-device workspace with cudaMalloc the
  * first time it runs on a device; this entry point calls no cudaMalloc, no cudaFree and no allocating
- * library routine, ever.  The device scratch its kernel needs beyond A, B, R and C (the record in which
- * a kernel reports a bounded wait that ran out, plus the profiling words of -DB200_PROFILE_WAITS builds:
- * about 3 KB, plus for reconn_sz = 8 the expanded copy of R: 32 * (n / group_size) * k bytes) lives in a
- * 64 KB array inside the library image, which every GPU that loads the
- * library keeps until the process exits.  A problem whose scratch need exceeds those 64 KB is refused
- * with B200_EUNSUPPORTED and a message naming both sizes.
- *   - Arguments, layouts and result are exactly those of b200_oft_tn_f16 (same kernel, same bits).
- *   - The first call on each device looks up the array's device address, reads two device attributes
- *     and zeroes the record with a synchronous cudaMemset; make that first call, with the device
- *     current, before any stream capture begins.  Later calls only enqueue work on `stream`.
+ * library routine, ever.  The device scratch its kernel needs beyond A, B, R and C lives in a 64 KB array
+ * inside the library image, which every GPU that loads the library keeps until the process exits: the first
+ * 256 bytes hold the record in which a kernel reports a bounded wait that ran out and the counters of the
+ * tile-round lock (36 KB in -DB200_PROFILE_WAITS builds, which add their profiling words); for
+ * reconn_sz = 8 the expanded copy of R follows, 32 * (n / group_size) * k bytes, so 8 x 8 blocks are served
+ * up to (n / group_size) * k <= 2040.  A problem whose scratch need exceeds the 64 KB is refused with
+ * B200_EUNSUPPORTED and a message naming both sizes.
+ *   - Arguments, layouts and result are exactly those of b200_oft_tn_f16 on its route 1 (the kernel that
+ *     keeps X.R in tensor memory, which needs no scratch for X.R): same bits as b200_oft_tn_f16 with the
+ *     option "oft_route" set to 1.
+ *   - The first call on each device looks up the array's device address, reads three device attributes
+ *     and zeroes the record with a cudaMemsetAsync on the caller's stream; make that first call, with the
+ *     device current, before any stream capture begins.  Later calls only enqueue work on `stream`.
  *   - All calls on a device share the one array, and it keeps whatever the previous call left in it.
- *     The record is cleared in stream order before each launch; two calls whose kernels overlap on the
- *     GPU (different streams, no dependency) race on it.  Serialise them.
- *   - b200_device_status reports the allocated workspace, not this array. */
+ *     Two calls whose kernels overlap on the GPU (different streams, no dependency) race on it.
+ *     Serialise them.
+ *   - A bounded wait that ran out is reported by b200_static_status (below), which reads this array;
+ *     b200_device_status reports the allocated workspace, not this array.  The record stays until read. */
 int b200_oft_tn_f16_static(int m, int n, int k, int group_size, int reconn_sz,
                            const void* A, int ldA, const void* B, int ldB, const void* R, int ldR,
                            void* C, int ldC, void* stream);
@@ -164,6 +170,11 @@ int b200_tile_coord(unsigned tiles_m, unsigned tiles_n, unsigned idx, unsigned* 
  * Clears the record.  Returns B200_EDEVICE when out[0] != 0. */
 int b200_device_status(int out[4]);
 
+/* The same for the array of b200_oft_tn_f16_static: synchronises the current device, copies the four
+ * words out of the array with cudaMemcpy and clears them if set.  Allocates nothing.  No counterpart in
+ * the reference. */
+int b200_static_status(int out[4]);
+
 /* Exercises the kernels' failure path without any fault: a one-thread kernel waits, with a limit of
  * limit_us microseconds (1..100000), on a barrier nothing arrives on; the wait gives up, records
  * {1, CTA 0, site 99, parity 0} and the kernel returns.  Returns B200_OK when exactly that was
@@ -182,6 +193,17 @@ int b200_wait_profile(unsigned long long* out, int n);
 
 /* Compile-time configuration of this build as a short JSON string (tile sizes, ring depths). */
 const char* b200_kernel_info(void);
+
+/* Overrides of the launch heuristics, for experiments and tests (the reference fixes such choices at compile
+ * time).  Names: "oft_route" (0 choose, 1 / 2 / 3 as in b200_oft_plan), "raster" (0 z-curve, g > 0 bands of g
+ * tile rows), "tile_sync", "gemm_tile_sync" (cross-CTA phase lock off / on), "l2_hints", "gemm_l2_hints"
+ * (10 * a + b with 0 normal, 1 evict-first, 2 evict-last for the A / B tile loads), "gemm_split" (0: never
+ * split small problems along K), "maps_3d" (0: per-chunk 2-D copies of MN-major tiles).  -1 (0 for the route)
+ * hands the choice back to the library.  Process-wide; the B200_* environment variables of the same meaning
+ * (B200_OFT_PATH, B200_RASTER, B200_TILE_SYNC, B200_L2_HINTS, B200_GEMM_TILE_SYNC, B200_GEMM_L2_HINTS,
+ * B200_GEMM_SPLIT, B200_MAPS_3D) are read once, at the first use of any option, as initial values. */
+int b200_set_option(const char* name, int value);
+int b200_get_option(const char* name, int* value);
 
 /* Text of the calling thread's last error ("" if none). */
 const char* b200_last_error(void);

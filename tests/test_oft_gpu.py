@@ -1,6 +1,4 @@
-"""GPU parity of the fused OFT kernel against the CPU oracle, through the C ABI."""
-import os
-
+"""GPU parity of the OFT product (every route of the library) against the CPU oracle, through the C ABI."""
 import numpy as np
 import pytest
 
@@ -11,10 +9,15 @@ from oracle import oracle
 pytestmark = pytest.mark.gpu
 
 
-def run_oft(lib, cuda, A, R, B, m, n, k, b, group_size=None, ldA=None, ldB=None, ldR=None, ldC=None, canary=True, fn=None):
+def run_oft(lib, cuda, A, R, B, m, n, k, b, group_size=None, ldA=None, ldB=None, ldR=None, ldC=None, canary=True, fn=None, route=None):
     """Uploads the operands (optionally with padded leading dimensions), runs b200_oft_tn_f16 and
-    returns C[m,n] as numpy.  The padding of C is filled with a canary and must come back untouched."""
+    returns C[m,n] as numpy.  The padding of C is filled with a canary and must come back untouched.
+    ``route`` forces one of the library's routes (option "oft_route") for this call."""
     import torch
+
+    if route is not None:
+        with ops.option("oft_route", route, lib):
+            return run_oft(lib, cuda, A, R, B, m, n, k, b, group_size, ldA, ldB, ldR, ldC, canary, fn)
 
     ldA, ldB, ldR, ldC = ldA or k, ldB or k, ldR or k, ldC or n
 
@@ -112,13 +115,72 @@ def test_oft_two_pass_matches_oracle_and_fused(lib, cuda, m, n, k, b, gs):
     assert bad_t == 0, (bad_t, worst_t)
     if k // b <= 4:
         assert oft_ok(got, ref)[0] == 0
-    os.environ["B200_OFT_PATH"] = "1"
-    try:
-        fused = run_oft(lib, cuda, A, R, B, m, n, k, b, gs)
-    finally:
-        del os.environ["B200_OFT_PATH"]
+    fused = run_oft(lib, cuda, A, R, B, m, n, k, b, gs, route=1)
     d = np.abs(got.astype(np.float64) - fused.astype(np.float64))
     assert np.all(d <= 2.0 ** -10 * (np.abs(fused.astype(np.float64)) + 1.0)), float(d.max())
+
+
+RING_CASES = [
+    # m, n, k, b, group_size: the route in which one X.R per row block serves all N tiles of a group
+    (128, 256, 64, 64, None),      # one tile, one rotation unit
+    (384, 512, 512, 64, None),     # two row blocks x two N tiles
+    (384, 512, 512, 32, None),
+    (384, 512, 512, 16, None),
+    (256, 512, 512, 128, None),    # a rotation unit spans two stages
+    (512, 1024, 1024, 32, None),   # the CPU-oracle configuration
+    (200, 328, 192, 64, None),     # ragged M and N
+    (136, 264, 96, 32, None),      # K not a multiple of the 64-wide stage
+    (200, 328, 264, 8, None),      # 8 x 8 blocks, odd number of them
+    (72, 40, 128, 16, None),       # smaller than one tile
+    (128, 768, 128, 16, 256),      # three groups: one launch per group
+    (256, 1024, 256, 128, 512),    # two groups of two N tiles
+    (2304, 5120, 256, 64, None),   # 180 tiles: several tiles per SM pair, more rotation units than pairs
+]
+
+
+@pytest.mark.parametrize("m,n,k,b,gs", RING_CASES)
+def test_oft_ring_route_matches_oracle_and_two_pass(lib, cuda, pair_build, m, n, k, b, gs):
+    """oft3_kernel (route 3): the oracle tolerances of the other routes, and the bits of the rotation pass +
+    GEMM (same X.R rounded once to fp16, same order of the fp32 sums over K)."""
+    if not pair_build:
+        pytest.skip("the shared-X.R kernel exists in the CTA-pair build only")
+    A, R, B = make_oft_case(m, n, k, b, gs, seed=23, kind="qr")
+    got = run_oft(lib, cuda, A, R, B, m, n, k, b, gs, route=3)
+    with ops.option("gemm_split", 0, lib):  # small problems: the plain GEMM would otherwise sum K in up to four pieces
+        two = run_oft(lib, cuda, A, R, B, m, n, k, b, gs, route=2)
+    diff = float(np.abs(got.astype(np.float64) - two.astype(np.float64)).max())
+    assert np.array_equal(got.view(np.uint16), two.view(np.uint16)), f"max difference {diff}"
+    if m * n * k <= 1 << 30:
+        ref = oracle_full(A, R, B, m, n, k, b, gs)
+        truth = oracle.oft_f64(A, R, B, m, n if gs is None else gs, 1 if gs is None else n // gs, k, b, round_xr=True)
+        bad, worst = oft_ok(got, ref, truth=truth)
+        assert bad == 0, (bad, worst)
+        bad_t, worst_t = truth_ok(got, truth)
+        assert bad_t == 0, (bad_t, worst_t)
+        if k // b <= 4:
+            assert oft_ok(got, ref)[0] == 0
+
+
+def test_oft_ring_route_reuses_its_slots_and_phase_locks(lib, cuda, pair_build):
+    """More row blocks (41) than the ring holds (16): slots are rewritten two bands later, after every tile that
+    read them has finished.  Run with and without the cross-CTA phase lock, with padded leading dimensions and
+    canaries around C, twice (the counters are per launch), against the rotation pass + GEMM."""
+    if not pair_build:
+        pytest.skip("the shared-X.R kernel exists in the CTA-pair build only")
+    m, n, k, b = 256 * 40 + 72, 768, 320, 64
+    A, R, B = make_oft_case(m, n, k, b, seed=27, kind="qr")
+    with ops.option("gemm_split", 0, lib):
+        two = run_oft(lib, cuda, A, R, B, m, n, k, b, route=2)
+    for sync in (0, 1, 1):
+        with ops.option("tile_sync", sync, lib):
+            got = run_oft(lib, cuda, A, R, B, m, n, k, b, ldA=k + 8, ldB=k + 16, ldR=k + 24, ldC=n + 8, route=3)
+        assert np.array_equal(got.view(np.uint16), two.view(np.uint16))
+    with ops.option("raster", 2, lib):  # bands of 2 row blocks, a ring of 4: twenty reuses per slot
+        got = run_oft(lib, cuda, A, R, B, m, n, k, b, route=3)
+    assert np.array_equal(got.view(np.uint16), two.view(np.uint16))
+    rows = np.array([0, 255, 256, 4095, 4096, 4097, m - 1])
+    ref = oracle.cpu_oft_tn(A[rows], R, B, len(rows), n, 1, k, b, threads=oracle.num_threads())
+    assert oft_ok(got[rows], ref)[0] == 0
 
 
 def test_oft_two_pass_padded_and_bit_exact_cases(lib, cuda):
@@ -135,20 +197,21 @@ def test_oft_two_pass_padded_and_bit_exact_cases(lib, cuda):
     assert np.array_equal(got.view(np.uint16), ref.view(np.uint16))
 
 
-def test_oft_path_choice_is_invisible(lib, cuda):
-    """A shape the cost estimate sends down the two-pass route (one group over many N tiles, b = 128) gives the
-    same answer, to summation-order noise, as the fused kernel forced by B200_OFT_PATH=1."""
-    import torch
+def test_oft_path_choice_is_invisible(lib, cuda, pair_build):
+    """A shape the library sends down the shared-X.R route (one group over many N tiles, b = 128) gives the
+    same answer, to summation-order noise, as the kernel that keeps X.R in tensor memory (route 1) and as the
+    two passes (route 2)."""
     m, n, k, b = 1024, 8192, 1024, 128
     A, R, B = make_oft_case(m, n, k, b, seed=31, kind="qr", xdist="normal", wsigma=0.02)
+    if pair_build:
+        assert ops.oft_plan(m, n, k, reconn_sz=b, lib=lib)["path"] == "fused_ring"
     auto = run_oft(lib, cuda, A, R, B, m, n, k, b)
-    os.environ["B200_OFT_PATH"] = "1"
-    try:
-        fused = run_oft(lib, cuda, A, R, B, m, n, k, b)
-    finally:
-        del os.environ["B200_OFT_PATH"]
+    fused = run_oft(lib, cuda, A, R, B, m, n, k, b, route=1)
+    two = run_oft(lib, cuda, A, R, B, m, n, k, b, route=2)
     d = np.abs(auto.astype(np.float64) - fused.astype(np.float64))
     assert np.all(d <= 2.0 ** -10 * (np.abs(fused.astype(np.float64)) + 1.0)), float(d.max())
+    d = np.abs(auto.astype(np.float64) - two.astype(np.float64))
+    assert np.all(d <= 2.0 ** -10 * (np.abs(two.astype(np.float64)) + 1.0)), float(d.max())
     truth = oracle.oft_f64(A, R, B, m, n, 1, k, b, round_xr=True)
     assert truth_ok(auto, truth)[0] == 0
 
@@ -335,15 +398,17 @@ def test_oft_large_slab_sampled(lib, cuda):
     _sampled_parity(lib, cuda, 8192, 3584, 8192, 128, "qr", 0.02, 12, seed=5)
 
 
-def test_oft_large_full_size_sampled_and_routes_agree(lib, cuda):
+def test_oft_large_full_size_sampled_and_routes_agree(lib, cuda, pair_build):
     """The large configuration whole on one GPU (M 65536, K 8192, N 28672, b 128, QR blocks): sampled rows
-    against the oracle, linearity over the whole output, and the two routes of the library (rotation pass +
-    GEMM, which the cost estimate picks here, and the fused kernel) must return the same bits."""
+    against the oracle, linearity over the whole output, and the route the library picks here (one X.R per row
+    block shared through the L2 ring) must return the same bits as the rotation pass + GEMM."""
     import torch
 
     m, k, n, b = 65536, 8192, 28672, 128
-    assert ops.oft_plan(m, n, k, reconn_sz=b, lib=lib)["path"] == "two_pass"
-    assert ops.oft_plan(8192, 8192, 8192, group_size=256, reconn_sz=8, lib=lib) == {"path": "fused", "kernel_launches": 2}
+    if pair_build:
+        assert ops.oft_plan(m, n, k, reconn_sz=b, lib=lib)["path"] == "fused_ring"
+        assert ops.oft_plan(16384, 4096, 4096, reconn_sz=64, lib=lib) == {"path": "fused_ring", "kernel_launches": 1}
+    assert ops.oft_plan(8192, 8192, 8192, group_size=256, reconn_sz=8, lib=lib) == {"path": "fused_tmem", "kernel_launches": 2}
     _sampled_parity(lib, cuda, m, n, k, b, "qr", 0.02, 8, seed=6)
     g = torch.Generator(device=cuda).manual_seed(6)  # the operands _sampled_parity drew
     dA = torch.randn((m, k), generator=g, device=cuda, dtype=torch.float32).to(torch.float16)
@@ -353,11 +418,8 @@ def test_oft_large_full_size_sampled_and_routes_agree(lib, cuda):
     c_auto = torch.empty((m, n), dtype=torch.float16, device=cuda)
     c_fused = torch.empty((m, n), dtype=torch.float16, device=cuda)
     ops.oft_tn(m, n, k, dA, k, dB, k, dR, k, c_auto, n, reconn_sz=b, lib=lib)
-    os.environ["B200_OFT_PATH"] = "1"
-    try:
+    with ops.option("oft_route", 2, lib):
         ops.oft_tn(m, n, k, dA, k, dB, k, dR, k, c_fused, n, reconn_sz=b, lib=lib)
-    finally:
-        del os.environ["B200_OFT_PATH"]
     assert ops.device_status(lib)[0] == 0
     assert torch.equal(c_auto.view(torch.int16), c_fused.view(torch.int16))
 
