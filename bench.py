@@ -11,6 +11,12 @@ the large N-sharded configuration (X [65536, 8192] ~ N(0,1), W [8192, 28672] ~ N
 orthogonal 128x128 blocks); with N GPUs rank r owns a column slab of W and Y, X and R are replicated,
 and there is no collective in the compute (strong scaling: total work is fixed).  FLOPs are counted
 as 2MKN + 2MKb at every GPU count (replicated X.R work is not credited).  Rank 0 prints one JSON line.
+
+`value` times b200_oft_tn_f16 on the route it takes by itself (the fused kernel that shares one X.R per row
+block among the N tiles through an L2-resident ring).  `roofline` carries, beside the figures of that kernel,
+the other routes on the same workload (`routes`), the single-GPU projection shape M 16384, K = N 4096, b 64
+(`projection_shape`) and the two plain GEMM configurations (`gemm_half_tn_8192`, `gemm_float_nt_4096`), each
+with a same-process torch.matmul figure beside it.
 """
 from __future__ import annotations
 
@@ -40,15 +46,12 @@ NOMINAL_FP16_TFLOPS = 2250.0  # vendor dense fp16 figure, context only
 # (dram__bytes_read.sum + dram__bytes_write.sum), keyed by workload and by the route the library takes;
 # None until a capture exists.
 NCU_TRAFFIC_BYTES = {
-    # fused kernel, per launch at N = 1, one-pass counters on the full workload: read 29.2 GB + write 5.7 GB
-    # against 5.3 GB algorithmic (every wave of 74 tiles re-reads its panels of X and W once)
-    ("oft_large_m65536_k8192_n28672_b128", "fused"): 34.94e9,
-    # two-pass route, GEMM pass (gemm2_kernel), same one-pass counters: read 17.86 GB + write 3.72 GB against
-    # 5.3 GB algorithmic (28.05 GB read before the band operand was loaded evict-last and the streaming one
-    # evict-first); the rotation pass before it moves 1.08 + 1.03 GB, its algorithmic bytes
+    # two-pass route, GEMM pass (gemm2_kernel): read 17.86 GB + write 3.72 GB against 5.3 GB algorithmic; the
+    # rotation pass before it moves 1.08 + 1.03 GB, its algorithmic bytes
     ("oft_large_m65536_k8192_n28672_b128", "two_pass"): 21.58e9,
-    # ncu --set full capture of the same shape (read 363 MB + write 154 MB; algorithmic 303 MB)
-    ("oft_proj_m16384_k4096_n4096_b64", "fused"): 517.2e6,
+    # kernel that keeps X.R in tensor memory (oft2_kernel): read 29.2 GB + write 5.7 GB
+    ("oft_large_m65536_k8192_n28672_b128", "fused_tmem"): 34.94e9,
+    ("oft_proj_m16384_k4096_n4096_b64", "fused_tmem"): 517.2e6,
 }
 
 
@@ -64,6 +67,14 @@ def measured_peaks():
 
 def flops_of(m, k, n, b):
     return 2.0 * m * k * n + 2.0 * m * k * b
+
+
+def config_of(workload: str, gpus: int) -> dict:
+    """The `config` object of the JSON line: the same for this repo's arm and for the reference arm."""
+    m, k, n, b, kind, wsigma = WORKLOADS[workload]
+    return {"workload": workload, "M": m, "K": k, "N": n, "b": b, "blocks": kind, "w_sigma": wsigma, "gpus": gpus,
+            "sharding": f"N over {gpus} GPU(s), X and R replicated", "flops": "2MKN + 2MKb",
+            "l2": "inputs larger than L2 (X alone exceeds 126 MB); no flush between steps"}
 
 
 class ClockSampler:
@@ -185,8 +196,9 @@ def run_reference_arm(args, workload):
     line = {"impl": "reference", "metric": METRIC, "value": value, "unit": "TFLOP/s", "n_gpus": args.gpus, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": full_ms, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
             "dtype": "f16", "data": "synthetic",
-            "config": {"workload": workload, "note": "ms_per_step extrapolates the sampled rate to the full problem"},
-            "cpu_baseline": {"value": value, "unit": "TFLOP/s", "cores": info["cores"], "kind": info["kind"], "sample": info["sample"]},
+            "config": config_of(workload, args.gpus),
+            "cpu_baseline": {"value": value, "unit": "TFLOP/s", "cores": info["cores"], "kind": info["kind"], "sample": info["sample"],
+                             "note": "ms_per_step extrapolates the sampled rate to the full problem"},
             "e2e": {"value": value, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}, "gpu_launches": 0}
     emit(line)
 
@@ -194,9 +206,28 @@ def run_reference_arm(args, workload):
 # --------------------------------------------------------------------------------------- GPU arm
 
 
-def projection_shape_rate(lib, dev, stream):
-    """Device-timed rate of the single-GPU projection shape (M 16384, K = N 4096, b 64, Cayley blocks),
-    reported beside the headline workload at N = 1: 50 launches after 5 warm-up launches."""
+def _device_timer(stream):
+    """timed(fn, reps, warm) -> ms per call, CUDA events on `stream` (the stream the kernels are launched on)."""
+    import torch
+
+    def timed(fn, reps, warm=2):
+        for _ in range(warm):
+            fn()
+        torch.cuda.synchronize()
+        t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        t0.record(stream)
+        for _ in range(reps):
+            fn()
+        t1.record(stream)
+        torch.cuda.synchronize()
+        return t0.elapsed_time(t1) / reps
+
+    return timed
+
+
+def projection_shape_rates(lib, dev, stream, peaks):
+    """Device-timed rates of the single-GPU projection shape (M 16384, K = N 4096, b 64, Cayley blocks) on every
+    route of the library, 50 launches after 5 warm-up launches each; the route the library takes by itself first."""
     import torch
 
     from cute_mma_b200 import inputs, ops
@@ -208,51 +239,92 @@ def projection_shape_rate(lib, dev, stream):
     dW = (torch.randn((n, k), generator=g, device=dev, dtype=torch.float32) * wsigma).to(torch.float16)
     dR = torch.from_numpy(inputs.pack_r(inputs.blocks_cayley(1, k // b, b, 7))).to(dev)
     dY = torch.empty((m, n), dtype=torch.float16, device=dev)
-    for _ in range(5):
-        ops.oft_tn(m, n, k, dX, k, dW, k, dR, k, dY, n, stream, reconn_sz=b, lib=lib)
-    torch.cuda.synchronize()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record(stream)
-    for _ in range(50):
-        ops.oft_tn(m, n, k, dX, k, dW, k, dR, k, dY, n, stream, reconn_sz=b, lib=lib)
-    e1.record(stream)
-    torch.cuda.synchronize()
-    ms = e0.elapsed_time(e1) / 50
-    assert ops.device_status(lib)[0] == 0
-    os.environ["B200_OFT_PATH"] = "1"  # the fused kernel on the same shape
-    try:
-        for _ in range(5):
-            ops.oft_tn(m, n, k, dX, k, dW, k, dR, k, dY, n, stream, reconn_sz=b, lib=lib)
-        torch.cuda.synchronize()
-        e0.record(stream)
-        for _ in range(50):
-            ops.oft_tn(m, n, k, dX, k, dW, k, dR, k, dY, n, stream, reconn_sz=b, lib=lib)
-        e1.record(stream)
-        torch.cuda.synchronize()
-        ms_fused = e0.elapsed_time(e1) / 50
-    finally:
-        del os.environ["B200_OFT_PATH"]
-    assert ops.device_status(lib)[0] == 0
-    tf = flops_of(m, k, n, b) / (ms * 1e-3) * 1e-12
-    peaks = measured_peaks()
-    return {"workload": name, "value": tf, "unit": "TFLOP/s", "ms_per_step": ms, "steps": 50, "route": ops.oft_plan(m, n, k, reconn_sz=b, lib=lib)["path"],
-            "fused_route": {"ms_per_step": ms_fused, "value": flops_of(m, k, n, b) / (ms_fused * 1e-3) * 1e-12, "unit": "TFLOP/s"},
-            "frac_of_measured_bf16_burst": tf / peaks["bf16_burst"], "frac_of_nominal_fp16": tf / NOMINAL_FP16_TFLOPS}
+    timed = _device_timer(stream)
+    fl = flops_of(m, k, n, b)
+    chosen = ops.oft_plan(m, n, k, reconn_sz=b, lib=lib)["path"]
+    routes = {}
+    for code, rname in sorted(ops.ROUTES.items(), key=lambda kv: kv[1] != chosen):
+        with ops.option("oft_route", code, lib):
+            ms = timed(lambda: ops.oft_tn(m, n, k, dX, k, dW, k, dR, k, dY, n, stream, reconn_sz=b, lib=lib), 50, warm=5)
+        assert ops.device_status(lib)[0] == 0
+        tf = fl / (ms * 1e-3) * 1e-12
+        routes[rname] = {"ms_per_step": ms, "value": tf, "unit": "TFLOP/s", "steps": 50,
+                         "frac_of_measured_bf16_burst": tf / peaks["bf16_burst"], "frac_of_nominal_fp16": tf / NOMINAL_FP16_TFLOPS}
+    # the plain GEMM of the same size (W . X^T, no rotation) and cuBLAS on it, as the ceiling of any route
+    ms_g = timed(lambda: ops.gemm_tn(n, m, k, dW, k, dX, k, dY, n, stream, lib=lib), 50, warm=5)
+    ms_t = timed(lambda: torch.matmul(dX, dW.t()), 50, warm=5)
+    out = {"workload": name, "M": m, "K": k, "N": n, "b": b, "route": chosen, "routes": routes,
+           "value": routes[chosen]["value"], "unit": "TFLOP/s", "ms_per_step": routes[chosen]["ms_per_step"],
+           "frac_of_measured_bf16_burst": routes[chosen]["frac_of_measured_bf16_burst"],
+           "frac_of_nominal_fp16": routes[chosen]["frac_of_nominal_fp16"],
+           "plain_gemm_same_size": {"ms": ms_g, "value": 2.0 * m * n * k / (ms_g * 1e-3) * 1e-12, "torch_matmul_ms": ms_t,
+                                    "torch_matmul_value": 2.0 * m * n * k / (ms_t * 1e-3) * 1e-12, "unit": "TFLOP/s"}}
+    return out
 
+
+def plain_gemm_rates(lib, dev, stream, peaks):
+    """The two plain GEMM configurations: gemm_half TN 8192^3 (fp16, U(-1,1)) and gemm_float NT 4096^3 (TF32, N(0,1)),
+    device-timed, each with torch.matmul (cuBLAS) on the same operands in the same process beside it."""
+    import torch
+
+    from cute_mma_b200 import ops
+
+    timed = _device_timer(stream)
+    out = {}
+    g = torch.Generator(device=dev).manual_seed(5)
+    m = 8192
+    A = (torch.rand((m, m), generator=g, device=dev) * 2 - 1).to(torch.float16)
+    B = (torch.rand((m, m), generator=g, device=dev) * 2 - 1).to(torch.float16)
+    C = torch.empty((m, m), dtype=torch.float16, device=dev)
+    fl = 2.0 * m ** 3
+    ms = timed(lambda: ops.gemm_tn(m, m, m, A, m, B, m, C, m, stream, lib=lib), 20, warm=3)
+    ms_t = timed(lambda: torch.matmul(A, B.t()), 20, warm=3)
+    tf = fl / (ms * 1e-3) * 1e-12
+    out["gemm_half_tn_8192"] = {"ms": ms, "value": tf, "unit": "TFLOP/s", "frac_of_measured_bf16_burst": tf / peaks["bf16_burst"],
+                                "frac_of_nominal_fp16": tf / NOMINAL_FP16_TFLOPS,
+                                "torch_matmul_fp16": {"ms": ms_t, "value": fl / (ms_t * 1e-3) * 1e-12}}
+    del A, B, C
+    m = 4096
+    A = torch.randn((m, m), generator=g, device=dev)   # [K][M], M contiguous
+    B = torch.randn((m, m), generator=g, device=dev)   # [K][N], N contiguous
+    C = torch.empty((m, m), dtype=torch.float32, device=dev)
+    fl = 2.0 * m ** 3
+    ms = timed(lambda: ops.gemm_nt(m, m, m, A, m, B, m, C, m, stream, dtype="float", lib=lib), 50, warm=5)
+    prev = torch.backends.cuda.matmul.allow_tf32
+    torch.backends.cuda.matmul.allow_tf32 = True
+    try:
+        ms_t = timed(lambda: torch.matmul(A.t(), B), 50, warm=5)
+    finally:
+        torch.backends.cuda.matmul.allow_tf32 = prev
+    tf, tf_t = fl / (ms * 1e-3) * 1e-12, fl / (ms_t * 1e-3) * 1e-12
+    out["gemm_float_nt_4096"] = {"ms": ms, "value": tf, "unit": "TFLOP/s", "dtype": "tf32",
+                                 "torch_matmul_tf32": {"ms": ms_t, "value": tf_t, "note": "the measured TF32 figure of this box: the reported denominator"},
+                                 "frac_of_torch_matmul_tf32": tf / tf_t, "frac_of_nominal_tf32": tf / (NOMINAL_FP16_TFLOPS / 2)}
+    assert ops.device_status(lib)[0] == 0
+    return out
 
 
 def run_gpu_arm(args, workload):
-    import numpy as np
     import torch
     import torch.distributed as dist
-
-    from cute_mma_b200 import inputs, ops, sharded
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     if world != args.gpus:
         raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}: launch N>1 with torch.distributed.run")
+    m, k, n, b, kind, wsigma = WORKLOADS[workload]
+
+    # The CPU leg runs first, on an otherwise idle host: no pinned buffers yet, no clock sampler, no CUDA context
+    # (measured after the GPU legs, beside ~5 GB of freshly pinned memory, the same routine ran at 0.6 of this rate).
+    cpu_baseline = None
+    if world == 1 and not args.no_cpu_baseline:
+        cpu_reference_rate(m, k, n, b, kind, 1.0)  # warm-up: library load, thread start, page faults
+        cpu_baseline = cpu_reference_rate(m, k, n, b, kind, 12.0)
+        cpu_baseline.pop("seconds", None)
+
+    from cute_mma_b200 import inputs, ops, sharded
+
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
     if world > 1:
@@ -260,7 +332,6 @@ def run_gpu_arm(args, workload):
         dist.init_process_group("nccl", device_id=dev)
     lib = ops.load_library()  # raises if the CUDA library is missing: there is no fallback
 
-    m, k, n, b, kind, wsigma = WORKLOADS[workload]
     n0, n1 = sharded.my_slab(n, n, world, rank, lib=lib)
     n_loc = n1 - n0
     g = torch.Generator(device=dev).manual_seed(1234)             # X identical on every rank
@@ -272,6 +343,7 @@ def run_gpu_arm(args, workload):
     dR = torch.from_numpy(R).to(dev)
     dY = torch.empty((m, n_loc), dtype=torch.float16, device=dev)
     stream = torch.cuda.current_stream()
+    total_flops = flops_of(m, k, n, b)
 
     def step():
         sharded.oft_tn_slab(m, n, k, dX, k, dW, k, dR, k, dY, n_loc, n0, n1, stream, reconn_sz=b, lib=lib)
@@ -281,81 +353,69 @@ def run_gpu_arm(args, workload):
             dist.barrier()
         torch.cuda.synchronize()
 
-    for _ in range(max(args.warmup, 3)):
+    def max_over_ranks(x: float) -> float:
+        t = torch.tensor([x], device=dev, dtype=torch.float64)
+        if world > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    def timed_steps(steps: int, warm: int) -> float:
+        """ms per step of `step`, CUDA events on the launch stream, barrier + synchronize on both sides, max over ranks."""
+        for _ in range(warm):
+            step()
+        barrier()
+        t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        t0.record(stream)
+        for _ in range(steps):
+            step()
+        t1.record(stream)
+        barrier()
+        return max_over_ranks(t0.elapsed_time(t1) / steps)
+
+    warm = max(args.warmup, 3)
+    plan = ops.oft_plan(m, n_loc, k, reconn_sz=b, lib=lib)
+    for _ in range(warm):
         step()
     barrier()
-    st = ops.device_status(lib)
+    assert ops.device_status(lib)[0] == 0
     sampler = ClockSampler(local_rank if "CUDA_VISIBLE_DEVICES" not in os.environ else int(os.environ["CUDA_VISIBLE_DEVICES"].split(",")[local_rank]))
     if rank == 0:
         sampler.start()
         time.sleep(0.15)
-    barrier()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record(stream)
-    for _ in range(args.steps):
-        step()
-    e1.record(stream)
-    barrier()
-    ms_local = e0.elapsed_time(e1) / args.steps
+    ms = timed_steps(args.steps, 0)   # the headline: the route the library takes by itself
     clocks = sampler.stop() if rank == 0 else None
     st = ops.device_status(lib)
     assert st[0] == 0, st
-    t = torch.tensor([ms_local], device=dev, dtype=torch.float64)
-    if world > 1:
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    ms = float(t.item())
-    total_flops = flops_of(m, k, n, b)
     value = total_flops / (ms * 1e-3) * 1e-12
+    y_chosen = dY.clone() if n_loc * m <= (1 << 31) else None
 
-    # which route the library took, and for the two-pass route the duration of each pass on its own
-    plan = ops.oft_plan(m, n_loc, k, reconn_sz=b, lib=lib)
-    passes = None
-    gemm_ms = ms_local
-    if plan["path"] == "two_pass":
-        dXR = torch.empty((m, k), dtype=torch.float16, device=dev)
-
-        def timed(fn, reps):
-            for _ in range(2):
-                fn()
-            torch.cuda.synchronize()
-            t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            t0.record(stream)
-            for _ in range(reps):
-                fn()
-            t1.record(stream)
-            torch.cuda.synchronize()
-            return t0.elapsed_time(t1) / reps
-
-        rot_ms = timed(lambda: ops.rotate(m, k, dX, k, dR, k, dXR, k, stream, reconn_sz=b, lib=lib), max(args.steps, 5))
-        gemm_ms = timed(lambda: ops.gemm_tn(n_loc, m, k, dW, k, dXR, k, dY, n_loc, stream, lib=lib), args.steps)
-        passes = {"rotate_ms": rot_ms, "rotate_gbs": 4.0 * m * k / (rot_ms * 1e-3) * 1e-9, "rotate_frac_of_measured_hbm": None,
-                  "gemm_ms": gemm_ms, "gemm_tflops": 2.0 * m * n_loc * k / (gemm_ms * 1e-3) * 1e-12}
-        del dXR
+    # every route of the library on the same workload, same steps, max over ranks
+    peaks = measured_peaks()
+    routes = {plan["path"]: {"ms_per_step": ms, "value": value, "unit": "TFLOP/s", "steps": args.steps, "chosen": True}}
+    for code, rname in ops.ROUTES.items():
+        if rname == plan["path"]:
+            continue
+        with ops.option("oft_route", code, lib):
+            r_ms = timed_steps(args.steps, 2)
         assert ops.device_status(lib)[0] == 0
-
-    # the fused kernel (X.R never leaves the SM) on the same workload, for comparison with the route taken
-    fused = None
-    if plan["path"] == "two_pass":
-        os.environ["B200_OFT_PATH"] = "1"
-        try:
-            fsteps = max(3, min(args.steps, 5))
-            for _ in range(2):
-                step()
-            barrier()
-            f0, f1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            f0.record(stream)
-            for _ in range(fsteps):
-                step()
-            f1.record(stream)
-            barrier()
-            tf_ = torch.tensor([f0.elapsed_time(f1) / fsteps], device=dev, dtype=torch.float64)
-            if world > 1:
-                dist.all_reduce(tf_, op=dist.ReduceOp.MAX)
-            fused = {"ms_per_step": float(tf_.item()), "value": total_flops / (float(tf_.item()) * 1e-3) * 1e-12, "unit": "TFLOP/s", "steps": fsteps,
-                     "kernel": "oft2_kernel (B200_OFT_PATH=1)"}
-        finally:
-            del os.environ["B200_OFT_PATH"]
-        assert ops.device_status(lib)[0] == 0
+        routes[rname] = {"ms_per_step": r_ms, "value": total_flops / (r_ms * 1e-3) * 1e-12, "unit": "TFLOP/s", "steps": args.steps, "chosen": False}
+        if y_chosen is not None:
+            routes[rname]["same_bits_as_chosen"] = bool(torch.equal(y_chosen.view(torch.int16), dY.view(torch.int16)))
+    del y_chosen
+    for r in routes.values():
+        r["frac_of_measured_bf16_burst_per_gpu"] = r["value"] / world / peaks["bf16_burst"]
+    # the two passes of the two-pass route on their own (rank 0's GPU)
+    timed = _device_timer(stream)
+    dXR = torch.empty((m, k), dtype=torch.float16, device=dev)
+    rot_ms = timed(lambda: ops.rotate(m, k, dX, k, dR, k, dXR, k, stream, reconn_sz=b, lib=lib), max(args.steps, 5))
+    gemm_ms = timed(lambda: ops.gemm_tn(n_loc, m, k, dW, k, dXR, k, dY, n_loc, stream, lib=lib), args.steps)
+    routes["two_pass"]["passes"] = {"rotate_ms": rot_ms, "rotate_gbs": 4.0 * m * k / (rot_ms * 1e-3) * 1e-9,
+                                    "rotate_frac_of_measured_hbm": 4.0 * m * k / (rot_ms * 1e-3) * 1e-9 / peaks["hbm_gbs"],
+                                    "gemm_ms": gemm_ms, "gemm_tflops": 2.0 * m * n_loc * k / (gemm_ms * 1e-3) * 1e-12}
+    del dXR
+    step()  # dY holds the chosen route's result again
+    barrier()
+    assert ops.device_status(lib)[0] == 0
 
     # optional exchange, timed on its own
     allgather_ms = None
@@ -368,9 +428,7 @@ def run_gpu_arm(args, workload):
         out = sharded.all_gather_c(dY, world)
         a1.record(stream)
         barrier()
-        ta = torch.tensor([a0.elapsed_time(a1)], device=dev, dtype=torch.float64)
-        dist.all_reduce(ta, op=dist.ReduceOp.MAX)
-        allgather_ms = float(ta.item())
+        allgather_ms = max_over_ranks(a0.elapsed_time(a1))
         # the same exchange overlapped with the product (copy engines push finished row chunks to the peers)
         ag = sharded.SlabProductAllGather(m, n, k, n0, n1, reconn_sz=b, world=world, rank=rank, device=dev, lib=lib)
         for _ in range(2):
@@ -380,9 +438,7 @@ def run_gpu_arm(args, workload):
         t0 = time.perf_counter()
         for _ in range(5):
             ag(dX, dW, dR)
-        tov = torch.tensor([(time.perf_counter() - t0) / 5 * 1e3], device=dev, dtype=torch.float64)
-        dist.all_reduce(tov, op=dist.ReduceOp.MAX)
-        overlapped_ms = float(tov.item())
+        overlapped_ms = max_over_ranks((time.perf_counter() - t0) / 5 * 1e3)
         del out, ag, y_all
 
     # end to end from pinned host buffers, H2D + product + D2H inside the timed region.  One GPU: the C ABI's
@@ -391,6 +447,7 @@ def run_gpu_arm(args, workload):
     hW = dW.cpu().pin_memory()
     hR = torch.from_numpy(R).pin_memory()
     hY = torch.empty((m, n_loc), dtype=torch.float16).pin_memory()
+    e2e_legs = None
     if world == 1:
         hX = dX.cpu().pin_memory()
         e2e_api = "b200_oft_tn_f16_host (pinned host buffers, synchronous)"
@@ -403,7 +460,7 @@ def run_gpu_arm(args, workload):
         r0, r1 = sharded.row_slice(m, world, rank)
         hX = dX[r0:r1].cpu().pin_memory()
         runner = sharded.HostSlabRunner(m, n, k, n0, n1, reconn_sz=b, world=world, rank=rank, device=dev, lib=lib)
-        e2e_api = "sharded.HostSlabRunner (pinned host buffers; X uploaded once per node, all-gathered over NVLink; synchronous)"
+        e2e_api = "sharded.HostSlabRunner (pinned host buffers; X uploaded once per node, all-gathered over NVLink in row chunks; synchronous)"
         h2d, d2h = runner.bytes_per_step()
 
         def e2e_step():
@@ -415,60 +472,49 @@ def run_gpu_arm(args, workload):
     t0 = time.perf_counter()
     for _ in range(args.e2e_steps):
         e2e_step()  # synchronous: returns when Y is back in host memory
-    e2e_s_local = (time.perf_counter() - t0) / args.e2e_steps
-    te = torch.tensor([e2e_s_local], device=dev, dtype=torch.float64)
+    e2e_s = max_over_ranks((time.perf_counter() - t0) / args.e2e_steps)
     if world > 1:
-        dist.all_reduce(te, op=dist.ReduceOp.MAX)
-    e2e_s = float(te.item())
+        e2e_legs = runner.leg_times(hX, hW, hR, hY)  # each leg on its own, max over ranks (ms)
+        e2e_legs = {name: max_over_ranks(v) for name, v in e2e_legs.items()}
     th = torch.tensor([h2d, d2h], device=dev, dtype=torch.float64)
     if world > 1:
         dist.all_reduce(th)
     same = bool(torch.equal(hY, dY.cpu()))  # the host-buffer path must reproduce the device path bit for bit
 
     if rank == 0:
-        peaks = measured_peaks()
-        # dominant kernel: the fused kernel (its launch is the step), or the GEMM pass of the two-pass route
-        # (timed on its own above; algorithmic FLOPs 2 M N K, the rotation's 2 M K b belong to the other pass)
-        two = plan["path"] == "two_pass"
-        flops_launch = 2.0 * m * n_loc * k if two else flops_of(m, k, n_loc, b)
-        achieved = flops_launch / (gemm_ms * 1e-3) * 1e-12
+        # dominant kernel = the one launch of the route taken: algorithmic FLOPs of this GPU's slab per launch
+        flops_launch = flops_of(m, k, n_loc, b)
+        achieved = flops_launch / (ms * 1e-3) * 1e-12
         timed_s = ms * args.steps * 1e-3
         peak = peaks["bf16_sustained"] if timed_s >= 2.0 else peaks["bf16_burst"]
-        if passes is not None:
-            passes["rotate_frac_of_measured_hbm"] = passes["rotate_gbs"] / peaks["hbm_gbs"]
+        kernel_of = {"fused_ring": "oft3_kernel", "fused_tmem": "oft2_kernel", "two_pass": "xr_kernel + gemm2_kernel"}
+        roofline = {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak,
+                    "peak_source": f"{peaks['source']} bf16 {'sustained' if timed_s >= 2.0 else 'burst'} (cuBLAS matmul on this pool)",
+                    "traffic": (NCU_TRAFFIC_BYTES.get((workload, plan["path"])) if world == 1 else None),
+                    "frac_of_nominal_fp16": achieved / NOMINAL_FP16_TFLOPS, "route": plan["path"], "kernel": kernel_of[plan["path"]],
+                    "launch_ms": ms, "kernel_config": ops.kernel_info(lib)["oft"], "n_per_gpu": n_loc, "routes": routes}
         line = {
-            "metric": METRIC, "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
+            "metric": METRIC, "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps, "warmup": warm,
             "ms_per_step": ms, "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f16",
-            "data": "synthetic",
-            "config": {"workload": workload, "M": m, "K": k, "N": n, "b": b, "n_per_gpu": n_loc, "sharding": f"N over {world} GPU(s), X and R replicated",
-                       "flops": "2MKN + 2MKb", "l2": "inputs larger than L2 (X alone exceeds 126 MB); no flush between steps",
-                       "route": plan["path"], "kernel": ops.kernel_info(lib)["gemm_half_tn" if two else "oft"]},
-            "roofline": {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak,
-                         "peak_source": f"{peaks['source']} bf16 {'sustained' if timed_s >= 2.0 else 'burst'} (cuBLAS matmul on this pool)",
-                         "traffic": (NCU_TRAFFIC_BYTES.get((workload, plan["path"])) if world == 1 else None),
-                         "frac_of_nominal_fp16": achieved / NOMINAL_FP16_TFLOPS,
-                         "kernel": "gemm2_kernel (GEMM pass of the two-pass route)" if two else "oft2_kernel", "launch_ms": gemm_ms},
+            "data": "synthetic", "config": config_of(workload, world), "roofline": roofline,
             "e2e": {"value": total_flops / e2e_s * 1e-12, "unit": "TFLOP/s", "h2d_bytes_per_step": int(th[0].item()),
                     "d2h_bytes_per_step": int(th[1].item()), "ms_per_step": e2e_s * 1e3, "steps": args.e2e_steps,
                     "api": e2e_api, "matches_device_path": same},
             "gpu_launches": args.steps * world * plan["kernel_launches"], "clocks": clocks,
         }
-        if passes is not None:
-            line["passes"] = passes
-        if fused is not None:
-            fused["frac_of_measured_bf16_burst"] = fused["value"] / world / peaks["bf16_burst"]  # per GPU
-            line["fused_route"] = fused
+        if e2e_legs is not None:
+            line["e2e"]["legs_ms"] = e2e_legs
         if allgather_ms is not None:
             line["allgather_y_ms"] = allgather_ms
             line["product_with_overlapped_allgather"] = {"ms_per_step": overlapped_ms, "sequential_ms": ms + allgather_ms,
                                                          "matches_nccl_allgather": overlapped_ok,
                                                          "api": "sharded.SlabProductAllGather (row chunks pushed into the peers' symmetric-memory buffers by copy engines)"}
         if world == 1 and workload == DEFAULT_WORKLOAD:
-            line["also"] = projection_shape_rate(lib, dev, stream)
-        if world == 1 and not args.no_cpu_baseline:
-            cb = cpu_reference_rate(m, k, n, b, kind, 12.0)
-            cb.pop("seconds", None)
-            line["cpu_baseline"] = cb
+            del hX, hW, hY
+            roofline["projection_shape"] = projection_shape_rates(lib, dev, stream, peaks)
+            roofline.update(plain_gemm_rates(lib, dev, stream, peaks))
+        if cpu_baseline is not None:
+            line["cpu_baseline"] = cpu_baseline
         emit(line)
     if world > 1:
         dist.barrier()

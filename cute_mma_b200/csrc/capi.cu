@@ -49,7 +49,7 @@ int fail(int code, const char* fmt, ...) {
 // library choose".  The B200_* environment variables of the same meaning are read ONCE, at the first use
 // of any option in the process, as initial values; after that only b200_set_option changes them, so
 // nothing on the launch path reads the environment.
-enum OptionId { kOptOftRoute, kOptRaster, kOptTileSync, kOptL2Hints, kOptGemmTileSync, kOptGemmL2Hints, kOptGemmSplit, kOptMaps3d, kOptCount };
+enum OptionId { kOptOftRoute, kOptRaster, kOptTileSync, kOptL2Hints, kOptGemmTileSync, kOptGemmL2Hints, kOptGemmSplit, kOptMaps3d, kOptRingBands, kOptPrefetch, kOptCount };
 struct OptionDef { const char* name; const char* env; int initial; };
 constexpr OptionDef kOptionDefs[kOptCount] = {
     {"oft_route", "B200_OFT_PATH", 0},            // 0 choose, 1 X.R in tensor memory per tile, 2 two passes, 3 X.R shared through the L2 ring
@@ -60,6 +60,8 @@ constexpr OptionDef kOptionDefs[kOptCount] = {
     {"gemm_l2_hints", "B200_GEMM_L2_HINTS", -1},
     {"gemm_split", "B200_GEMM_SPLIT", -1},        // 0: never split small problems along K
     {"maps_3d", "B200_MAPS_3D", -1},              // 0: one 2-D copy per 128-byte chunk of an MN-major tile
+    {"ring_bands", "B200_RING_BANDS", -1},        // bands of row blocks the X.R ring of route 3 holds (>= 2)
+    {"prefetch", "B200_PREFETCH", -1},            // route 3: K steps by which W tiles are asked into L2 ahead of their load (0 off)
 };
 std::atomic<int> g_opt[kOptCount];
 std::once_flag g_opt_once;
@@ -557,9 +559,25 @@ int launch_oft3(int m, int n, int k, const void* A, int ldA, const void* B, int 
   using T = Oft3Traits<kB, 2, 5>;
   if (!st->pool) return kNoRing;
   const int tiles_m = (m + 2 * T::kBM - 1) / (2 * T::kBM), tiles_n = (n + T::kBN - 1) / T::kBN;
-  const int raster = opt(kOptRaster) > 0 ? opt(kOptRaster) : 8;
-  const int slots = tiles_m <= 2 * raster ? tiles_m : 2 * raster;
+  // Tile order and ring size.  A band of row blocks sweeps once over all of W.  When W stays in L2 beside the ring
+  // the sweeps cost no DRAM traffic, so bands are short (4 row blocks): the tiles in flight then touch few row
+  // blocks and the rotation can run further ahead in a ring of the same size.  When W streams from DRAM once per
+  // band, bands of 8 halve that traffic.  The ring takes what L2 has left beside W (32 to 64 MB), at least two
+  // bands, in whole bands.  The options raster and ring_bands override both.
+  const long long w_bytes = static_cast<long long>(n) * k * 2, mib = 1ll << 20;
+  const bool w_resident = w_bytes <= 64 * mib;
+  const int raster = opt(kOptRaster) > 0 ? opt(kOptRaster) : (w_resident ? 4 : 8);
   const long long ldx = (static_cast<long long>(k) + 63) & ~63ll;
+  const long long block_bytes = 2ll * T::kBM * ldx * 2;
+  long long budget = 64 * mib;
+  if (w_resident) {
+    budget = st->l2_bytes - w_bytes - 16 * mib;
+    budget = budget < 32 * mib ? 32 * mib : (budget > 64 * mib ? 64 * mib : budget);
+  }
+  int bands = static_cast<int>(budget / (block_bytes * raster));
+  if (bands < 2) bands = 2;
+  if (opt(kOptRingBands) >= 2) bands = opt(kOptRingBands);
+  const int slots = tiles_m <= bands * raster ? tiles_m : bands * raster;
   const size_t counter_bytes = ((static_cast<size_t>(3) * tiles_m + 4) * sizeof(int) + 1023) & ~static_cast<size_t>(1023);
   const size_t ring_bytes = static_cast<size_t>(slots) * 2 * T::kBM * ldx * 2;
   unsigned char* scratch = nullptr;
@@ -582,17 +600,21 @@ int launch_oft3(int m, int n, int k, const void* A, int ldA, const void* B, int 
   if (int rc = make_map(&mr, Rg, 2, k, kB, ldR, T::kBK, kB / 2, "R")) return finish(rc);
   if (int rc = make_map(&mxr, ring, 2, ldx, static_cast<long long>(slots) * 2 * T::kBM, ldx, T::kBK, T::kBM, "XR ring")) return finish(rc);
   if (int rc = make_map(&mb, B, 2, k, n, ldB, T::kBK, T::kBNHalf, "B")) return finish(rc);
-  // Phase lock and eviction priorities as for the plain pair GEMM (launch_gemm_bn): the band's rows of X.R are what
-  // the tiles of a band share, W streams past them once per band, X is read once.
+  // Eviction priorities as for the plain pair GEMM (launch_gemm_bn): the band's rows of X.R are what the tiles of
+  // a band share, W streams past them once per band, X is read once.
   const long long operand_bytes = (static_cast<long long>(m) + n) * k * 2;
   const bool big = operand_bytes > 3ll * st->l2_bytes / 2;
   const bool streams = big && static_cast<long long>(n) * k * 2 > st->l2_bytes;
   unsigned long long hint_a = streams ? kL2EvictLast : kL2EvictNormal, hint_b = streams ? kL2EvictFirst : kL2EvictNormal;
   if (const int h = opt(kOptL2Hints); h >= 0) { hint_a = hint_word(h / 10); hint_b = hint_word(h % 10); }
-  int tile_sync = big ? 1 : 0;
+  // No phase lock by default: the ready / done counters already keep the pairs within a band of each other, and
+  // with the lock on top this kernel measured 8 to 17 % slower (interleaved runs, M 65536, K 8192, N 3584 and 28672).
+  (void)big;
+  int tile_sync = 0;
   if (opt(kOptTileSync) >= 0) tile_sync = opt(kOptTileSync);
+  const int prefetch_w = opt(kOptPrefetch) >= 0 ? opt(kOptPrefetch) : (streams ? 4 : 0);
   Oft3Args args{m, n, k, static_cast<__half*>(C), ldC, st->status, raster, big ? kL2EvictFirst : kL2EvictNormal, hint_a, hint_b,
-                tile_sync, counters + 3 * tiles_m, slots, counters, counters + 2 * tiles_m};
+                tile_sync, counters + 3 * tiles_m, prefetch_w, slots, counters, counters + 2 * tiles_m};
   auto kernel = oft3_kernel<T>;
   if (int rc = opt_in_smem(kernel, T::kSmemBytes)) return finish(rc);
   const long long tiles = static_cast<long long>(tiles_m) * tiles_n;
@@ -617,18 +639,21 @@ int oft_ring(int m, int n, int k, int group_size, const void* A, int ldA, const 
 
 // Routes of the AR_W product.  1: oft2_kernel, X.R kept in tensor memory and formed again for every N tile (no
 // scratch; the only route for groups narrower than the N tile).  2: rotation pass + plain GEMM.  3: oft3_kernel,
-// one X.R per row block shared by all N tiles of the group through the L2 ring.  0 = choose: the ring kernel as
-// soon as a group spans two N tiles (its rotation work is 1 / tiles_n of route 1's, and unlike route 2 it neither
-// writes X.R to HBM nor serialises the rotation in front of the product), else route 1.
+// one X.R per row block shared by all N tiles of the group through the L2 ring.  0 = choose: the ring kernel when a
+// group spans enough N tiles (its rotation work is 1 / tiles_n of route 1's, and unlike route 2 it neither writes
+// X.R to HBM nor serialises the rotation in front of the product), else route 1.  Crossover measured at M 16384,
+// K 4096 (interleaved runs, route 3 / route 1 time): b 64: 4 tiles 1.13, 6 tiles 1.00, 8 tiles 0.98, 12 tiles 0.92,
+// 16 tiles 0.95; b 128: 2 tiles 1.43, 4 tiles 0.95, 6 tiles 0.84, 8 tiles 0.82; b 32: 8 tiles 1.00; b 16: 16 tiles 0.89.
 // Set by b200_oft_tn_f16_two_pass for its own call and by the option "oft_route".
 thread_local int g_oft_path = 0;
 
-int choose_route(int group_size, const DeviceState* st) {
+int choose_route(int group_size, int b, const DeviceState* st) {
   int path = g_oft_path != 0 ? g_oft_path : opt(kOptOftRoute);
   const bool can_share = kOftPair && st->pool != nullptr;  // routes 2 and 3 need scratch from the pool
   if (path == 2 || path == 3) return can_share ? path : 1;
   if (path == 1) return 1;
-  return (can_share && group_size >= 2 * static_cast<int>(CurrCompParams::bN)) ? 3 : 1;
+  const int min_tiles = b >= 128 ? 4 : 8;
+  return (can_share && group_size >= min_tiles * static_cast<int>(CurrCompParams::bN)) ? 3 : 1;
 }
 
 // group_size == n or a multiple of the N tile: one R per tile.  group_size a divisor of the N tile (the
@@ -637,7 +662,7 @@ template <int kB>
 int launch_oft(int m, int n, int k, int group_size, const void* A, int ldA, const void* B, int ldB, const void* R, int ldR,
                void* C, int ldC, cudaStream_t stream, DeviceState* st) {
   constexpr int kBN = CurrCompParams::bN;
-  const int route = choose_route(group_size, st);
+  const int route = choose_route(group_size, kB, st);
   if (route == 2) {
     const int rc = oft_two_pass<kB>(m, n, k, group_size, A, ldA, B, ldB, R, ldR, C, ldC, stream, st);
     if (rc != kNoScratch) return rc;
@@ -909,7 +934,7 @@ int b200_oft_plan(int m, int n, int k, int group_size, int reconn_sz, int* path,
     return fail(B200_EINVAL, "bad plan arguments (m=%d n=%d k=%d group_size=%d reconn_sz=%d)", m, n, k, group_size, reconn_sz);
   DeviceState* st;
   if (int rc = device_state(&st)) return rc;
-  const int route = choose_route(group_size, st);
+  const int route = choose_route(group_size, reconn_sz == 8 ? 16 : reconn_sz, st);
   if (path) *path = route;
   const int groups = n / group_size;
   if (kernel_launches) *kernel_launches = (route == 2 ? 2 * groups : (route == 3 ? groups : 1)) + (reconn_sz == 8 ? 1 : 0);

@@ -4,8 +4,8 @@
 //
 // oft2_kernel keeps X.R in tensor memory and therefore forms it again for every N tile (b / bN extra tensor
 // work: +25 % at b = 64, +50 % at b = 128).  Here the rotation is a second, much smaller job of the same
-// persistent kernel.  The pairs split all (256 rows x U columns) units of X.R among themselves, round-robin in
-// row-block order:
+// persistent kernel.  The pairs split the (256 rows x U columns) units of X.R among themselves, band by band, each
+// pair a contiguous share of every band:
 //   rotation  XR unit [256 x U] fp32 (TMEM) = X[256 x U] . Rblk^T        tcgen05.mma, N = b
 //             -> fp16 (RNE) -> 128-byte-swizzled staging in shared memory -> TMA tile store into a ring of
 //             row blocks in global memory that is sized to stay in L2 (2 bands of row blocks)
@@ -13,7 +13,7 @@
 // Tiles are visited band by band (bands of `raster` row blocks, all N tiles of a band before the next band), so
 // a row block of X.R is written once, read by all its N tiles while it sits in L2, and its ring slot is reused
 // two bands later.  Cross-CTA ordering goes through counters in global memory:
-//   ready[2 * tm + rank]  += 1 per unit stored by a CTA of that rank   (a tile waits for all units of its rows)
+//   ready[2 * tm + rank]  += units stored by a CTA of that rank        (a tile waits for all units of its rows)
 //   done[tm]              += 1 per finished tile of row block tm        (a slot is rewritten after all its tiles)
 // Every CTA is resident (grid <= SM count, cooperative launch) and the rotation roles never wait for the
 // product roles of their own CTA, so the oldest unfinished tile can always complete.  All waits are bounded.
@@ -67,9 +67,49 @@ struct Oft3Args {
   unsigned long long hint_x, hint_a, hint_b;  // L2 eviction priority of the X, X.R and W tile loads
   int tile_sync;                   // producers of all CTAs start each tile round together
   int* rounds;                     // 4 zeroed counters of this launch's tile rounds (tile_sync only)
+  int prefetch_w;                  // > 0: W tiles are asked into L2 this many K steps ahead of their load (W streams from DRAM)
   int slots;                       // row blocks the X.R ring holds (all of them, or 2 * raster)
   int* ready;                      // [2 * row blocks] zeroed
   int* done;                       // [row blocks] zeroed
+};
+
+// A pair's rotation units: band after band (the order the tiles consume them), and inside each band a
+// contiguous share of the band's units in (row block, unit) order.  Consecutive units of a pair therefore lie
+// in the same row block, so one publication covers several of them.
+struct RotationShare {
+  unsigned raster, tiles_m, upb, pair, num_pairs;
+  unsigned band = 0, j = 0, j_end = 0;
+  bool started = false;
+  __device__ RotationShare(unsigned raster_, unsigned tiles_m_, unsigned upb_, unsigned pair_, unsigned num_pairs_)
+      : raster(raster_), tiles_m(tiles_m_), upb(upb_), pair(pair_), num_pairs(num_pairs_) {}
+  __device__ unsigned band_units(unsigned b) const {
+    const unsigned rows = (tiles_m - b * raster) < raster ? (tiles_m - b * raster) : raster;
+    return rows * upb;
+  }
+  __device__ unsigned total() const {  // all full bands give this pair the same share
+    const unsigned full = tiles_m / raster, u = raster * upb, rest = (tiles_m % raster) * upb;
+    return full * ((pair + 1) * u / num_pairs - pair * u / num_pairs) + ((pair + 1) * rest / num_pairs - pair * rest / num_pairs);
+  }
+  // next unit of this pair: row block tm, unit ku inside it; false when there is none left
+  __device__ bool next(unsigned& tm, unsigned& ku) {
+    while (true) {
+      if (!started) {
+        if (band * raster >= tiles_m) return false;
+        const unsigned u = band_units(band);
+        j = pair * u / num_pairs;
+        j_end = (pair + 1) * u / num_pairs;
+        started = true;
+      }
+      if (j < j_end) {
+        tm = band * raster + j / upb;
+        ku = j % upb;
+        ++j;
+        return true;
+      }
+      ++band;
+      started = false;
+    }
+  }
 };
 
 template <class T>
@@ -95,6 +135,10 @@ oft3_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ 
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
   volatile int* conv_abort = reinterpret_cast<volatile int*>(tmem_slot + 2);  // rotation epilogue: one of its warps gave up
   const WaitCtx ctx{abort_flag, args.status, kWaitLimitNs};
+#ifdef B200_PROFILE_WAITS
+  const long long kernel_c0 = clock64();
+  if (threadIdx.x == 0) skew_stamp(ctx, kSkewTiles - 2);  // when this CTA started
+#endif
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t rank = cluster_ctarank();
@@ -103,10 +147,9 @@ oft3_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ 
   const unsigned num_tiles = tiles_m * tiles_n;
   const int k_steps = (args.k + T::kBK - 1) / T::kBK;
   const unsigned upb = (args.k + T::kUnitK - 1) / T::kUnitK;  // rotation units per row block
-  const unsigned num_units = tiles_m * upb;
-  unsigned my_tiles = 0, my_units = 0;
+  unsigned my_tiles = 0;
   if (pair < num_tiles) my_tiles = (num_tiles - pair + num_pairs - 1) / num_pairs;
-  if (pair < num_units) my_units = (num_units - pair + num_pairs - 1) / num_pairs;
+  const unsigned my_units = RotationShare(args.raster, tiles_m, upb, pair, num_pairs).total();
 
   if (threadIdx.x == 0) {
     *abort_flag = 0;
@@ -139,7 +182,9 @@ oft3_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ 
     if (lane == 0) {
       uint32_t it = 0;
       bool ok = true;
-      unsigned done_rounds = 0, sync_target = 0;
+      unsigned done_rounds = 0, sync_target = 0, next_tm = 0;
+      int next_n0 = -1;
+      bool have_next = false;
       for (unsigned tile = pair; ok && tile < num_tiles; tile += num_pairs) {
         if (args.tile_sync && done_rounds > 0) {
           if (!(ok = tile_round_sync(args.rounds + rank, sync_target, ctx, 12))) break;
@@ -151,10 +196,20 @@ oft3_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ 
         }
         unsigned tm, tn;
         tile_coord_r(args.raster, tiles_m, tiles_n, tile, tm, tn);
-        // this CTA's 128 rows of the row block: every unit of them has been stored and is visible
-        if (!(ok = flag_wait_ge(args.ready + 2 * tm + rank, static_cast<int>(upb), ctx, 14))) break;
+        // this CTA's 128 rows of the row block: every unit of them has been stored and is visible.  (Usually known
+        // since the middle of the previous tile, see below: the fences behind the counter take 1 to 2 us.)
+        if (!(have_next && next_tm == tm))
+          if (!(ok = flag_wait_ge(args.ready + 2 * tm + rank, static_cast<int>(upb), ctx, 14))) break;
+        have_next = false;
+        if (tile == pair) skew_stamp(ctx, kSkewTiles - 1);  // profiling build: when the first tile's rows were ready
         const int xr_row0 = static_cast<int>(tm % static_cast<unsigned>(args.slots)) * 2 * T::kBM + rank * T::kBM;
         const int n0 = tn * T::kBN + rank * T::kBNHalf;  // this CTA's half of the W tile
+        next_n0 = -1;
+        if (tile + num_pairs < num_tiles) {
+          unsigned tn_next;
+          tile_coord_r(args.raster, tiles_m, tiles_n, tile + num_pairs, next_tm, tn_next);
+          next_n0 = tn_next * T::kBN + rank * T::kBNHalf;
+        }
         for (int ks = 0; ks < k_steps; ++ks, ++it) {
           const int s = it % T::kS2;
           if (!(ok = mbar_wait(empty2 + 8 * s, ((it / T::kS2) & 1) ^ 1, ctx, 11))) break;
@@ -162,6 +217,17 @@ oft3_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ 
           const uint32_t a_dst = ring2 + s * T::kS2Bytes;
           tma_load_2d_pair_hint(a_dst, &tmap_xr, full2 + 8 * s, ks * T::kBK, xr_row0, args.hint_a);
           tma_load_2d_pair_hint(a_dst + T::kABytes, &tmap_b, full2 + 8 * s, ks * T::kBK, n0, args.hint_b);
+          if (args.prefetch_w > 0) {  // W comes from DRAM: the ring alone (5 stages) does not cover that latency
+            const int q = ks + args.prefetch_w;
+            if (q < k_steps) tma_prefetch_2d(&tmap_b, q * T::kBK, n0);
+            else if (next_n0 >= 0 && q - k_steps < k_steps) tma_prefetch_2d(&tmap_b, (q - k_steps) * T::kBK, next_n0);
+          }
+          if (ks == k_steps / 2 && next_n0 >= 0) {
+            // The ring is full and this thread would only wait for a free slot: look at the next tile's rows now.
+            // If they are there already (the normal case), the acquire and proxy fences are paid here instead
+            // of between two tiles, where the MMAs would run dry behind them.
+            have_next = flag_test_ge(args.ready + 2 * next_tm + rank, static_cast<int>(upb));
+          }
         }
       }
       // leaving after its last round, this thread still counts for the rendezvous the others make
@@ -174,9 +240,9 @@ oft3_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ 
     if (lane == 0) {
       uint32_t it = 0;
       bool ok = true;
-      unsigned last_tm = ~0u;
-      for (unsigned g = pair; ok && g < num_units; g += num_pairs) {
-        const unsigned tm = g / upb, ku = g % upb;
+      unsigned last_tm = ~0u, tm = 0, ku = 0, unit_no = 0;
+      RotationShare share(args.raster, tiles_m, upb, pair, num_pairs);
+      for (; ok && share.next(tm, ku); ++unit_no) {
         if (tm != last_tm) {
           // the ring slot of this row block still belongs to row block tm - slots until all its tiles are finished
           if (tm >= static_cast<unsigned>(args.slots))
@@ -187,6 +253,7 @@ oft3_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ 
         for (int su = 0; su < T::kStagesPerUnit; ++su, ++it) {
           const int s = it % T::kS1;
           if (!(ok = mbar_wait(empty1 + 8 * s, ((it / T::kS1) & 1) ^ 1, ctx, 10))) break;
+          if (su == 0) early_stamp(ctx, unit_no, 0);
           if (rank == 0) mbar_expect_tx(full1 + 8 * s, 2 * T::kS1Bytes);
           const uint32_t x_dst = ring1 + s * T::kS1Bytes;
           tma_load_2d_pair_hint(x_dst, &tmap_x, full1 + 8 * s, k0 + su * T::kBK, m0, args.hint_x);
@@ -225,6 +292,7 @@ oft3_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ 
           umma_commit_pair(empty1 + 8 * s, 3);
         }
         if (!ok) break;
+        early_stamp(ctx, i, 1);
         umma_commit_pair(x_acc + 8 * xb, 3);  // the rotation epilogues of both CTAs start on their halves
       }
     }
@@ -279,27 +347,44 @@ oft3_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ 
     const int r = quad * 32 + lane;  // row of the unit this thread converts
     const uint32_t my_row = out_stage + r * 128;
     const bool issuer = (warp == 4 && lane == 0);
+    // The issuer publishes units once their tile stores are complete (bulk_wait_group), several units of one row
+    // block with one add: the publication (proxy fence + release) takes about 2 us, measured with in-kernel
+    // timers, so it happens when the row block changes, when the next unit is not there yet (the thread would
+    // idle anyway), and at the end.
+    constexpr int kGroupsPerUnit = T::kUnitK / 64;
+    int* pending = nullptr;
+    int pending_n = 0;
     bool ok = true;
-    for (unsigned i = 0; ok && i < my_units; ++i) {
-      const unsigned g = pair + i * num_pairs;
-      const unsigned tm = g / upb, ku = g % upb;
+    unsigned tm = 0, ku = 0;
+    RotationShare share(args.raster, tiles_m, upb, pair, num_pairs);
+    for (unsigned i = 0; ok && share.next(tm, ku); ++i) {
       const int xb = i % T::kXrBufs;
       const int xr_row0 = static_cast<int>(tm % static_cast<unsigned>(args.slots)) * 2 * T::kBM + rank * T::kBM;
       const int k0 = ku * T::kUnitK;
+      int* const counter = args.ready + 2 * tm + rank;
+      if (issuer && pending && (pending != counter || !mbar_test_wait(x_acc + 8 * xb, (i / T::kXrBufs) & 1))) {
+        bulk_wait_group<0>();
+        early_stamp(ctx, i, 4);
+        flag_signal(pending, pending_n);
+        early_stamp(ctx, i, 5);
+        pending = nullptr;
+        pending_n = 0;
+      }
       // The four warps meet at named barriers below, so they must leave together: a warp whose wait gave up says
       // so in shared memory and all of them read the word after a barrier that every one of them reaches.
       if (!mbar_wait_warp(x_acc + 8 * xb, (i / T::kXrBufs) & 1, ctx, 30)) *conv_abort = 1;
       named_barrier_sync(2, 128);
       if (*conv_abort) { ok = false; break; }
       tc_fence_after();
+      if (issuer) early_stamp(ctx, i, 2);
       const uint32_t buf = tmem_base + lane_off + T::kColXr + xb * T::kUnitK;
 #pragma unroll
-      for (int h = 0; h < T::kUnitK / 64; ++h) {
+      for (int h = 0; h < kGroupsPerUnit; ++h) {
         uint32_t v0[32], v1[32];
         tmem_ld_x32(buf + h * 64, v0);
         tmem_ld_x32(buf + h * 64 + 32, v1);
         tmem_wait_ld();
-        if (h == T::kUnitK / 64 - 1) {  // everything of this buffer is in registers: hand it back before storing
+        if (h == kGroupsPerUnit - 1) {  // everything of this buffer is in registers: hand it back before storing
           tc_fence_before();
           mbar_arrive_cluster(mapa_shared(x_empty + 8 * xb, 0));  // the leader's barrier collects both CTAs
         }
@@ -323,12 +408,16 @@ oft3_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ 
           bulk_commit_group();
         }
       }
-      if (issuer) {  // the unit's rows are written: publish them to the tiles of this row block
-        bulk_wait_group<0>();
-        flag_signal(args.ready + 2 * tm + rank);
+      if (issuer) {
+        early_stamp(ctx, i, 3);
+        pending = counter;
+        ++pending_n;
       }
     }
-    if (issuer) bulk_wait_group<0>();
+    if (issuer) {
+      bulk_wait_group<0>();
+      if (ok && pending) flag_signal(pending, pending_n);
+    }
   } else if (warp >= 8) {
     // -------------------------------------------------------------- product epilogue (both CTAs, own 128 rows)
     setmaxnreg_inc<248>();
@@ -342,20 +431,22 @@ oft3_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ 
       tile_coord_r(args.raster, tiles_m, tiles_n, tile, tm, tn);
       if (!(ok = mbar_wait_warp(acc_full, tcount & 1, ctx, 40))) break;
       tc_fence_after();
-      // every MMA of the tile is done, so every load of its X.R rows (both CTAs') has landed: one count per tile
-      if (threadIdx.x == 256 && rank == 0) flag_signal(args.done + tm);
+      if (threadIdx.x == 256 && tcount < kSkewTiles - 2) skew_stamp(ctx, tcount);  // profiling build: end of each tile's MMAs
       const int row = tm * 2 * T::kBM + rank * T::kBM + quad * 32 + lane;
       __half* c_row = args.C + static_cast<long long>(row) * args.ldC;
       uint32_t p[T::kBN / 2];
 #pragma unroll
-      for (int c = 0; c < T::kBN / 32; ++c) {
-        uint32_t v[32];
+      for (int c = 0; c < T::kBN / 32; c += 2) {  // two loads in flight per wait
+        uint32_t v[32], w[32];
         tmem_ld_x32(t_row + c * 32, v);
+        tmem_ld_x32(t_row + c * 32 + 32, w);
         tmem_wait_ld();
 #pragma unroll
         for (int j = 0; j < 16; ++j) {
           __half2 h2 = __floats2half2_rn(__uint_as_float(v[2 * j]), __uint_as_float(v[2 * j + 1]));
+          __half2 g2 = __floats2half2_rn(__uint_as_float(w[2 * j]), __uint_as_float(w[2 * j + 1]));
           p[c * 16 + j] = *reinterpret_cast<uint32_t*>(&h2);
+          p[c * 16 + 16 + j] = *reinterpret_cast<uint32_t*>(&g2);
         }
       }
       tc_fence_before();
@@ -379,10 +470,22 @@ oft3_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ 
           }
         }
       }
+      // Every MMA of the tile was done when acc_full completed, so every load of its X.R rows (both CTAs') has
+      // landed: one count per tile.  Last in the tile's epilogue: the publication takes about 2 us, which must not
+      // delay the hand-back of the accumulator.
+      if (threadIdx.x == 256 && rank == 0) flag_signal(args.done + tm, 1);
     }
   }
 
   // ---------------------------------------------------------------------- teardown
+#ifdef B200_PROFILE_WAITS
+  if (threadIdx.x == 0) {
+    ctx.prof_cycles[7] += static_cast<unsigned long long>(clock64() - kernel_c0);
+    ctx.prof_count[7] += 1u;
+    ctx.prof_site[7] = 63;
+  }
+#endif
+  wait_profile_flush(ctx);
   __syncthreads();
   if (*abort_flag) {  // a wait ran out: let the copies in flight land before shared and tensor memory go away
     for (int i = 0; i < 200; ++i) __nanosleep(1000);

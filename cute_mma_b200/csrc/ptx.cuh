@@ -138,6 +138,15 @@ __device__ __forceinline__ void trace_stamp(const WaitCtx& ctx, unsigned unit, i
   }
 #endif
 }
+// Profiling build: globaltimer stamps of CTA 0 for its first kTraceUnits work items (same area as trace_stamp).
+__device__ __forceinline__ void early_stamp(const WaitCtx& ctx, unsigned item, int event) {
+#ifdef B200_PROFILE_WAITS
+  if (blockIdx.x == 0 && item < kTraceUnits) {
+    unsigned long long* tr = reinterpret_cast<unsigned long long*>(ctx.status + kStatusInts) + 2 * kWaitSites;
+    tr[item * kTraceEvents + event] = globaltimer_ns();
+  }
+#endif
+}
 __device__ __forceinline__ void skew_stamp(const WaitCtx& ctx, unsigned tile_round) {
 #ifdef B200_PROFILE_WAITS
   if (blockIdx.x < kSkewCtas && tile_round < kSkewTiles) {
@@ -188,18 +197,18 @@ __device__ __forceinline__ int ld_acquire_gpu(const int* p) {
   asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
   return v;
 }
-// Publishes whatever the calling thread wrote (or saw complete) before: release, then one relaxed add.
-__device__ __forceinline__ void flag_signal(int* counter) {
+// Publishes whatever the calling thread wrote (or saw complete) before: one add with release semantics.
+__device__ __forceinline__ void flag_signal(int* counter, int n) {
   fence_proxy_async_all();
-  __threadfence();
-  atomicAdd(counter, 1);
+  asm volatile("red.release.gpu.global.add.s32 [%0], %1;" ::"l"(counter), "r"(n) : "memory");
 }
 // Bounded wait until *counter >= target.  False when this CTA is aborting (this wait or another one ran out).
-__device__ __forceinline__ bool flag_wait_ge(const int* counter, int target, const WaitCtx& ctx, int site) {
-  if (ld_acquire_gpu(counter) < target) {
+__device__ __forceinline__ bool flag_wait_ge_impl(const int* counter, int target, const WaitCtx& ctx, int site) {
+  // polls with plain (volatile) loads; the acquire that orders the data behind the counter comes once, at the end
+  if (*reinterpret_cast<const volatile int*>(counter) < target) {
     const unsigned long long t0 = globaltimer_ns();
     int it = 0;
-    while (ld_acquire_gpu(counter) < target) {
+    while (*reinterpret_cast<const volatile int*>(counter) < target) {
       if ((++it & 15) == 0) {
         if (*ctx.abort_flag) return false;
         if (globaltimer_ns() - t0 > ctx.limit_ns) {
@@ -207,11 +216,32 @@ __device__ __forceinline__ bool flag_wait_ge(const int* counter, int target, con
           return false;
         }
       }
-      __nanosleep(100);
+      __nanosleep(32);
     }
   }
+  asm volatile("fence.acq_rel.gpu;" ::: "memory");
   fence_proxy_async_all();
   return true;
+}
+
+// One look, no waiting: true (with the same fences as a completed wait) when the counter has reached target.
+__device__ __forceinline__ bool flag_test_ge(const int* counter, int target) {
+  if (*reinterpret_cast<const volatile int*>(counter) < target) return false;
+  asm volatile("fence.acq_rel.gpu;" ::: "memory");
+  fence_proxy_async_all();
+  return true;
+}
+__device__ __forceinline__ bool flag_wait_ge(const int* counter, int target, const WaitCtx& ctx, int site) {
+#if defined(B200_PROFILE_WAITS) && !defined(B200_PROFILE_CYCLES_ONLY)
+  const long long c0 = clock64();
+  const bool ok = flag_wait_ge_impl(counter, target, ctx, site);
+  ctx.prof_cycles[site & 7] += static_cast<unsigned long long>(clock64() - c0);
+  ctx.prof_count[site & 7] += 1u;
+  ctx.prof_site[site & 7] = site;
+  return ok;
+#else
+  return flag_wait_ge_impl(counter, target, ctx, site);
+#endif
 }
 
 // Whole-warp form for roles whose next instruction is warp-collective (tcgen05.ld / st / wait):
@@ -382,6 +412,12 @@ __device__ __forceinline__ void tma_load_2d_pair_hint(uint32_t smem_dst, const C
       "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1, {%3, %4}], [%2], %5;"
       ::"r"(smem_dst), "l"(reinterpret_cast<uint64_t>(m)), "r"(bar & kPeerBitMask), "r"(x), "r"(y), "l"(hint)
       : "memory");
+}
+// Asks the copy engine to bring a tile into L2 ahead of the load that will use it (no shared memory, no barrier).
+__device__ __forceinline__ void tma_prefetch_2d(const CUtensorMap* m, int x, int y) {
+  asm volatile("cp.async.bulk.prefetch.tensor.2d.L2.global.tile [%0, {%1, %2}];"
+               ::"l"(reinterpret_cast<uint64_t>(m)), "r"(x), "r"(y)
+               : "memory");
 }
 // Pre-encoded L2 cache policies (what createpolicy.fractional.L2::evict_* with fraction 1.0 returns).
 constexpr uint64_t kL2EvictNormal = 0x1000000000000000ull;
