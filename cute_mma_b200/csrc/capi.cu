@@ -607,12 +607,16 @@ int launch_oft3(int m, int n, int k, const void* A, int ldA, const void* B, int 
   const bool streams = big && static_cast<long long>(n) * k * 2 > st->l2_bytes;
   unsigned long long hint_a = streams ? kL2EvictLast : kL2EvictNormal, hint_b = streams ? kL2EvictFirst : kL2EvictNormal;
   if (const int h = opt(kOptL2Hints); h >= 0) { hint_a = hint_word(h / 10); hint_b = hint_word(h % 10); }
-  // No phase lock by default: the ready / done counters already keep the pairs within a band of each other, and
-  // with the lock on top this kernel measured 8 to 17 % slower (interleaved runs, M 65536, K 8192, N 3584 and 28672).
+  // Phase lock of the tile rounds only when W streams from DRAM: the pairs that share a W tile then fetch it
+  // together (one-pass ncu counters at M 16384, K 8192, N 28672: DRAM reads 19.1 -> 5.8 GB per launch, 6.13 -> 5.53 ms).
+  // With W resident in L2 the ready / done counters keep the pairs close enough and the lock only costs time
+  // (interleaved runs at M 65536, K 8192, N 3584: 17 % slower with it).
   (void)big;
-  int tile_sync = 0;
+  int tile_sync = streams ? 1 : 0;
   if (opt(kOptTileSync) >= 0) tile_sync = opt(kOptTileSync);
-  const int prefetch_w = opt(kOptPrefetch) >= 0 ? opt(kOptPrefetch) : (streams ? 4 : 0);
+  // (asking W tiles into L2 a few K steps ahead of their loads was measured too: with the phase lock it added
+  // 1.2 GB of DRAM reads and 5 % of time at the shape above, so it stays off unless the option asks for it)
+  const int prefetch_w = opt(kOptPrefetch) >= 0 ? opt(kOptPrefetch) : 0;
   Oft3Args args{m, n, k, static_cast<__half*>(C), ldC, st->status, raster, big ? kL2EvictFirst : kL2EvictNormal, hint_a, hint_b,
                 tile_sync, counters + 3 * tiles_m, prefetch_w, slots, counters, counters + 2 * tiles_m};
   auto kernel = oft3_kernel<T>;

@@ -64,12 +64,14 @@ class HostSlabRunner:
     """End-to-end N-sharded product from HOST buffers on the ranks of one node.
 
     Every rank needs all of X, but X crosses the host link only once per node: rank r uploads rows
-    row_slice(m, world, r) of X from its (pinned) host buffer, and the slices are all-gathered over NVLink
-    (torch.distributed, NCCL on GPUs) while each rank's slab of W^T and R go up on a second stream.  Then the
-    rank's slab product runs (ops.oft_tn on the device buffers) and its [m][n_loc] slab of Y comes back to
-    host memory in row chunks whose downloads overlap the next chunk's product.  Device buffers are allocated
-    once per runner.  ``compute`` / ``device`` exist so that the data movement can be exercised on CPU ranks over
-    gloo with the oracle standing in for the kernel."""
+    row_slice(m, world, r) of X from its (pinned) host buffer and the slices are all-gathered over NVLink
+    (torch.distributed, NCCL on GPUs).  The slice goes up in ``chunks`` row chunks; as soon as chunk j of every
+    rank is gathered, the rank's slab product runs on those world x chunk rows and their [rows][n_loc] piece of Y
+    goes back to host memory while later chunks are still uploading, gathering and multiplying (four streams:
+    upload, collective, product, download).  The slab of W^T and R go up right behind the first chunk of X.
+    Device buffers are allocated once per runner; rows are independent, so the chunking changes no bit.
+    ``compute`` / ``device`` exist so that the data movement can be exercised on CPU ranks over gloo with the
+    oracle standing in for the kernel."""
 
     def __init__(self, m, n_total, k, n0, n1, *, group_size=None, reconn_sz=8, world=None, rank=None, device=None, compute=None,
                  lib=None, chunks=8):
@@ -87,64 +89,128 @@ class HostSlabRunner:
         self.r_rows = max(1, self.n_loc // self.gs_loc) * reconn_sz
         self.device = torch.device(device if device is not None else "cuda")
         self.compute, self.lib = compute, lib
-        self.per = (m + self.world - 1) // self.world
+        self.per = (m + self.world - 1) // self.world                 # rows of X per rank (the last slices may be short)
+        self.pc = max(8, ((self.per + chunks - 1) // chunks + 7) // 8 * 8)  # rows per chunk of a rank's slice
+        self.n_chunks = (self.per + self.pc - 1) // self.pc
         f16 = torch.float16
-        self.dX = torch.empty((self.per * self.world, k), dtype=f16, device=self.device)  # padded to equal slices
+        self.dSend = torch.zeros((self.n_chunks, self.pc, k), dtype=f16, device=self.device)             # my slice, chunked, zero padded
+        self.dX = torch.empty((self.n_chunks, self.world * self.pc, k), dtype=f16, device=self.device)   # gathered: [chunk][rank][row]
         self.dW = torch.empty((self.n_loc, k), dtype=f16, device=self.device)
         self.dR = torch.empty((self.r_rows, k), dtype=f16, device=self.device)
-        self.dY = torch.empty((m, self.n_loc), dtype=f16, device=self.device)
+        self.dY = torch.empty((self.n_chunks, self.world * self.pc, self.n_loc), dtype=f16, device=self.device)
         self.cuda = self.device.type == "cuda"
         if self.cuda:
-            self.s_in, self.s_out = torch.cuda.Stream(self.device), torch.cuda.Stream(self.device)
-        self.chunk_rows = max(256, ((m + chunks - 1) // chunks + 255) // 256 * 256)
+            self.s_in, self.s_comm, self.s_out = (torch.cuda.Stream(self.device) for _ in range(3))
 
     def bytes_per_step(self):
         """(host-to-device, device-to-host) bytes this rank moves per call."""
         r0, r1 = row_slice(self.m, self.world, self.rank)
         return ((r1 - r0) * self.k + self.n_loc * self.k + self.r_rows * self.k) * 2, self.m * self.n_loc * 2
 
-    def __call__(self, hX_rows, hW_slab, hR_slab, hY_slab):
-        """hX_rows: this rank's rows row_slice(m, world, rank) of X [rows][k]; hW_slab [n_loc][k]; hR_slab
-        [r_rows][k]; hY_slab [m][n_loc] (written).  Host tensors, pinned for asynchronous copies.  Returns when
-        hY_slab is complete."""
-        torch, dist = self.torch, self.dist
-        r0, r1 = row_slice(self.m, self.world, self.rank)
-        mine = self.dX[self.rank * self.per: self.rank * self.per + self.per]
-        if self.cuda:
-            main = torch.cuda.current_stream(self.device)
-            self.s_in.wait_stream(main)
-            with torch.cuda.stream(self.s_in):  # W and R go up beside the slice of X and the all-gather
-                self.dW.copy_(hW_slab, non_blocking=True)
-                self.dR.copy_(hR_slab, non_blocking=True)
-            if r1 > r0:
-                mine[: r1 - r0].copy_(hX_rows, non_blocking=True)
-        else:
-            self.dW.copy_(hW_slab)
-            self.dR.copy_(hR_slab)
-            if r1 > r0:
-                mine[: r1 - r0].copy_(hX_rows)
+    def _rows_of(self, r: int, j: int) -> int:
+        """Valid rows of chunk j of rank r's slice."""
+        rows_r = min(self.per, max(0, self.m - r * self.per))
+        return min(self.pc, max(0, rows_r - j * self.pc))
+
+    # the four legs, each on the stream the caller has made current
+    def _upload_chunk(self, hX_rows, j):
+        rows = self._rows_of(self.rank, j)
+        if rows > 0:
+            self.dSend[j, :rows].copy_(hX_rows[j * self.pc: j * self.pc + rows], non_blocking=True)
+
+    def _gather_chunk(self, j):
         if self.world > 1:
-            # in place on NCCL (rank r's input is slice r of the output); a copy of the slice where the backend may not alias
-            dist.all_gather_into_tensor(self.dX, mine if self.cuda else mine.clone())
-        if self.cuda:
-            main.wait_stream(self.s_in)
+            self.dist.all_gather_into_tensor(self.dX[j], self.dSend[j])
+        else:
+            self.dX[j].copy_(self.dSend[j])
+
+    def _product_chunk(self, j):
+        torch = self.torch
         fn = self.compute or ops.oft_tn
         kwargs = dict(group_size=self.gs_loc, reconn_sz=self.b)
         if self.compute is None:
             kwargs["lib"] = self.lib
-        for c0 in range(0, self.m, self.chunk_rows):
-            rows = min(self.chunk_rows, self.m - c0)
-            stream = torch.cuda.current_stream(self.device).cuda_stream if self.cuda else None
-            fn(rows, self.n_loc, self.k, self.dX[c0:], self.k, self.dW, self.k, self.dR, self.k, self.dY[c0:], self.n_loc, stream, **kwargs)
-            if self.cuda:
-                self.s_out.wait_stream(main)
-                with torch.cuda.stream(self.s_out):
-                    hY_slab[c0: c0 + rows].copy_(self.dY[c0: c0 + rows], non_blocking=True)
-            else:
-                hY_slab[c0: c0 + rows].copy_(self.dY[c0: c0 + rows])
-        if self.cuda:
-            self.s_out.synchronize()
-            main.synchronize()
+        stream = torch.cuda.current_stream(self.device).cuda_stream if self.cuda else None
+        rows = self.world * self.pc
+        fn(rows, self.n_loc, self.k, self.dX[j], self.k, self.dW, self.k, self.dR, self.k, self.dY[j], self.n_loc, stream, **kwargs)
+
+    def _download_chunk(self, hY_slab, j):
+        for r in range(self.world):
+            rows = self._rows_of(r, j)
+            if rows > 0:
+                g0 = r * self.per + j * self.pc
+                hY_slab[g0: g0 + rows].copy_(self.dY[j, r * self.pc: r * self.pc + rows], non_blocking=True)
+
+    def __call__(self, hX_rows, hW_slab, hR_slab, hY_slab):
+        """hX_rows: this rank's rows row_slice(m, world, rank) of X [rows][k]; hW_slab [n_loc][k]; hR_slab
+        [r_rows][k]; hY_slab [m][n_loc] (written).  Host tensors, pinned for asynchronous copies.  Returns when
+        hY_slab is complete."""
+        torch = self.torch
+        if not self.cuda:
+            self.dW.copy_(hW_slab)
+            self.dR.copy_(hR_slab)
+            for j in range(self.n_chunks):
+                self._upload_chunk(hX_rows, j)
+                self._gather_chunk(j)
+                self._product_chunk(j)
+                self._download_chunk(hY_slab, j)
+            return
+        main = torch.cuda.current_stream(self.device)
+        for s in (self.s_in, self.s_comm, self.s_out):
+            s.wait_stream(main)
+        ev_w = torch.cuda.Event()
+        for j in range(self.n_chunks):
+            ev_up, ev_g, ev_p = torch.cuda.Event(), torch.cuda.Event(), torch.cuda.Event()
+            with torch.cuda.stream(self.s_in):
+                self._upload_chunk(hX_rows, j)
+                ev_up.record(self.s_in)
+                if j == 0:  # W and R right behind the first rows of X: the first product needs all three
+                    self.dW.copy_(hW_slab, non_blocking=True)
+                    self.dR.copy_(hR_slab, non_blocking=True)
+                    ev_w.record(self.s_in)
+            with torch.cuda.stream(self.s_comm):
+                self.s_comm.wait_event(ev_up)
+                self._gather_chunk(j)
+                ev_g.record(self.s_comm)
+            main.wait_event(ev_g)
+            if j == 0:
+                main.wait_event(ev_w)
+            self._product_chunk(j)
+            ev_p.record(main)
+            with torch.cuda.stream(self.s_out):
+                self.s_out.wait_event(ev_p)
+                self._download_chunk(hY_slab, j)
+        self.s_out.synchronize()
+        main.synchronize()
+        self.s_in.synchronize()
+        self.s_comm.synchronize()
+
+    def leg_times(self, hX_rows, hW_slab, hR_slab, hY_slab) -> dict:
+        """Milliseconds of each leg of one call run on its own, back to back on one stream (no overlap): what the
+        overlapped call is made of.  GPU ranks only."""
+        import time
+
+        torch = self.torch
+
+        def timed(fn):
+            if self.world > 1:
+                self.dist.barrier()
+            torch.cuda.synchronize(self.device)
+            t0 = time.perf_counter()
+            fn()
+            torch.cuda.synchronize(self.device)
+            return (time.perf_counter() - t0) * 1e3
+
+        def upload():
+            for j in range(self.n_chunks):
+                self._upload_chunk(hX_rows, j)
+            self.dW.copy_(hW_slab, non_blocking=True)
+            self.dR.copy_(hR_slab, non_blocking=True)
+
+        return {"h2d_x_slice_w_r": timed(upload),
+                "all_gather_x": timed(lambda: [self._gather_chunk(j) for j in range(self.n_chunks)]),
+                "products": timed(lambda: [self._product_chunk(j) for j in range(self.n_chunks)]),
+                "d2h_y_slab": timed(lambda: [self._download_chunk(hY_slab, j) for j in range(self.n_chunks)])}
 
 
 class SlabProductAllGather:
