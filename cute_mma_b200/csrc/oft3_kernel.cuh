@@ -134,6 +134,7 @@ oft3_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ 
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem_gen + (bars - smem_base) + T::kNumBars * 8);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
   volatile int* conv_abort = reinterpret_cast<volatile int*>(tmem_slot + 2);  // rotation epilogue: one of its warps gave up
+  volatile unsigned* seen_tile = reinterpret_cast<volatile unsigned*>(tmem_slot + 3);  // tile whose X.R rows the epilogue saw ready
   const WaitCtx ctx{abort_flag, args.status, kWaitLimitNs};
 #ifdef B200_PROFILE_WAITS
   const long long kernel_c0 = clock64();
@@ -154,6 +155,7 @@ oft3_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ 
   if (threadIdx.x == 0) {
     *abort_flag = 0;
     *conv_abort = 0;
+    *seen_tile = ~0u;
     for (int s = 0; s < T::kS1; ++s) { mbar_init(full1 + 8 * s, 1); mbar_init(empty1 + 8 * s, 1); }
     for (int s = 0; s < T::kS2; ++s) { mbar_init(full2 + 8 * s, 1); mbar_init(empty2 + 8 * s, 1); }
     for (int i = 0; i < T::kXrBufs; ++i) { mbar_init(x_acc + 8 * i, 1); mbar_init(x_empty + 8 * i, 256); }
@@ -184,7 +186,6 @@ oft3_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ 
       bool ok = true;
       unsigned done_rounds = 0, sync_target = 0, next_tm = 0;
       int next_n0 = -1;
-      bool have_next = false;
       for (unsigned tile = pair; ok && tile < num_tiles; tile += num_pairs) {
         if (args.tile_sync && done_rounds > 0) {
           if (!(ok = tile_round_sync(args.rounds + rank, sync_target, ctx, 12))) break;
@@ -196,11 +197,14 @@ oft3_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ 
         }
         unsigned tm, tn;
         tile_coord_r(args.raster, tiles_m, tiles_n, tile, tm, tn);
-        // this CTA's 128 rows of the row block: every unit of them has been stored and is visible.  (Usually known
-        // since the middle of the previous tile, see below: the fences behind the counter take 1 to 2 us.)
-        if (!(have_next && next_tm == tm))
-          if (!(ok = flag_wait_ge(args.ready + 2 * tm + rank, static_cast<int>(upb), ctx, 14))) break;
-        have_next = false;
+        // This CTA's 128 rows of the row block: every unit of them has been stored and is visible.  Usually the
+        // epilogue has seen that already while this thread was feeding the previous tile (the fences behind the
+        // counter take 1 to 2 us, during which this thread could issue no load and the MMAs would run dry).
+        if (*seen_tile == tile) {
+          __threadfence_block();
+        } else if (!(ok = flag_wait_ge(args.ready + 2 * tm + rank, static_cast<int>(upb), ctx, 14))) {
+          break;
+        }
         if (tile == pair) skew_stamp(ctx, kSkewTiles - 1);  // profiling build: when the first tile's rows were ready
         const int xr_row0 = static_cast<int>(tm % static_cast<unsigned>(args.slots)) * 2 * T::kBM + rank * T::kBM;
         const int n0 = tn * T::kBN + rank * T::kBNHalf;  // this CTA's half of the W tile
@@ -222,12 +226,7 @@ oft3_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ 
             if (q < k_steps) tma_prefetch_2d(&tmap_b, q * T::kBK, n0);
             else if (next_n0 >= 0 && q - k_steps < k_steps) tma_prefetch_2d(&tmap_b, (q - k_steps) * T::kBK, next_n0);
           }
-          if (ks == k_steps / 2 && next_n0 >= 0) {
-            // The ring is full and this thread would only wait for a free slot: look at the next tile's rows now.
-            // If they are there already (the normal case), the acquire and proxy fences are paid here instead
-            // of between two tiles, where the MMAs would run dry behind them.
-            have_next = flag_test_ge(args.ready + 2 * next_tm + rank, static_cast<int>(upb));
-          }
+
         }
       }
       // leaving after its last round, this thread still counts for the rendezvous the others make
@@ -252,7 +251,7 @@ oft3_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ 
         const int m0 = tm * 2 * T::kBM + rank * T::kBM, k0 = ku * T::kUnitK;
         for (int su = 0; su < T::kStagesPerUnit; ++su, ++it) {
           const int s = it % T::kS1;
-          if (!(ok = mbar_wait(empty1 + 8 * s, ((it / T::kS1) & 1) ^ 1, ctx, 10))) break;
+          if (!(ok = mbar_wait_parked(empty1 + 8 * s, ((it / T::kS1) & 1) ^ 1, ctx, 10))) break;
           if (su == 0) early_stamp(ctx, unit_no, 0);
           if (rank == 0) mbar_expect_tx(full1 + 8 * s, 2 * T::kS1Bytes);
           const uint32_t x_dst = ring1 + s * T::kS1Bytes;
@@ -272,11 +271,11 @@ oft3_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ 
       bool ok = true;
       for (unsigned i = 0; ok && i < my_units; ++i) {
         const int xb = i % T::kXrBufs;
-        if (!(ok = mbar_wait(x_empty + 8 * xb, ((i / T::kXrBufs) & 1) ^ 1, ctx, 20))) break;
+        if (!(ok = mbar_wait_parked(x_empty + 8 * xb, ((i / T::kXrBufs) & 1) ^ 1, ctx, 20))) break;
         const uint32_t d1 = tmem_base + T::kColXr + xb * T::kUnitK;
         for (int su = 0; su < T::kStagesPerUnit; ++su, ++it) {
           const int s = it % T::kS1;
-          if (!(ok = mbar_wait(full1 + 8 * s, (it / T::kS1) & 1, ctx, 21))) break;
+          if (!(ok = mbar_wait_parked(full1 + 8 * s, (it / T::kS1) & 1, ctx, 21))) break;
           tc_fence_after();
           const uint64_t x_desc = x_desc0 + static_cast<uint64_t>(s * (T::kS1Bytes >> 4));
           const uint64_t r_desc = r_desc0 + static_cast<uint64_t>(s * (T::kS1Bytes >> 4));
@@ -474,6 +473,16 @@ oft3_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ 
       // landed: one count per tile.  Last in the tile's epilogue: the publication takes about 2 us, which must not
       // delay the hand-back of the accumulator.
       if (threadIdx.x == 256 && rank == 0) flag_signal(args.done + tm, 1);
+      // ... and a look ahead for the producer of the {XR, W} ring: are the rows of this pair's tile after next there?
+      // (The next tile is already being fed.)  One look; if not, the producer waits for them itself.
+      if (threadIdx.x == 256 && tile + 2 * num_pairs < num_tiles) {
+        unsigned tm2, tn2;
+        tile_coord_r(args.raster, tiles_m, tiles_n, tile + 2 * num_pairs, tm2, tn2);
+        if (flag_test_ge(args.ready + 2 * tm2 + rank, static_cast<int>(upb))) {
+          __threadfence_block();
+          *seen_tile = tile + 2 * num_pairs;
+        }
+      }
     }
   }
 

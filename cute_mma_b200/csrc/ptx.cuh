@@ -244,11 +244,59 @@ __device__ __forceinline__ bool flag_wait_ge(const int* counter, int target, con
 #endif
 }
 
-// Whole-warp form for roles whose next instruction is warp-collective (tcgen05.ld / st / wait):
-// every lane gets the same answer, so the warp stays converged when a wait gives up.
+// Waits that may take long and are not on the critical path of the tensor pipe (an epilogue waiting a whole tile
+// for its accumulator, the rotation roles waiting for work): try_wait with a suspend-time hint, so that the
+// hardware parks the thread until the phase completes instead of the thread polling.
+__device__ __forceinline__ bool mbar_try_wait_parked(uint32_t bar, uint32_t parity, uint32_t hint_ns) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity), "r"(hint_ns)
+      : "memory");
+  return ok != 0;
+}
+__device__ __forceinline__ bool mbar_wait_parked_impl(uint32_t bar, uint32_t parity, const WaitCtx& ctx, int site) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const unsigned long long t0 = globaltimer_ns();
+  int it = 0;
+  while (true) {
+    if (mbar_try_wait_parked(bar, parity, 20000u)) return true;
+    if ((++it & 3) == 0) {
+      if (*ctx.abort_flag) return false;
+      if (globaltimer_ns() - t0 > ctx.limit_ns) {
+        report_timeout(ctx, site, parity);
+        return false;
+      }
+    }
+  }
+}
+__device__ __forceinline__ bool mbar_wait_parked(uint32_t bar, uint32_t parity, const WaitCtx& ctx, int site) {
+#if defined(B200_PROFILE_WAITS) && !defined(B200_PROFILE_CYCLES_ONLY)
+  const long long c0 = clock64();
+  const bool ok = mbar_wait_parked_impl(bar, parity, ctx, site);
+  ctx.prof_cycles[site & 7] += static_cast<unsigned long long>(clock64() - c0);
+  ctx.prof_count[site & 7] += 1u;
+  ctx.prof_site[site & 7] = site;
+  return ok;
+#else
+  return mbar_wait_parked_impl(bar, parity, ctx, site);
+#endif
+}
+
+// Whole-warp form for roles whose next instruction is warp-collective (tcgen05.ld / st / wait): every lane gets
+// the same answer, so the warp stays converged when a wait gives up.  One lane waits (parked); the others then
+// look at the completed phase once, which gives each of them the barrier's acquire.
 __device__ __forceinline__ bool mbar_wait_warp(uint32_t bar, uint32_t parity, const WaitCtx& ctx, int site) {
-  const bool ok = mbar_wait(bar, parity, ctx, site);
-  return __all_sync(0xffffffffu, ok);
+  bool ok = true;
+  if ((threadIdx.x & 31) == 0) ok = mbar_wait_parked(bar, parity, ctx, site);
+  ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+  if (ok)
+    while (!mbar_try_wait(bar, parity)) {
+    }
+  return ok;
 }
 
 // Register re-balancing between warpgroups (all four warps of a warpgroup execute the same one).
