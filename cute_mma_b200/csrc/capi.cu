@@ -274,20 +274,20 @@ void release_round_counters(DeviceState* st, cudaStream_t stream, int* p) {
 
 template <typename TIn, typename TOut, bool kNT, class P, int kBN>
 int launch_gemm_bn(int m, int n, int k, const void* A, int ldA, const void* B, int ldB, void* C, int ldC, void* stream_v,
-                   int k2, const void* A2, int ldA2, const void* B2, int ldB2);
+                   int k2, const void* A2, int ldA2, const void* B2, int ldB2, float alpha, float beta);
 
 // (A pair kernel with half the N extent was tried for evening out the last wave of tiles and for small problems:
 // a half-width tile takes 0.8 of the time of a full one, M = N = K = 4096 TF32 0.286 ms against 0.203 ms, so it
 // never pays; the tiles of a short last wave are split along K instead, see below.)
 template <typename TIn, typename TOut, bool kNT, class P>
 int launch_gemm(int m, int n, int k, const void* A, int ldA, const void* B, int ldB, void* C, int ldC, void* stream_v,
-                int k2 = 0, const void* A2 = nullptr, int ldA2 = 0, const void* B2 = nullptr, int ldB2 = 0) {
-  return launch_gemm_bn<TIn, TOut, kNT, P, P::bN>(m, n, k, A, ldA, B, ldB, C, ldC, stream_v, k2, A2, ldA2, B2, ldB2);
+                int k2 = 0, const void* A2 = nullptr, int ldA2 = 0, const void* B2 = nullptr, int ldB2 = 0, float alpha = 1.f, float beta = 0.f) {
+  return launch_gemm_bn<TIn, TOut, kNT, P, P::bN>(m, n, k, A, ldA, B, ldB, C, ldC, stream_v, k2, A2, ldA2, B2, ldB2, alpha, beta);
 }
 
 template <typename TIn, typename TOut, bool kNT, class P, int kBN>
 int launch_gemm_bn(int m, int n, int k, const void* A, int ldA, const void* B, int ldB, void* C, int ldC, void* stream_v,
-                   int k2, const void* A2, int ldA2, const void* B2, int ldB2) {
+                   int k2, const void* A2, int ldA2, const void* B2, int ldB2, float alpha, float beta) {
   constexpr bool kPair = CtasOf<P>::value == 2;
   using T1 = GemmTraits<TIn, TOut, kNT, kNT, kBN, kPair ? 4 : P::bP>;
   using T2 = Gemm2Traits<TIn, TOut, kNT, kNT, kBN, kPair ? P::bP : 6>;
@@ -299,7 +299,8 @@ int launch_gemm_bn(int m, int n, int k, const void* A, int ldA, const void* B, i
   if (m == 0 || n == 0) return B200_OK;
   if (k2 < 0 || (k2 > 0 && (!A2 || !B2))) return fail(B200_EINVAL, "bad second operand pair (k2=%d)", k2);
   if (k2 > 0 && (kNT || !kPair)) return fail(B200_EUNSUPPORTED, "a second operand pair needs K-contiguous operands and the CTA-pair kernel (ctas = 2)");
-  if (k == 0 && k2 > 0) return launch_gemm_bn<TIn, TOut, kNT, P, kBN>(m, n, k2, A2, ldA2, B2, ldB2, C, ldC, stream_v, 0, nullptr, 0, nullptr, 0);
+  if (k == 0 && k2 > 0) return launch_gemm_bn<TIn, TOut, kNT, P, kBN>(m, n, k2, A2, ldA2, B2, ldB2, C, ldC, stream_v, 0, nullptr, 0, nullptr, 0, alpha, beta);
+  if (k == 0 && beta != 0.f) return fail(B200_EUNSUPPORTED, "k = 0 with beta != 0 (C = beta * C) is not a product; scale C yourself");
   if (k == 0) {
     CUDA_TRY(cudaMemset2DAsync(C, static_cast<size_t>(ldC) * sizeof(TOut), 0, static_cast<size_t>(m) * sizeof(TOut), n, stream));
     return B200_OK;
@@ -338,7 +339,7 @@ int launch_gemm_bn(int m, int n, int k, const void* A, int ldA, const void* B, i
   // A is loaded evict-last, B evict-first.  Same shape: DRAM reads 26.2 -> 17.6 GB per launch, 23.9 -> 22.4 ms.
   unsigned long long hint_a = big ? kL2EvictLast : kL2EvictNormal, hint_b = big ? kL2EvictFirst : kL2EvictNormal;
   if (const int h = opt(kOptGemmL2Hints); h >= 0) { hint_a = hint_word(h / 10); hint_b = hint_word(h % 10); }
-  GemmArgs args{m, n, k, C, ldC, st->status, raster, tile_sync, rounds, a3d, b3d, hint_a, hint_b, k2, 0u, 1, nullptr, nullptr};
+  GemmArgs args{m, n, k, C, ldC, st->status, raster, tile_sync, rounds, a3d, b3d, hint_a, hint_b, k2, 0u, 1, nullptr, nullptr, alpha, beta};
   if constexpr (kPair) {
     CUtensorMap ma2 = ma, mb2 = mb;  // never read when k2 == 0
     if (k2 > 0) {
@@ -363,7 +364,7 @@ int launch_gemm_bn(int m, int n, int k, const void* A, int ldA, const void* B, i
     long long parts = (rest > 0 && rest * 2 <= all_pairs && full_waves == 0 && !big && st->pool) ? all_pairs / rest : 1;
     if (parts > 4) parts = 4;
     if (parts > k_steps_all / 8) parts = k_steps_all / 8;
-    if (opt(kOptGemmSplit) == 0) parts = 1;
+    if (opt(kOptGemmSplit) == 0 || alpha != 1.f || beta != 0.f) parts = 1;  // the split instance sums pieces, it does not scale
     if (parts >= 2) {
       void* scratch = nullptr;
       const size_t tile_floats = static_cast<size_t>(T2::kBM) * T2::kBN;
@@ -1112,6 +1113,28 @@ int b200_gemm(char transA, char transB, int is_float, int m, int n, int k, const
   if (tn) return is_float ? b200_gemm_tn_tf32(m, n, k, A, ldA, B, ldB, C, ldC, stream) : b200_gemm_tn_f16(m, n, k, A, ldA, B, ldB, C, ldC, stream);
   if (nt) return is_float ? b200_gemm_nt_tf32(m, n, k, A, ldA, B, ldB, C, ldC, stream) : b200_gemm_nt_f16(m, n, k, A, ldA, B, ldB, C, ldC, stream);
   return fail(B200_EUNSUPPORTED, "gemm('%c','%c'): only ('T','N') and ('N','T') exist, as in the reference", transA, transB);
+}
+
+int b200_gemm_ex(char transA, char transB, int in_type, int out_type, int m, int n, int k, float alpha, const void* A, int ldA,
+                 const void* B, int ldB, float beta, void* C, int ldC, void* stream) {
+  const bool tn = (transA == 'T' || transA == 't') && (transB == 'N' || transB == 'n');
+  const bool nt = (transA == 'N' || transA == 'n') && (transB == 'T' || transB == 't');
+  g_err.clear();
+  if (!tn && !nt) return fail(B200_EUNSUPPORTED, "gemm('%c','%c'): only ('T','N') and ('N','T') exist, as in the reference", transA, transB);
+  using PH_TN = Params<half, half, MMA_T, MMA_N>;
+  using PH_NT = Params<half, half, MMA_N, MMA_T>;
+  using PF_TN = Params<float, float, MMA_T, MMA_N>;
+  using PF_NT = Params<float, float, MMA_N, MMA_T>;
+  if (in_type == B200_F16 && out_type == B200_F16)
+    return tn ? launch_gemm<__half, __half, false, PH_TN>(m, n, k, A, ldA, B, ldB, C, ldC, stream, 0, nullptr, 0, nullptr, 0, alpha, beta)
+              : launch_gemm<__half, __half, true, PH_NT>(m, n, k, A, ldA, B, ldB, C, ldC, stream, 0, nullptr, 0, nullptr, 0, alpha, beta);
+  if (in_type == B200_F16 && out_type == B200_F32)
+    return tn ? launch_gemm<__half, float, false, PH_TN>(m, n, k, A, ldA, B, ldB, C, ldC, stream, 0, nullptr, 0, nullptr, 0, alpha, beta)
+              : launch_gemm<__half, float, true, PH_NT>(m, n, k, A, ldA, B, ldB, C, ldC, stream, 0, nullptr, 0, nullptr, 0, alpha, beta);
+  if (in_type == B200_TF32 && out_type == B200_F32)
+    return tn ? launch_gemm<float, float, false, PF_TN>(m, n, k, A, ldA, B, ldB, C, ldC, stream, 0, nullptr, 0, nullptr, 0, alpha, beta)
+              : launch_gemm<float, float, true, PF_NT>(m, n, k, A, ldA, B, ldB, C, ldC, stream, 0, nullptr, 0, nullptr, 0, alpha, beta);
+  return fail(B200_EUNSUPPORTED, "operand / result types %d / %d: f16 -> f16, f16 -> f32 and tf32 -> f32 exist", in_type, out_type);
 }
 
 int b200_gemm_rowmajor(char transA, char transB, int is_float, int m, int n, int k, const void* A, int ldA, const void* B, int ldB,

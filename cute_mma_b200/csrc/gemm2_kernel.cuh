@@ -130,10 +130,6 @@ gemm2_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__
         for (int ks = item_ks0(item), ks_end = item_ks1(item); ks < ks_end; ++ks, ++it) {
           const int s = it % T::kStages;
           if (!(ok = mbar_wait(empty_bar(s), ((it / T::kStages) & 1) ^ 1, ctx, 1))) break;
-#ifdef B200_DEBUG_NO_TMA  // timing experiment only: the ring is never filled, results are garbage
-          if (rank == 0) mbar_arrive(full_bar(s));
-          continue;
-#endif
           if (rank == 0) mbar_expect_tx(full_bar(s), 2 * T::kStageBytes);  // both CTAs' bytes land on this barrier
           const uint32_t a_dst = smem_base + s * T::kStageBytes, b_dst = a_dst + T::kABytes;
           const bool second = ks >= k_steps1;
@@ -239,7 +235,8 @@ gemm2_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__
     const int quad = warp & 3;
     uint32_t tcount = 0;
     bool ok = true;
-    TOut* __restrict__ C = reinterpret_cast<TOut*>(args.C);
+    TOut* C = reinterpret_cast<TOut*>(args.C);
+    const bool scaled = args.alpha != 1.f || args.beta != 0.f;
     for (unsigned item = pair; ok && item < num_items; item += num_pairs, ++tcount) {
       const unsigned tile = item_tile(item);
       unsigned tm, tn;
@@ -312,10 +309,6 @@ gemm2_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__
           continue;
         }
       }
-#ifdef B200_EXP_NO_EPI  // timing experiment: the accumulator is never read or stored
-      (void)row; (void)t_row; (void)C; (void)tm; (void)tn;
-      if (false)
-#endif
 #pragma unroll 1
       for (int c = 0; c < T::kBN / 32; ++c) {
         uint32_t v[32];
@@ -326,9 +319,14 @@ gemm2_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__
 #pragma unroll
           for (int j = 0; j < 32; ++j) {
             if (col0 + j < args.n) {
-              const float f = __uint_as_float(v[j]);
-              if constexpr (sizeof(TOut) == 2) C[row + static_cast<long long>(col0 + j) * args.ldC] = __float2half_rn(f);
-              else C[row + static_cast<long long>(col0 + j) * args.ldC] = f;
+              float f = __uint_as_float(v[j]);
+              TOut* dst = C + row + static_cast<long long>(col0 + j) * args.ldC;
+              if (scaled) {  // C = alpha * A.B^T + beta * C (the epilogue the reference leaves as a stub, gemm_tc.hpp:241)
+                f *= args.alpha;
+                if (args.beta != 0.f) f += args.beta * static_cast<float>(*dst);
+              }
+              if constexpr (sizeof(TOut) == 2) *dst = __float2half_rn(f);
+              else *dst = f;
             }
           }
         }

@@ -58,6 +58,7 @@ struct GemmArgs {
   int split_parts;
   float* split_scratch;
   int* split_count;
+  float alpha = 1.f, beta = 0.f;  // C = alpha * A.B^T + beta * C; (1, 0) takes the plain store
 };
 
 template <class T>
@@ -192,7 +193,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
     const int quad = warp & 3;  // TMEM lane quadrant this warp may access
     uint32_t tcount = 0;
     bool ok = true;
-    TOut* __restrict__ C = reinterpret_cast<TOut*>(args.C);
+    TOut* C = reinterpret_cast<TOut*>(args.C);
+    const bool scaled = args.alpha != 1.f || args.beta != 0.f;
     for (unsigned tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x, ++tcount) {
       unsigned tm, tn;
       tile_coord_r(args.raster, tiles_m, tiles_n, tile, tm, tn);
@@ -211,9 +213,14 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
 #pragma unroll
           for (int j = 0; j < 32; ++j) {
             if (col0 + j < args.n) {
-              const float f = __uint_as_float(v[j]);
-              if constexpr (sizeof(TOut) == 2) C[row + static_cast<long long>(col0 + j) * args.ldC] = __float2half_rn(f);
-              else C[row + static_cast<long long>(col0 + j) * args.ldC] = f;
+              float f = __uint_as_float(v[j]);
+              TOut* dst = C + row + static_cast<long long>(col0 + j) * args.ldC;
+              if (scaled) {  // C = alpha * A.B^T + beta * C (the epilogue the reference leaves as a stub, gemm_tc.hpp:241)
+                f *= args.alpha;
+                if (args.beta != 0.f) f += args.beta * static_cast<float>(*dst);
+              }
+              if constexpr (sizeof(TOut) == 2) *dst = __float2half_rn(f);
+              else *dst = f;
             }
           }
         }

@@ -141,15 +141,10 @@ oft_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ C
         for (int st = 0; st < units * T::kStagesPerUnit; ++st, ++it) {
           const int s = it % T::kS1;
           if (!(ok = mbar_wait(empty1 + 8 * s, ((it / T::kS1) & 1) ^ 1, ctx, 10))) break;
-#ifdef B200_DEBUG_NO_TMA  // timing experiment only: the rings are never filled, results are garbage
-          mbar_arrive(full1 + 8 * s);
-          (void)m0; (void)r_row0;
-#else
           mbar_expect_tx(full1 + 8 * s, T::kS1Bytes);
           const uint32_t a_dst = ring1 + s * T::kS1Bytes;
           tma_load_2d(a_dst, &tmap_a, full1 + 8 * s, st * T::kBK, m0);
           tma_load_2d(a_dst + T::kABytes, &tmap_r, full1 + 8 * s, st * T::kBK, r_row0);
-#endif
         }
       }
     }
@@ -167,13 +162,8 @@ oft_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ C
         for (int st = 0; st < units * T::kStagesPerUnit; ++st, ++it) {
           const int s = it % T::kS2;
           if (!(ok = mbar_wait(empty2 + 8 * s, ((it / T::kS2) & 1) ^ 1, ctx, 11))) break;
-#ifdef B200_DEBUG_NO_TMA
-          mbar_arrive(full2 + 8 * s);
-          (void)n0;
-#else
           mbar_expect_tx(full2 + 8 * s, T::kS2Bytes);
           tma_load_2d(ring2 + s * T::kS2Bytes, &tmap_b, full2 + 8 * s, st * T::kBK, n0);
-#endif
         }
       }
     }

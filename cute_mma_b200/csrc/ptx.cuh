@@ -54,9 +54,6 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
 
 // Non-blocking look at a barrier phase (try_wait may suspend the thread; this never does).
 __device__ __forceinline__ bool mbar_test_wait(uint32_t bar, uint32_t parity) {
-#ifdef B200_NO_PEEK  // timing experiment: never look ahead
-  return false;
-#endif
   uint32_t ok;
   asm volatile(
       "{\n\t.reg .pred p;\n\t"

@@ -25,7 +25,7 @@ OK, EINVAL, EUNSUPPORTED, ECUDA, EDEVICE = 0, 1, 2, 3, 4
 SYMBOLS = (
     "b200_oft_tn_f16", "b200_oft_tn_f16_two_pass", "b200_rotate_f16", "b200_oft_plan", "b200_oft_tn_f16_host", "b200_oft_tn_f16_static", "b200_transform_weight_f16", "b200_oft_tn_f16_a_rw", "b200_gemm_tn_f16", "b200_gemm_nt_f16", "b200_gemm_tn_tf32",
     "b200_gemm_nt_tf32", "b200_gemm", "b200_gemm_tn_f16_acc2", "b200_lora_tn_f16", "b200_gemm_rowmajor", "b200_peer_copy_async", "b200_shard_range", "b200_tile_coord", "b200_device_status", "b200_selftest_wait_timeout", "b200_wait_profile", "b200_kernel_info",
-    "b200_last_error", "b200_shutdown", "b200_static_status", "b200_set_option", "b200_get_option",
+    "b200_last_error", "b200_shutdown", "b200_static_status", "b200_set_option", "b200_get_option", "b200_gemm_ex",
 )
 
 
@@ -64,6 +64,7 @@ def load_library(path: str | None = None):
     for name in ("b200_gemm_tn_f16", "b200_gemm_nt_f16", "b200_gemm_tn_tf32", "b200_gemm_nt_tf32"):
         getattr(lib, name).argtypes = [i, i, i, vp, i, vp, i, vp, i, vp]
     lib.b200_gemm.argtypes = [c, c, i, i, i, i, vp, i, vp, i, vp, i, vp]
+    lib.b200_gemm_ex.argtypes = [c, c, i, i, i, i, i, ctypes.c_float, vp, i, vp, i, ctypes.c_float, vp, i, vp]
     lib.b200_gemm_tn_f16_acc2.argtypes = [i, i, i, vp, i, vp, i, i, vp, i, vp, i, vp, i, vp]
     lib.b200_lora_tn_f16.argtypes = [i, i, i, i, vp, i, vp, i, vp, i, vp, i, vp, i, vp]
     lib.b200_gemm_rowmajor.argtypes = [c, c, i, i, i, i, vp, i, vp, i, vp, i, vp]
@@ -231,6 +232,16 @@ def gemm(transA, transB, m, n, k, A, ldA, B, ldB, C, ldC, stream=None, *, dtype=
     lib = lib or load_library()
     _check(lib, lib.b200_gemm(transA.encode(), transB.encode(), 0 if dtype == "half" else 1, m, n, k, _ptr(A), ldA,
                               _ptr(B), ldB, _ptr(C), ldC, _stream(stream)))
+
+
+F16, F32, TF32 = 0, 1, 2
+
+
+def gemm_ex(transA, transB, m, n, k, alpha, A, ldA, B, ldB, beta, C, ldC, stream=None, *, in_type=F16, out_type=F16, lib=None) -> None:
+    """C (column-major) = alpha * A.B^T + beta * C, half or float result from half operands, float from float (TF32)."""
+    lib = lib or load_library()
+    _check(lib, lib.b200_gemm_ex(transA.encode(), transB.encode(), in_type, out_type, m, n, k, float(alpha), _ptr(A), ldA, _ptr(B), ldB,
+                                 float(beta), _ptr(C), ldC, _stream(stream)))
 
 
 def gemm_tn_acc2(m, n, k, A, ldA, B, ldB, k2, A2, ldA2, B2, ldB2, C, ldC, stream=None, *, lib=None) -> None:

@@ -145,6 +145,18 @@ int b200_lora_tn_f16(int m, int n, int k, int r, const void* X, int ldX, const v
 int b200_gemm(char transA, char transB, int is_float, int m, int n, int k,
               const void* A, int ldA, const void* B, int ldB, void* C, int ldC, void* stream);
 
+/* The epilogue variants the reference leaves out: C = alpha * A.B^T + beta * C (its axpby is a commented-out stub,
+ * gemm_tc.hpp:241; its kernels store the bare product), and a float result from half operands (the fp32
+ * accumulator stored unrounded).  in_type / out_type: B200_F16 -> B200_F16, B200_F16 -> B200_F32,
+ * B200_TF32 -> B200_F32 (float operands multiplied as TF32).  Layouts and transA / transB as in b200_gemm,
+ * C column-major.  beta != 0 reads C, which then must hold valid numbers; (alpha, beta) = (1, 0) returns the bits
+ * of b200_gemm.  Products scaled this way are never split along K. */
+#define B200_F16 0
+#define B200_F32 1
+#define B200_TF32 2
+int b200_gemm_ex(char transA, char transB, int in_type, int out_type, int m, int n, int k, float alpha,
+                 const void* A, int ldA, const void* B, int ldB, float beta, void* C, int ldC, void* stream);
+
 /* The same products with C row-major: C(i,j) at C[i*ldC + j], ldC >= n.  The reference's kernels only write
  * column-major C (gemm_tc.hpp:12-14); the rotation + GEMM route of the OFT product uses this form internally. */
 int b200_gemm_rowmajor(char transA, char transB, int is_float, int m, int n, int k,

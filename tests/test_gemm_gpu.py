@@ -52,7 +52,7 @@ SHAPES = [(128, 256, 64), (128, 256, 512), (384, 512, 256), (200, 328, 136), (72
 
 @pytest.mark.parametrize("layout", ["TN", "NT"])
 @pytest.mark.parametrize("m,n,k", SHAPES)
-def test_gemm_half(lib, cuda, layout, m, n, k):
+def test_gemm_half_matches_fp64_truth(lib, cuda, layout, m, n, k):
     A, B, ldA, ldB, _, _ = make_operands(layout, "half", m, n, k, seed=1)
     got = run_gemm(lib, cuda, layout, "half", m, n, k, A, B, ldA, ldB, ldC=m)
     ref = truth(layout, m, n, k, A, ldA, B, ldB, np.arange(m), np.arange(n))
@@ -64,7 +64,7 @@ def test_gemm_half(lib, cuda, layout, m, n, k):
 
 @pytest.mark.parametrize("layout", ["TN", "NT"])
 @pytest.mark.parametrize("m,n,k", SHAPES)
-def test_gemm_float_tf32(lib, cuda, layout, m, n, k):
+def test_gemm_float_tf32_matches_fp64_truth(lib, cuda, layout, m, n, k):
     A, B, ldA, ldB, a_rows, b_cols = make_operands(layout, "float", m, n, k, seed=2, dist="normal")
     got = run_gemm(lib, cuda, layout, "float", m, n, k, A, B, ldA, ldB, ldC=m)
     ref = truth(layout, m, n, k, A, ldA, B, ldB, np.arange(m), np.arange(n))
@@ -135,6 +135,41 @@ def test_gemm_rowmajor_is_the_transpose_of_colmajor(lib, cuda, layout, dtype):
     assert e.value.code == ops.EINVAL
 
 
+@pytest.mark.parametrize("layout", ["TN", "NT"])
+@pytest.mark.parametrize("in_type,out_type,alpha,beta", [(0, 0, 1.0, 0.0), (0, 0, 0.5, 0.0), (0, 0, -1.25, 0.75), (0, 1, 1.0, 0.0), (0, 1, 2.0, -0.5),
+                                                         (2, 1, 1.0, 0.0), (2, 1, 0.25, 1.0)])
+def test_gemm_ex_scaled_and_float_output(lib, cuda, layout, in_type, out_type, alpha, beta):
+    """b200_gemm_ex: C = alpha * A.B^T + beta * C with half or float C from half operands and float C from float (TF32)
+    operands, against fp64 arithmetic on the same inputs; (1, 0) must return the bits of the plain entry point."""
+    import torch
+
+    m, n, k = 328, 264, 200 if layout == "TN" else 264
+    dtype = "half" if in_type == 0 else "float"
+    A, B, ldA, ldB, a_rows, b_cols = make_operands(layout, dtype, m, n, k, seed=5, dist="uniform" if in_type == 0 else "normal")
+    out_dt = torch.float16 if out_type == 0 else torch.float32
+    c0 = (np.random.default_rng(6).standard_normal((n, m)) * 4).astype(np.float16 if out_type == 0 else np.float32)  # column-major C: n columns of m
+    dA, dB = torch.from_numpy(A).to(cuda), torch.from_numpy(B).to(cuda)
+    dC = torch.from_numpy(c0).to(cuda).to(out_dt).contiguous()
+    ta, tb = ("T", "N") if layout == "TN" else ("N", "T")
+    ops.gemm_ex(ta, tb, m, n, k, alpha, dA, ldA, dB, ldB, beta, dC, m, in_type=in_type, out_type=out_type, lib=lib)
+    assert ops.device_status(lib)[0] == 0
+    got = dC.cpu().numpy().T.astype(np.float64)
+    prod = truth(layout, m, n, k, A, ldA, B, ldB, np.arange(m), np.arange(n))
+    want = alpha * prod + beta * c0.T.astype(np.float64)
+    if in_type == 2:
+        floor = abs(alpha) * np.outer(np.linalg.norm(a_rows, axis=1), np.linalg.norm(b_cols, axis=1)) / np.sqrt(k) + abs(beta) * np.abs(c0.T)
+        assert np.all(np.abs(got - want) <= TF32_TOL * np.maximum(np.abs(want), floor))
+    else:
+        tol = 1e-2 if out_type == 0 else 2e-4  # float result: only the fp32 summation order separates it from fp64
+        assert np.all(np.abs(got - want) <= tol * (np.abs(want) + abs(beta) * np.abs(c0.T.astype(np.float64)) + 1.0)), float(np.abs(got - want).max())
+    if (alpha, beta) == (1.0, 0.0) and out_type == (0 if in_type == 0 else 1):
+        plain = run_gemm(lib, cuda, layout, dtype, m, n, k, A, B, ldA, ldB, ldC=m)
+        assert np.array_equal(plain.astype(np.float64), got)
+    with pytest.raises(ops.Error) as e:
+        ops.gemm_ex(ta, tb, m, n, k, 1.0, dA, ldA, dB, ldB, 0.0, dC, m, in_type=2, out_type=0, lib=lib)  # float operands, half result
+    assert e.value.code == ops.EUNSUPPORTED
+
+
 @pytest.mark.parametrize("m,n,k,k2", [(200, 328, 192, 64), (384, 512, 136, 16), (128, 256, 64, 200), (256, 256, 0, 72)])
 def test_gemm_second_operand_pair(lib, cuda, pair_build, m, n, k, k2):
     if not pair_build:
@@ -158,7 +193,7 @@ def test_gemm_second_operand_pair(lib, cuda, pair_build, m, n, k, k2):
 
 
 @pytest.mark.parametrize("m,n,k,r", [(256, 512, 256, 16), (200, 328, 192, 64), (1024, 1024, 512, 8), (128, 256, 128, 0)])
-def test_lora_matches_three_gemm_reference(lib, cuda, pair_build, m, n, k, r):
+def test_lora_matches_three_gemm_arithmetic(lib, cuda, pair_build, m, n, k, r):
     if not pair_build and r > 0:
         pytest.skip("the second operand pair is a feature of the CTA-pair kernel")
     """b200_lora_tn_f16 against the arithmetic of the reference's comparator (playgrounds/lora.cu:33-64) done in
