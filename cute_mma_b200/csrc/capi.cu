@@ -725,6 +725,59 @@ __global__ void __launch_bounds__(256) transform_weight_kernel(const __half* __r
   }
 }
 
+// Tensor-core form of the same transform.  Per block, Bt_blk = B_blk . (R_blk^T)^T: the rotation pass of the two-pass
+// route (xr_kernel) with the weight in X's place and every b x b block of R transposed, which a small kernel
+// writes to scratch first (R is tiny beside B).  The reference does this step with batched tensor-core GEMMs
+// through cuBLAS (cublas_oft.hpp:20-43).
+__global__ void transpose_r_blocks_kernel(const __half* __restrict__ R, long long ldR, __half* __restrict__ Rt, long long ldt, int b, long long total) {
+  for (long long idx = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; idx < total;
+       idx += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const long long row = idx / ldt, col = idx % ldt;  // row = g*b + p, col = kb*b + q  <-  R[g*b + q][kb*b + p]
+    const long long g = row / b, p = row % b, kb = col / b, q = col % b;
+    Rt[idx] = R[(g * b + q) * ldR + kb * b + p];
+  }
+}
+
+template <int kB>
+int launch_xr(int m, int k, const void* A, int ldA, const void* Rg, int ldR, void* XR, long long ldX, cudaStream_t stream, DeviceState* st);
+int expand_r8(const void* R, int ldR, void* Rx, int n_groups, int k, cudaStream_t stream);
+inline long long r8_ld(int k);
+inline size_t r8_bytes(int n_groups, int k);
+
+int transform_weight_tc(int n, int k, int group_size, int b, const void* B, int ldB, const void* R, int ldR, void* Bt, int ldBt, cudaStream_t stream,
+                        DeviceState* st) {
+  const int n_groups = n / group_size;
+  const long long ldt = k;  // k is a multiple of b >= 8, so rows of the scratch stay 16-byte aligned
+  __half* rt = nullptr;
+  CUDA_TRY(cudaMallocFromPoolAsync(reinterpret_cast<void**>(&rt), static_cast<size_t>(n_groups) * b * ldt * 2, st->pool, stream));
+  const long long total = static_cast<long long>(n_groups) * b * ldt;
+  transpose_r_blocks_kernel<<<static_cast<int>(total / 256 + 1 < 2048 ? total / 256 + 1 : 2048), 256, 0, stream>>>(static_cast<const __half*>(R), ldR, rt, ldt, b, total);
+  int rc = cudaGetLastError() == cudaSuccess ? B200_OK : fail(B200_ECUDA, "launch of the block transpose failed");
+  void* rx = nullptr;
+  if (rc == B200_OK && b == 8) {  // 8 x 8 blocks: pairs of them embedded in 16 x 16 blocks, as for the product itself
+    if (cudaMallocFromPoolAsync(&rx, r8_bytes(n_groups, k), st->pool, stream) != cudaSuccess) rc = fail(B200_ECUDA, "no scratch for the expanded R");
+    if (rc == B200_OK) rc = expand_r8(rt, static_cast<int>(ldt), rx, n_groups, k, stream);
+  }
+  for (int g = 0; rc == B200_OK && g < n_groups; ++g) {
+    const __half* Bg = static_cast<const __half*>(B) + static_cast<long long>(g) * group_size * ldB;
+    __half* Btg = static_cast<__half*>(Bt) + static_cast<long long>(g) * group_size * ldBt;
+    const __half* Rg = rt + static_cast<long long>(g) * b * ldt;
+    switch (b) {
+      case 8: rc = launch_xr<16>(group_size, k, Bg, ldB, static_cast<const __half*>(rx) + static_cast<long long>(g) * 16 * r8_ld(k), static_cast<int>(r8_ld(k)), Btg, ldBt, stream, st); break;
+      case 16: rc = launch_xr<16>(group_size, k, Bg, ldB, Rg, static_cast<int>(ldt), Btg, ldBt, stream, st); break;
+      case 32: rc = launch_xr<32>(group_size, k, Bg, ldB, Rg, static_cast<int>(ldt), Btg, ldBt, stream, st); break;
+      case 64: rc = launch_xr<64>(group_size, k, Bg, ldB, Rg, static_cast<int>(ldt), Btg, ldBt, stream, st); break;
+      case 128: rc = launch_xr<128>(group_size, k, Bg, ldB, Rg, static_cast<int>(ldt), Btg, ldBt, stream, st); break;
+      default: rc = fail(B200_EUNSUPPORTED, "reconn_sz=%d", b);
+    }
+  }
+  const std::string keep = g_err;
+  if (rx) cudaFreeAsync(rx, stream);
+  cudaFreeAsync(rt, stream);
+  g_err = keep;
+  return rc;
+}
+
 int transform_weight(int n, int k, int group_size, int b, const void* B, int ldB, const void* R, int ldR, void* Bt, int ldBt, cudaStream_t stream) {
   if (n < 0 || k < 0 || b <= 0 || group_size <= 0) return fail(B200_EINVAL, "bad transform_weight sizes (n=%d k=%d group_size=%d reconn_sz=%d)", n, k, group_size, b);
   if (b > 128) return fail(B200_EUNSUPPORTED, "reconn_sz=%d: the weight transform handles block edges up to 128", b);
@@ -733,6 +786,14 @@ int transform_weight(int n, int k, int group_size, int b, const void* B, int ldB
   if (ldB < k || ldR < k || ldBt < k) return fail(B200_EINVAL, "leading dimension smaller than k=%d", k);
   if (n == 0 || k == 0) return B200_OK;
   if (!B || !R || !Bt) return fail(B200_EINVAL, "B, R or the output is null");
+  // Tensor cores when the block edge is one the rotation kernel is built for and the operands can be moved by TMA
+  // (16-byte aligned bases, leading dimensions multiples of 8 elements); else the CUDA-core kernel below.
+  const bool tma_ok = ((reinterpret_cast<uintptr_t>(B) | reinterpret_cast<uintptr_t>(Bt)) & 15) == 0 && ldB % 8 == 0 && ldBt % 8 == 0;
+  if (tma_ok && (b == 8 || b == 16 || b == 32 || b == 64 || b == 128)) {
+    DeviceState* st;
+    if (int rc = device_state(&st)) return rc;
+    if (st->pool) return transform_weight_tc(n, k, group_size, b, B, ldB, R, ldR, Bt, ldBt, stream, st);
+  }
   const int chunks = (group_size + 63) / 64, n_groups = n / group_size;
   const size_t smem = (static_cast<size_t>(b) * b + 64 * b) * sizeof(__half);
   CUDA_TRY(cudaFuncSetAttribute(transform_weight_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
@@ -1185,6 +1246,34 @@ int b200_shard_range(int n, int group_size, int world, int rank, int* n_begin, i
   *n_begin = static_cast<int>(b0);
   *n_end = static_cast<int>(b1);
   return B200_OK;
+}
+
+int b200_oft_tn_f16_sharded(int m, int n, int k, int group_size, int reconn_sz, int world, const int* devices, const void* const* A, int ldA,
+                            const void* const* B_slab, int ldB, const void* const* R_slab, int ldR, void* const* C_slab, int ldC,
+                            void* const* streams) {
+  g_err.clear();
+  if (world <= 0 || !devices || !A || !B_slab || !R_slab || !C_slab) return fail(B200_EINVAL, "bad sharded arguments (world=%d)", world);
+  if (group_size <= 0 || n < 0 || n % group_size != 0) return fail(B200_EINVAL, "n=%d is not a multiple of group_size=%d", n, group_size);
+  int cur = 0;
+  CUDA_TRY(cudaGetDevice(&cur));
+  int rc = B200_OK;
+  for (int r = 0; rc == B200_OK && r < world; ++r) {
+    int n0 = 0, n1 = 0;
+    rc = b200_shard_range(n, group_size, world, r, &n0, &n1);
+    if (rc != B200_OK || n1 <= n0) continue;
+    const int n_loc = n1 - n0;
+    const int gs_loc = group_size >= n ? n_loc : group_size;  // one group over all of N: the slab is one group of its own width
+    if (cudaError_t e = cudaSetDevice(devices[r])) {
+      rc = fail(B200_ECUDA, "cudaSetDevice(%d): %s", devices[r], cudaGetErrorString(e));
+      break;
+    }
+    rc = oft_dispatch(m, n_loc, k, gs_loc, reconn_sz, A[r], ldA, B_slab[r], ldB, R_slab[r], ldR, C_slab[r], ldC,
+                      static_cast<cudaStream_t>(streams ? streams[r] : nullptr));
+  }
+  const std::string keep = g_err;
+  cudaSetDevice(cur);
+  g_err = keep;
+  return rc;
 }
 
 int b200_tile_coord(unsigned tiles_m, unsigned tiles_n, unsigned idx, unsigned* tile_m, unsigned* tile_n) {

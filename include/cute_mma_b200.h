@@ -174,6 +174,19 @@ int b200_peer_copy_async(void* dst, int dst_device, const void* src, int src_dev
  * tiles).  Pure host arithmetic, no CUDA call. */
 int b200_shard_range(int n, int group_size, int world, int rank, int* n_begin, int* n_end);
 
+/* The N-sharded product on `world` GPUs of this process, one call: for r = 0 .. world-1 the slab of
+ * b200_shard_range(n, group_size, world, r) is launched on device devices[r] (asynchronously, on streams[r] or
+ * that device's default stream when streams is NULL) through b200_oft_tn_f16, and the calling thread's current
+ * device is restored.  Per device r the caller supplies, in that device's memory: A[r] = all of X (replicated),
+ * B_slab[r] = rows [n0, n1) of the stored B, R_slab[r] = the stored R rows of the slab's groups (all of R when
+ * group_size == n), C_slab[r] = where column n0 of C goes (a private [m][n1-n0] buffer with ldC = n1 - n0, or
+ * column n0 of a full C with ldC = n).  No collective and no peer access are involved: the product shards with no
+ * exchange; gathering C is left to the caller (NCCL, or b200_peer_copy_async).  The same device may appear more
+ * than once (its slabs then run one after the other).  The reference is single-GPU (cute_oft_pc.cu:257-264). */
+int b200_oft_tn_f16_sharded(int m, int n, int k, int group_size, int reconn_sz, int world, const int* devices,
+                            const void* const* A, int ldA, const void* const* B_slab, int ldB,
+                            const void* const* R_slab, int ldR, void* const* C_slab, int ldC, void* const* streams);
+
 /* Tile visiting order of the persistent kernels; same order as z_curve(grid, idx) (z_curve.hpp:28-49). */
 int b200_tile_coord(unsigned tiles_m, unsigned tiles_n, unsigned idx, unsigned* tile_m, unsigned* tile_n);
 

@@ -512,3 +512,71 @@ def test_a_rw_order_matches_oracle(lib, cuda, m, n, k, b, gs):
     # against exact arithmetic on the fp16-rounded transformed weight (this order's only intermediate rounding)
     exact = A.astype(np.float64) @ want.astype(np.float16).astype(np.float64).T
     assert truth_ok(out[:m], exact)[0] == 0
+
+
+def test_route_choice_either_side_of_the_crossover(lib, cuda, pair_build):
+    """b200_oft_plan on shapes either side of the measured crossover between the kernel that keeps X.R in tensor
+    memory (few N tiles per group) and the kernel that shares one X.R per row block (8 tiles or more; 4 for 128 x 128
+    blocks), and the option that overrides the choice."""
+    if not pair_build:
+        pytest.skip("the single-CTA build has one route")
+    plan = lambda n, b, gs=None: ops.oft_plan(16384, n, 4096, group_size=gs, reconn_sz=b, lib=lib)["path"]
+    assert plan(1792, 64) == "fused_tmem" and plan(2048, 64) == "fused_ring"
+    assert plan(768, 128) == "fused_tmem" and plan(1024, 128) == "fused_ring"
+    assert plan(4096, 8) == "fused_ring" and plan(1024, 16) == "fused_tmem"
+    assert plan(8192, 64, 256) == "fused_tmem" and plan(8192, 64, 2048) == "fused_ring"   # the group's width counts, not N
+    assert ops.oft_plan(16384, 8192, 4096, group_size=2048, reconn_sz=64, lib=lib)["kernel_launches"] == 4  # one launch per group
+    with ops.option("oft_route", 2, lib):
+        assert plan(4096, 64) == "two_pass"
+    with ops.option("oft_route", 1, lib):
+        assert plan(4096, 64) == "fused_tmem"
+    assert plan(4096, 64) == "fused_ring"
+    with pytest.raises(ops.Error):
+        ops.set_option("no_such_option", 1, lib)
+
+
+@pytest.mark.parametrize("n,gs,b,world", [(1024, None, 32, 2), (2560, None, 64, 3), (1024, 256, 16, 2), (512, None, 64, 1)])
+def test_sharded_entry_point_slabs_on_one_device(lib, cuda, n, gs, b, world):
+    """b200_oft_tn_f16_sharded with every rank mapped to this GPU (its slabs then run one after the other): the
+    slabs written side by side equal the unsharded product bit for bit."""
+    import torch
+
+    m, k = 384, 256
+    A, R, B = make_oft_case(m, n, k, b, gs, seed=51)
+    whole = run_oft(lib, cuda, A, R, B, m, n, k, b, gs, route=1)
+    dA, dB, dR = (torch.from_numpy(x).to(cuda) for x in (A, B, R))
+    dC = torch.full((m, n), -7.0, dtype=torch.float16, device=cuda)
+    g_sz = n if gs is None else gs
+    Bs, Rs, Cs = [], [], []
+    for r in range(world):
+        n0, n1 = ops.shard_range(n, g_sz, world, r, lib=lib)
+        Bs.append(dB[n0:]); Cs.append(dC[:, n0:])
+        Rs.append(dR[(n0 // g_sz) * b:] if gs is not None else dR)
+    with ops.option("oft_route", 1, lib):
+        ops.oft_tn_sharded(m, n, k, [0] * world, [dA] * world, k, Bs, k, Rs, k, Cs, n, group_size=gs, reconn_sz=b, lib=lib)
+    assert ops.device_status(lib)[0] == 0
+    assert np.array_equal(dC.cpu().numpy().view(np.uint16), whole.view(np.uint16))
+
+
+def test_sharded_entry_point_on_two_devices(lib, cuda):
+    """Two GPUs of this process, one call (skipped on a single-GPU box)."""
+    import torch
+
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    m, n, k, b = 512, 4096, 512, 64
+    A, R, B = make_oft_case(m, n, k, b, seed=52, xdist="normal", wsigma=0.02)
+    whole = run_oft(lib, cuda, A, R, B, m, n, k, b)
+    parts = []
+    As, Bs, Rs, Cs = [], [], [], []
+    for r in range(2):
+        dev = torch.device("cuda", r)
+        n0, n1 = ops.shard_range(n, n, 2, r, lib=lib)
+        As.append(torch.from_numpy(A).to(dev)); Bs.append(torch.from_numpy(B[n0:n1]).to(dev)); Rs.append(torch.from_numpy(R).to(dev))
+        Cs.append(torch.empty((m, n1 - n0), dtype=torch.float16, device=dev))
+    ops.oft_tn_sharded(m, n, k, [0, 1], As, k, Bs, k, Rs, k, Cs, n // 2, reconn_sz=b, lib=lib)
+    for r in range(2):
+        torch.cuda.synchronize(r)
+    got = np.concatenate([c.cpu().numpy() for c in Cs], axis=1)
+    torch.cuda.set_device(0)
+    assert np.array_equal(got.view(np.uint16), whole.view(np.uint16))
