@@ -46,6 +46,12 @@ NOMINAL_FP16_TFLOPS = 2250.0  # vendor dense fp16 figure, context only
 # (dram__bytes_read.sum + dram__bytes_write.sum), keyed by workload and by the route the library takes;
 # None until a capture exists.
 NCU_TRAFFIC_BYTES = {
+    # Shared-X.R kernel (oft3_kernel).  Large workload: captured at M 16384 (one kernel, two launches: read 5.79 GB +
+    # write 1.26 GB against 1.68 GB algorithmic) and scaled by 4 to M 65536 -- W is re-streamed once per band of 8 row
+    # blocks, X and Y once, so traffic grows in proportion to M.  Projection shape: captured whole (584.5 + 295.3 MB
+    # against 303 MB algorithmic; the extra is X.R leaving L2 once and W read again by later bands).
+    ("oft_large_m65536_k8192_n28672_b128", "fused_ring"): 28.2e9,
+    ("oft_proj_m16384_k4096_n4096_b64", "fused_ring"): 879.8e6,
     # two-pass route, GEMM pass (gemm2_kernel): read 17.86 GB + write 3.72 GB against 5.3 GB algorithmic; the
     # rotation pass before it moves 1.08 + 1.03 GB, its algorithmic bytes
     ("oft_large_m65536_k8192_n28672_b128", "two_pass"): 21.58e9,
