@@ -498,7 +498,8 @@ def run_gpu_arm(args, workload):
                     "peak_source": f"{peaks['source']} bf16 {'sustained' if timed_s >= 2.0 else 'burst'} (cuBLAS matmul on this pool)",
                     "traffic": (NCU_TRAFFIC_BYTES.get((workload, plan["path"])) if world == 1 else None),
                     "frac_of_nominal_fp16": achieved / NOMINAL_FP16_TFLOPS, "route": plan["path"], "kernel": kernel_of[plan["path"]],
-                    "launch_ms": ms, "kernel_config": ops.kernel_info(lib)["oft"], "n_per_gpu": n_loc, "routes": routes}
+                    "launch_ms": ms, "kernel_config": ops.kernel_info(lib)["oft_ring" if plan["path"] == "fused_ring" else "oft"], "n_per_gpu": n_loc,
+                    "routes": routes}
         line = {
             "metric": METRIC, "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps, "warmup": warm,
             "ms_per_step": ms, "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f16",

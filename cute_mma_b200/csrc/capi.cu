@@ -1375,20 +1375,25 @@ int b200_wait_profile(unsigned long long* out, int n) {
 }
 
 const char* b200_kernel_info(void) {
-  static char buf[768];
+  static char buf[1024];
   using PH = Params<half, half, MMA_T, MMA_N>;
   using PF = Params<float, float, MMA_N, MMA_T>;
   using O64 = OftT<64, 1>;
   using O128 = OftT<128, 1>;
+  using R64 = Oft3Traits<64, 2, 5>;
+  using R128 = Oft3Traits<128, 2, 5>;
   snprintf(buf, sizeof buf,
            "{\"arch\": \"sm_100a\", \"gemm_half_tn\": {\"bM\": %d, \"bN\": %d, \"bK\": %d, \"bP\": %d}, "
            "\"gemm_float_nt\": {\"bM\": %d, \"bN\": %d, \"bK\": %d, \"bP\": %d}, "
            "\"oft\": {\"ctas\": %d, \"bM\": %d, \"bN\": %d, \"bK\": %d, \"bP1\": %d, \"bP2\": %d, \"threads\": %d, "
            "\"b64\": {\"smem\": %d, \"tmem_cols\": %d, \"xr_bufs\": %d}, "
-           "\"b128\": {\"smem\": %d, \"tmem_cols\": %d, \"xr_bufs\": %d}}}",
+           "\"b128\": {\"smem\": %d, \"tmem_cols\": %d, \"xr_bufs\": %d}}, "
+           "\"oft_ring\": {\"ctas\": 2, \"bM\": 128, \"bN\": 256, \"bK\": 64, \"stages_x_r\": %d, \"stages_xr_w\": %d, \"threads\": %d, "
+           "\"accumulators\": 1, \"b64\": {\"smem\": %d, \"rotation_bufs\": %d}, \"b128\": {\"smem\": %d, \"rotation_bufs\": %d}}}",
            PH::bM, PH::bN, PH::bK, PH::bP, PF::bM, PF::bN, PF::bK, PF::bP, kOftPair ? 2 : 1, (int)CurrCompParams::bM, (int)CurrCompParams::bN,
            (int)CurrCompParams::bK, (int)CurrCompParams::bP1, (int)CurrCompParams::bP2, O64::kThreads, O64::kSmemBytes,
-           O64::kTmemUsed, O64::kXrBufs, O128::kSmemBytes, O128::kTmemUsed, O128::kXrBufs);
+           O64::kTmemUsed, O64::kXrBufs, O128::kSmemBytes, O128::kTmemUsed, O128::kXrBufs, R64::kS1, R64::kS2, R64::kThreads, R64::kSmemBytes,
+           R64::kXrBufs, R128::kSmemBytes, R128::kXrBufs);
   return buf;
 }
 
