@@ -36,7 +36,13 @@ enum {
  * (the reference's bN % group_size == 0 case, cute_oft_coop_pc.cu:383).  reconn_sz = 8 (the reference's
  * default) first expands R into pairs of 8 x 8 blocks embedded in zero-padded 16 x 16 blocks (device
  * scratch of twice the size of R, stream-ordered on `stream` from a memory pool the library keeps until
- * b200_shutdown) and then runs as 16. */
+ * b200_shutdown) and then runs as 16.
+ * The product is fused in one of two ways (b200_oft_plan tells which, the option "oft_route" overrides): a group of
+ * fewer than 8 N tiles of 256 columns (4 for reconn_sz = 128) keeps X.R in tensor memory and forms it per N tile, as
+ * the reference's kernel forms it per thread block (cute_oft_coop_pc.cu:19-186); a wider group forms one X.R per block
+ * of 256 rows and shares it among all its N tiles through a ring of row blocks in device scratch that is sized to
+ * stay in L2 (32 to 64 MB and a few counters per call in flight, from the same pool, one launch per N-group).  Both
+ * give the same numbers; the second also the same bits as b200_oft_tn_f16_two_pass. */
 int b200_oft_tn_f16(int m, int n, int k, int group_size, int reconn_sz,
                     const void* A, int ldA, const void* B, int ldB, const void* R, int ldR,
                     void* C, int ldC, void* stream);

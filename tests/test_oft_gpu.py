@@ -580,3 +580,31 @@ def test_sharded_entry_point_on_two_devices(lib, cuda):
     got = np.concatenate([c.cpu().numpy() for c in Cs], axis=1)
     torch.cuda.set_device(0)
     assert np.array_equal(got.view(np.uint16), whole.view(np.uint16))
+
+
+def test_oft_ring_route_on_two_streams(lib, cuda, pair_build):
+    """Two launches of the shared-X.R kernel queued on two streams with no synchronisation between them, repeatedly:
+    each has its own ring and counters (stream-ordered from the library's pool) and is launched cooperatively, so
+    both finish, no wait runs out, and both return the bits of a launch that ran alone."""
+    import torch
+
+    if not pair_build:
+        pytest.skip("the shared-X.R kernel exists in the CTA-pair build only")
+    m, n, k, b = 4608, 2304, 512, 64   # 18 row blocks (more than the ring of 16 holds) x 9 N tiles
+    g = torch.Generator(device=cuda).manual_seed(78)
+    dA = torch.randn((m, k), generator=g, device=cuda).to(torch.float16)
+    dB = (torch.randn((n, k), generator=g, device=cuda) * 0.05).to(torch.float16)
+    from cute_mma_b200 import inputs
+    dR = torch.from_numpy(inputs.pack_r(inputs.blocks_qr(1, k // b, b, 78))).to(cuda)
+    alone = torch.empty((m, n), dtype=torch.float16, device=cuda)
+    with ops.option("oft_route", 3, lib), ops.option("raster", 4, lib), ops.option("ring_bands", 2, lib):
+        ops.oft_tn(m, n, k, dA, k, dB, k, dR, k, alone, n, reconn_sz=b, lib=lib)
+        torch.cuda.synchronize()
+        s1, s2 = torch.cuda.Stream(), torch.cuda.Stream()
+        c1, c2 = torch.empty_like(alone), torch.empty_like(alone)
+        for _ in range(4):
+            ops.oft_tn(m, n, k, dA, k, dB, k, dR, k, c1, n, s1.cuda_stream, reconn_sz=b, lib=lib)
+            ops.oft_tn(m, n, k, dA, k, dB, k, dR, k, c2, n, s2.cuda_stream, reconn_sz=b, lib=lib)
+        torch.cuda.synchronize()
+    assert ops.device_status(lib)[0] == 0
+    assert torch.equal(c1, alone) and torch.equal(c2, alone)
