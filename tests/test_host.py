@@ -28,6 +28,10 @@ def test_kernel_info_matches_config_headers(lib):
         assert info["oft"][key] == want
     assert info["oft"]["b64"]["tmem_cols"] <= 512 and info["oft"]["b128"]["tmem_cols"] <= 512
     assert info["oft"]["b128"]["smem"] <= 232448
+    ring = info["oft_ring"]   # the shared-X.R kernel: 5 stages of 32 KB, 2 of {X, R}, 16 KB staging, barriers, alignment slack
+    for b, r_half in ((64, 4096), (128, 8192)):
+        assert ring[f"b{b}"]["smem"] == 5 * 32768 + 2 * (16384 + r_half) + 16384 + (2 * 2 + 2 * 5 + 2 * ring[f"b{b}"]["rotation_bufs"] + 2) * 8 + 64 + 1024
+        assert ring[f"b{b}"]["smem"] <= 232448 and 256 + ring[f"b{b}"]["rotation_bufs"] * max(b, 64) <= 512
 
 
 def test_argument_validation_without_a_gpu(lib):
@@ -50,6 +54,57 @@ def test_argument_validation_without_a_gpu(lib):
     with pytest.raises(ops.Error) as e:
         ops.gemm("T", "T", 8, 8, 8, p, 8, p, 8, p, 8, lib=lib)
     assert e.value.code == ops.EUNSUPPORTED and "('T','N')" in e.value.message
+
+
+def test_new_entry_points_validate_before_any_cuda_call(lib):
+    """b200_gemm_ex, b200_oft_tn_f16_sharded and the option calls reject bad arguments by status code without a GPU."""
+    buf = (ctypes.c_uint16 * 64)()
+    p = ctypes.addressof(buf)
+    assert lib.b200_gemm_ex(b"N", b"N", 0, 0, 8, 8, 8, 1.0, p, 8, p, 8, 0.0, p, 8, None) == ops.EUNSUPPORTED   # only TN and NT exist
+    assert lib.b200_gemm_ex(b"T", b"N", 2, 0, 8, 8, 8, 1.0, p, 8, p, 8, 0.0, p, 8, None) == ops.EUNSUPPORTED   # float operands, half result
+    assert b"f16 -> f32" in lib.b200_last_error()
+    assert lib.b200_gemm_ex(b"T", b"N", 0, 1, -1, 8, 8, 1.0, p, 8, p, 8, 0.0, p, 8, None) == ops.EINVAL
+    devs = (ctypes.c_int * 1)(0)
+    ptrs = (ctypes.c_void_p * 1)(p)
+    assert lib.b200_oft_tn_f16_sharded(8, 16, 16, 16, 16, 0, devs, ptrs, 16, ptrs, 16, ptrs, 16, ptrs, 16, None) == ops.EINVAL  # world = 0
+    assert lib.b200_oft_tn_f16_sharded(8, 16, 16, 5, 16, 1, devs, ptrs, 16, ptrs, 16, ptrs, 16, ptrs, 16, None) == ops.EINVAL  # n % group_size
+    assert lib.b200_oft_tn_f16_sharded(8, 16, 16, 16, 16, 1, devs, None, 16, ptrs, 16, ptrs, 16, ptrs, 16, None) == ops.EINVAL
+    with pytest.raises(ops.Error):
+        ops.set_option("no_such_option", 1, lib)
+    for name in ("oft_route", "raster", "tile_sync", "l2_hints", "gemm_tile_sync", "gemm_l2_hints", "gemm_split", "maps_3d", "ring_bands", "prefetch"):
+        old = ops.get_option(name, lib)
+        with ops.option(name, 3, lib):
+            assert ops.get_option(name, lib) == 3
+        assert ops.get_option(name, lib) == old
+
+
+def test_rotation_shares_cover_every_unit_once():
+    """The split of the rotation units among the SM pairs of the shared-X.R kernel (a contiguous share of every band per
+    pair, bands in tile order), restated here: every (row block, unit) exactly once, shares differ by at most one
+    unit per band, and a pair's units come in non-decreasing row-block order."""
+    def shares(raster, tiles_m, upb, pairs):
+        out = []
+        for p in range(pairs):
+            mine = []
+            band = 0
+            while band * raster < tiles_m:
+                rows = min(raster, tiles_m - band * raster)
+                u = rows * upb
+                for j in range(p * u // pairs, (p + 1) * u // pairs):
+                    mine.append((band * raster + j // upb, j % upb))
+                band += 1
+            out.append(mine)
+        return out
+
+    for raster, tiles_m, upb, pairs in ((4, 64, 64, 74), (8, 256, 64, 74), (8, 3, 5, 74), (2, 41, 5, 74), (4, 18, 8, 37), (1, 7, 129, 74)):
+        sh = shares(raster, tiles_m, upb, pairs)
+        flat = [u for mine in sh for u in mine]
+        assert sorted(flat) == [(tm, ku) for tm in range(tiles_m) for ku in range(upb)]
+        for mine in sh:
+            assert [tm for tm, _ in mine] == sorted(tm for tm, _ in mine)
+        full = tiles_m // raster
+        counts = [len(m_) for m_ in sh]
+        assert max(counts) - min(counts) <= full + (1 if tiles_m % raster else 0)
 
 
 def test_missing_library_fails_loudly(tmp_path):
