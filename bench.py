@@ -445,6 +445,17 @@ def run_gpu_arm(args, workload):
         for _ in range(5):
             ag(dX, dW, dR)
         overlapped_ms = max_over_ranks((time.perf_counter() - t0) / 5 * 1e3)
+        del ag, y_all
+        # ... and with the exchange done by the kernel's own epilogue (plain stores into the peers' buffers)
+        ag = sharded.SlabProductAllGather(m, n, k, n0, n1, reconn_sz=b, world=world, rank=rank, device=dev, lib=lib, mode="stores")
+        for _ in range(2):
+            y_all = ag(dX, dW, dR)
+        stores_ok = bool(torch.equal(y_all.view(world * m, n_loc), out.view(world * m, n_loc)))
+        barrier()
+        t0 = time.perf_counter()
+        for _ in range(5):
+            ag(dX, dW, dR)
+        stores_ms = max_over_ranks((time.perf_counter() - t0) / 5 * 1e3)
         del out, ag, y_all
 
     # end to end from pinned host buffers, H2D + product + D2H inside the timed region.  One GPU: the C ABI's
@@ -516,6 +527,8 @@ def run_gpu_arm(args, workload):
             line["product_with_overlapped_allgather"] = {"ms_per_step": overlapped_ms, "sequential_ms": ms + allgather_ms,
                                                          "matches_nccl_allgather": overlapped_ok,
                                                          "api": "sharded.SlabProductAllGather (row chunks pushed into the peers' symmetric-memory buffers by copy engines)"}
+            line["product_with_epilogue_allgather"] = {"ms_per_step": stores_ms, "matches_nccl_allgather": stores_ok,
+                                                       "api": "b200_oft_tn_f16_gather (the kernel's epilogue stores every tile into all GPUs' buffers)"}
         if world == 1 and workload == DEFAULT_WORKLOAD:
             del hX, hW, hY
             roofline["projection_shape"] = projection_shape_rates(lib, dev, stream, peaks)

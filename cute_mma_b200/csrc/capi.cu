@@ -554,9 +554,19 @@ int oft_two_pass(int m, int n, int k, int group_size, const void* A, int ldA, co
 // ever launched cooperatively (all CTAs resident); kNoRing tells the caller to take another route.
 constexpr int kNoRing = -1001;
 
+// Further destinations of the result, set by b200_oft_tn_f16_gather for its own call: the shared-X.R kernel stores
+// every tile to each of them from its epilogue (plain stores; the buffers may be another GPU's memory mapped into
+// this process).  `stored` tells the entry point whether a launch took them; otherwise it copies.
+struct MoreDst {
+  int n = 0;
+  __half* p[7] = {nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr};
+  bool stored = false;
+};
+thread_local MoreDst g_more;
+
 template <int kB>
 int launch_oft3(int m, int n, int k, const void* A, int ldA, const void* B, int ldB, const void* Rg, int ldR, void* C, int ldC,
-                cudaStream_t stream, DeviceState* st) {
+                cudaStream_t stream, DeviceState* st, long long more_offset) {
   using T = Oft3Traits<kB, 2, 5>;
   if (!st->pool) return kNoRing;
   const int tiles_m = (m + 2 * T::kBM - 1) / (2 * T::kBM), tiles_n = (n + T::kBN - 1) / T::kBN;
@@ -619,7 +629,8 @@ int launch_oft3(int m, int n, int k, const void* A, int ldA, const void* B, int 
   // 1.2 GB of DRAM reads and 5 % of time at the shape above, so it stays off unless the option asks for it)
   const int prefetch_w = opt(kOptPrefetch) >= 0 ? opt(kOptPrefetch) : 0;
   Oft3Args args{m, n, k, static_cast<__half*>(C), ldC, st->status, raster, big ? kL2EvictFirst : kL2EvictNormal, hint_a, hint_b,
-                tile_sync, counters + 3 * tiles_m, prefetch_w, slots, counters, counters + 2 * tiles_m};
+                tile_sync, counters + 3 * tiles_m, prefetch_w, slots, counters, counters + 2 * tiles_m, g_more.n, {}};
+  for (int d = 0; d < g_more.n; ++d) args.C_more[d] = g_more.p[d] + more_offset;
   auto kernel = oft3_kernel<T>;
   if (int rc = opt_in_smem(kernel, T::kSmemBytes)) return finish(rc);
   const long long tiles = static_cast<long long>(tiles_m) * tiles_n;
@@ -638,7 +649,8 @@ int oft_ring(int m, int n, int k, int group_size, const void* A, int ldA, const 
   for (int g = 0; rc == B200_OK && g < n / group_size; ++g)  // stream order serialises the groups
     rc = launch_oft3<kB>(m, group_size, k, A, ldA, static_cast<const __half*>(B) + static_cast<long long>(g) * group_size * ldB, ldB,
                          static_cast<const __half*>(R) + static_cast<long long>(g) * kB * ldR, ldR,
-                         static_cast<__half*>(C) + static_cast<long long>(g) * group_size, ldC, stream, st);
+                         static_cast<__half*>(C) + static_cast<long long>(g) * group_size, ldC, stream, st, static_cast<long long>(g) * group_size);
+  if (rc == B200_OK) g_more.stored = true;
   return rc;
 }
 
@@ -1274,6 +1286,27 @@ int b200_oft_tn_f16_sharded(int m, int n, int k, int group_size, int reconn_sz, 
   cudaSetDevice(cur);
   g_err = keep;
   return rc;
+}
+
+int b200_oft_tn_f16_gather(int m, int n, int k, int group_size, int reconn_sz, const void* A, int ldA, const void* B, int ldB,
+                           const void* R, int ldR, int n_dst, void* const* C_dst, int ldC, void* stream_v) {
+  g_err.clear();
+  if (n_dst < 1 || n_dst > 8 || !C_dst) return fail(B200_EINVAL, "n_dst=%d: between 1 and 8 destinations", n_dst);
+  for (int d = 0; d < n_dst; ++d)
+    if (!C_dst[d] && m > 0 && n > 0) return fail(B200_EINVAL, "destination %d is null", d);
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
+  g_more = MoreDst{};
+  g_more.n = n_dst - 1;
+  for (int d = 1; d < n_dst; ++d) g_more.p[d - 1] = static_cast<__half*>(C_dst[d]);
+  int rc = oft_dispatch(m, n, k, group_size, reconn_sz, A, ldA, B, ldB, R, ldR, C_dst[0], ldC, stream);
+  const bool stored = g_more.stored;
+  g_more = MoreDst{};
+  if (rc != B200_OK || stored || m == 0 || n == 0) return rc;
+  // a route without the multi-destination epilogue (few N tiles per group, k = 0, no scratch): copy the result
+  for (int d = 1; d < n_dst; ++d)
+    CUDA_TRY(cudaMemcpy2DAsync(C_dst[d], static_cast<size_t>(ldC) * 2, C_dst[0], static_cast<size_t>(ldC) * 2, static_cast<size_t>(n) * 2, m,
+                               cudaMemcpyDeviceToDevice, stream));
+  return B200_OK;
 }
 
 int b200_tile_coord(unsigned tiles_m, unsigned tiles_n, unsigned idx, unsigned* tile_m, unsigned* tile_n) {

@@ -71,6 +71,8 @@ struct Oft3Args {
   int slots;                       // row blocks the X.R ring holds (all of them, or 2 * raster)
   int* ready;                      // [2 * row blocks] zeroed
   int* done;                       // [row blocks] zeroed
+  int n_more;                      // the result is also stored to this many further buffers of the same shape and ldC,
+  __half* C_more[7];               // e.g. this rank's columns of Y on every other GPU of the node (plain stores over NVLink)
 };
 
 // A pair's rotation units: band after band (the order the tiles consume them), and inside each band a
@@ -436,7 +438,6 @@ oft3_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ 
       tc_fence_after();
       if (threadIdx.x == 256 && tcount < kSkewTiles - 2) skew_stamp(ctx, tcount);  // profiling build: end of each tile's MMAs
       const int row = tm * 2 * T::kBM + rank * T::kBM + quad * 32 + lane;
-      __half* c_row = args.C + static_cast<long long>(row) * args.ldC;
       uint32_t p[T::kBN / 2];
 #pragma unroll
       for (int c = 0; c < T::kBN / 32; c += 2) {  // two loads in flight per wait
@@ -455,21 +456,25 @@ oft3_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ 
       tc_fence_before();
       mbar_arrive_cluster(mapa_shared(acc_empty, 0));
       if (row < args.m) {
+        for (int d = 0; d <= args.n_more; ++d) {  // the caller's C, then every further destination
+          __half* out_row = (d == 0 ? args.C : args.C_more[d - 1]) + static_cast<long long>(row) * args.ldC;
+          const bool vec = vec_ok && (d == 0 || (reinterpret_cast<uintptr_t>(args.C_more[d - 1]) & 15) == 0);
 #pragma unroll
-        for (int c = 0; c < T::kBN / 32; ++c) {
-          const int col0 = tn * T::kBN + c * 32;
-          if (vec_ok && col0 + 32 <= args.n) {
-            uint4* dst = reinterpret_cast<uint4*>(c_row + col0);
+          for (int c = 0; c < T::kBN / 32; ++c) {
+            const int col0 = tn * T::kBN + c * 32;
+            if (vec && col0 + 32 <= args.n) {
+              uint4* dst = reinterpret_cast<uint4*>(out_row + col0);
 #pragma unroll
-            for (int q = 0; q < 4; ++q)
-              dst[q] = make_uint4(p[c * 16 + 4 * q], p[c * 16 + 4 * q + 1], p[c * 16 + 4 * q + 2], p[c * 16 + 4 * q + 3]);
-          } else {
+              for (int q = 0; q < 4; ++q)
+                dst[q] = make_uint4(p[c * 16 + 4 * q], p[c * 16 + 4 * q + 1], p[c * 16 + 4 * q + 2], p[c * 16 + 4 * q + 3]);
+            } else {
 #pragma unroll
-            for (int j = 0; j < 32; ++j)
-              if (col0 + j < args.n) {
-                const uint32_t w = p[c * 16 + j / 2];
-                c_row[col0 + j] = __ushort_as_half(static_cast<unsigned short>((j & 1) ? (w >> 16) : (w & 0xFFFFu)));
-              }
+              for (int j = 0; j < 32; ++j)
+                if (col0 + j < args.n) {
+                  const uint32_t w = p[c * 16 + j / 2];
+                  out_row[col0 + j] = __ushort_as_half(static_cast<unsigned short>((j & 1) ? (w >> 16) : (w & 0xFFFFu)));
+                }
+            }
           }
         }
       }

@@ -25,7 +25,7 @@ OK, EINVAL, EUNSUPPORTED, ECUDA, EDEVICE = 0, 1, 2, 3, 4
 SYMBOLS = (
     "b200_oft_tn_f16", "b200_oft_tn_f16_two_pass", "b200_rotate_f16", "b200_oft_plan", "b200_oft_tn_f16_host", "b200_oft_tn_f16_static", "b200_transform_weight_f16", "b200_oft_tn_f16_a_rw", "b200_gemm_tn_f16", "b200_gemm_nt_f16", "b200_gemm_tn_tf32",
     "b200_gemm_nt_tf32", "b200_gemm", "b200_gemm_tn_f16_acc2", "b200_lora_tn_f16", "b200_gemm_rowmajor", "b200_peer_copy_async", "b200_shard_range", "b200_tile_coord", "b200_device_status", "b200_selftest_wait_timeout", "b200_wait_profile", "b200_kernel_info",
-    "b200_last_error", "b200_shutdown", "b200_static_status", "b200_set_option", "b200_get_option", "b200_gemm_ex", "b200_oft_tn_f16_sharded",
+    "b200_last_error", "b200_shutdown", "b200_static_status", "b200_set_option", "b200_get_option", "b200_gemm_ex", "b200_oft_tn_f16_sharded", "b200_oft_tn_f16_gather",
 )
 
 
@@ -66,6 +66,7 @@ def load_library(path: str | None = None):
     lib.b200_gemm.argtypes = [c, c, i, i, i, i, vp, i, vp, i, vp, i, vp]
     pp = ctypes.POINTER(ctypes.c_void_p)
     lib.b200_oft_tn_f16_sharded.argtypes = [i, i, i, i, i, i, ctypes.POINTER(i), pp, i, pp, i, pp, i, pp, i, pp]
+    lib.b200_oft_tn_f16_gather.argtypes = [i, i, i, i, i, vp, i, vp, i, vp, i, i, pp, i, vp]
     lib.b200_gemm_ex.argtypes = [c, c, i, i, i, i, i, ctypes.c_float, vp, i, vp, i, ctypes.c_float, vp, i, vp]
     lib.b200_gemm_tn_f16_acc2.argtypes = [i, i, i, vp, i, vp, i, i, vp, i, vp, i, vp, i, vp]
     lib.b200_lora_tn_f16.argtypes = [i, i, i, i, vp, i, vp, i, vp, i, vp, i, vp, i, vp]
@@ -204,6 +205,16 @@ def oft_tn_sharded(m, n, k, devices, A, ldA, B_slabs, ldB, R_slabs, ldR, C_slabs
     gs = n if group_size is None else group_size
     _check(lib, lib.b200_oft_tn_f16_sharded(m, n, k, gs, reconn_sz, w, (ctypes.c_int * w)(*devices), arr(A), ldA, arr(B_slabs), ldB,
                                             arr(R_slabs), ldR, arr(C_slabs), ldC, st))
+
+
+def oft_tn_gather(m, n, k, A, ldA, B, ldB, R, ldR, C_dsts, ldC, stream=None, *, group_size=None, reconn_sz=8, lib=None) -> None:
+    """oft_tn whose result goes to every buffer of ``C_dsts`` (same ldC), e.g. this rank's columns of Y on every GPU of
+    the node (see b200_oft_tn_f16_gather)."""
+    lib = lib or load_library()
+    w = len(C_dsts)
+    gs = n if group_size is None else group_size
+    _check(lib, lib.b200_oft_tn_f16_gather(m, n, k, gs, reconn_sz, _ptr(A), ldA, _ptr(B), ldB, _ptr(R), ldR, w,
+                                           (ctypes.c_void_p * w)(*[_ptr(x) for x in C_dsts]), ldC, _stream(stream)))
 
 
 def transform_weight(n, k, B, ldB, R, ldR, Bt, ldBt, stream=None, *, group_size=None, reconn_sz=8, lib=None) -> None:

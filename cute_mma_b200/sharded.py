@@ -217,18 +217,24 @@ class SlabProductAllGather:
     """The rank's slab product with the all-gather of Y overlapped: when the call returns, every rank holds
     all of Y, rank-major [world][m][n_loc] (the layout of all_gather_c).
 
-    The product runs in row chunks on the compute stream; as soon as a chunk of the rank's slab is written, copy
+    mode "copy_engines" (default): the product runs in row chunks on the compute stream; as soon as a chunk of the rank's slab is written, copy
     streams push it into the same place of every peer's buffer over NVLink (contiguous device-to-device copies,
     i.e. copy engines, no SMs and no kernel that waits for another GPU).  The peers' buffers are symmetric memory
     (torch.distributed._symmetric_memory), mapped once at construction.  A host barrier at the end of the call tells a rank that
     its peers' chunks have landed.  At 8 GPUs the exchange (7/8 of Y leaving every GPU) takes longer than the
-    product, so the step costs about the exchange instead of product + exchange."""
+    product, so the step costs about the exchange instead of product + exchange.
+    mode "stores": one launch whose epilogue writes every tile straight into all GPUs' buffers (the direct peer-store
+    epilogue); simpler, but the 16-byte stores of one row per lane use NVLink poorly and the SMs wait for them."""
 
-    def __init__(self, m, n_total, k, n0, n1, *, reconn_sz=8, world=None, rank=None, device=None, lib=None, chunks=4, copy_streams=3):
+    def __init__(self, m, n_total, k, n0, n1, *, reconn_sz=8, world=None, rank=None, device=None, lib=None, chunks=4, copy_streams=3,
+                 mode="copy_engines"):
         import torch
         import torch.distributed as dist
 
         self.torch, self.dist = torch, dist
+        if mode not in ("copy_engines", "stores"):
+            raise ValueError("mode is 'copy_engines' or 'stores'")
+        self.mode = mode
         self.world = world if world is not None else dist.get_world_size()
         self.rank = rank if rank is not None else dist.get_rank()
         self.m, self.k, self.n_loc, self.b, self.lib = m, k, n1 - n0, reconn_sz, lib
@@ -252,6 +258,16 @@ class SlabProductAllGather:
         torch, dist = self.torch, self.dist
         main = torch.cuda.current_stream(self.device)
         mine = self.y_all[self.rank]
+        if self.mode == "stores":
+            # One launch: the kernel's epilogue stores every tile into this rank's place of every GPU's buffer (plain
+            # global stores over NVLink into the peers' symmetric memory; ops.oft_tn_gather).
+            dsts = [mine] + [self.peer_views[(self.rank + p) % self.world][self.rank] for p in range(1, self.world)]
+            ops.oft_tn_gather(self.m, self.n_loc, self.k, dX, self.k, dW_slab, self.k, dR, self.k, dsts, self.n_loc, main.cuda_stream,
+                              group_size=self.n_loc, reconn_sz=self.b, lib=self.lib)
+            main.synchronize()
+            if self.world > 1:
+                dist.barrier()  # every peer's stores into this rank's buffer are complete
+            return self.y_all
         for s in self.copy_streams:
             s.wait_stream(main)
         i = 0

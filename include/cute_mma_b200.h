@@ -193,6 +193,17 @@ int b200_oft_tn_f16_sharded(int m, int n, int k, int group_size, int reconn_sz, 
                             const void* const* A, int ldA, const void* const* B_slab, int ldB,
                             const void* const* R_slab, int ldR, void* const* C_slab, int ldC, void* const* streams);
 
+/* The product with its result stored to n_dst (1..8) buffers at once: C_dst[d][i*ldC + j] for every d, all with the
+ * same ldC.  On the route that shares X.R through L2 the epilogue of the kernel writes every tile to each destination
+ * with ordinary global stores, so a destination may be another GPU's memory mapped into this process (peer access or
+ * a shared allocation): with C_dst[d] = column n0 of GPU d's full Y[m][N] and ldC = N, every GPU of a node ends up
+ * with all of Y without a separate all-gather (the direct peer-store epilogue; no TMA and no multicast touch peer
+ * memory).  Other routes compute into C_dst[0] and copy.  The caller synchronises the GPUs before reading (the
+ * stores of a peer are complete when that peer's stream is).  No counterpart in the reference, which is single-GPU. */
+int b200_oft_tn_f16_gather(int m, int n, int k, int group_size, int reconn_sz,
+                           const void* A, int ldA, const void* B, int ldB, const void* R, int ldR,
+                           int n_dst, void* const* C_dst, int ldC, void* stream);
+
 /* Tile visiting order of the persistent kernels; same order as z_curve(grid, idx) (z_curve.hpp:28-49). */
 int b200_tile_coord(unsigned tiles_m, unsigned tiles_n, unsigned idx, unsigned* tile_m, unsigned* tile_n);
 

@@ -608,3 +608,24 @@ def test_oft_ring_route_on_two_streams(lib, cuda, pair_build):
         torch.cuda.synchronize()
     assert ops.device_status(lib)[0] == 0
     assert torch.equal(c1, alone) and torch.equal(c2, alone)
+
+
+@pytest.mark.parametrize("m,n,k,b,gs", [(384, 2048, 256, 64, None), (200, 2056, 192, 32, None), (256, 512, 256, 64, None), (256, 2048, 128, 128, 1024)])
+def test_gather_entry_point_stores_every_destination(lib, cuda, pair_build, m, n, k, b, gs):
+    """b200_oft_tn_f16_gather with three destinations on this GPU (padded ldC, canaries): each holds the bits of the
+    plain call, whether the shared-X.R kernel stores them from its epilogue (wide groups) or the library copies."""
+    import torch
+
+    A, R, B = make_oft_case(m, n, k, b, gs, seed=81)
+    want = run_oft(lib, cuda, A, R, B, m, n, k, b, gs)
+    dA, dB, dR = (torch.from_numpy(x).to(cuda) for x in (A, B, R))
+    ldc = n + 8
+    dsts = [torch.full((m + 1, ldc), -7.0, dtype=torch.float16, device=cuda) for _ in range(3)]
+    ops.oft_tn_gather(m, n, k, dA, k, dB, k, dR, k, dsts, ldc, group_size=gs, reconn_sz=b, lib=lib)
+    assert ops.device_status(lib)[0] == 0
+    for d in dsts:
+        out = d.cpu().numpy()
+        assert np.array_equal(out[:m, :n].view(np.uint16), want.view(np.uint16))
+        assert np.all(out[m] == np.float16(-7.0)) and np.all(out[:m, n:] == np.float16(-7.0))
+    with pytest.raises(ops.Error):
+        ops.oft_tn_gather(m, n, k, dA, k, dB, k, dR, k, dsts * 3, ldc, group_size=gs, reconn_sz=b, lib=lib)  # nine destinations
