@@ -615,7 +615,7 @@ int launch_oft3(int m, int n, int k, const void* A, int ldA, const void* B, int 
   // a band share, W streams past them once per band, X is read once.
   const long long operand_bytes = (static_cast<long long>(m) + n) * k * 2;
   const bool big = operand_bytes > 3ll * st->l2_bytes / 2;
-  const bool streams = big && static_cast<long long>(n) * k * 2 > st->l2_bytes;
+  const bool streams = big && !w_resident;  // W cannot stay in L2 beside the ring: it streams from DRAM once per band
   unsigned long long hint_a = streams ? kL2EvictLast : kL2EvictNormal, hint_b = streams ? kL2EvictFirst : kL2EvictNormal;
   if (const int h = opt(kOptL2Hints); h >= 0) { hint_a = hint_word(h / 10); hint_b = hint_word(h % 10); }
   // Phase lock of the tile rounds only when W streams from DRAM: the pairs that share a W tile then fetch it
