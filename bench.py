@@ -51,6 +51,9 @@ NCU_TRAFFIC_BYTES = {
     # blocks, X and Y once, so traffic grows in proportion to M.  Projection shape: captured whole (584.5 + 295.3 MB
     # against 303 MB algorithmic; the extra is X.R leaving L2 once and W read again by later bands).
     ("oft_large_m65536_k8192_n28672_b128", "fused_ring"): 28.2e9,
+    # The same ring with the rotation on SM pairs of its own (oft4_kernel), captured the same way at M 16384:
+    # read 4.79 GB + write 1.17 GB, times 4.
+    ("oft_large_m65536_k8192_n28672_b128", "fused_ring_split"): 23.9e9,
     ("oft_proj_m16384_k4096_n4096_b64", "fused_ring"): 879.8e6,
     # two-pass route, GEMM pass (gemm2_kernel): read 17.86 GB + write 3.72 GB against 5.3 GB algorithmic; the
     # rotation pass before it moves 1.08 + 1.03 GB, its algorithmic bytes
@@ -504,12 +507,13 @@ def run_gpu_arm(args, workload):
         achieved = flops_launch / (ms * 1e-3) * 1e-12
         timed_s = ms * args.steps * 1e-3
         peak = peaks["bf16_sustained"] if timed_s >= 2.0 else peaks["bf16_burst"]
-        kernel_of = {"fused_ring": "oft3_kernel", "fused_tmem": "oft2_kernel", "two_pass": "xr_kernel + gemm2_kernel"}
+        kernel_of = {"fused_ring": "oft3_kernel", "fused_ring_split": "oft4_kernel", "fused_tmem": "oft2_kernel", "two_pass": "xr_kernel + gemm2_kernel"}
+        config_of_route = {"fused_ring": "oft_ring", "fused_ring_split": "oft_ring_split"}
         roofline = {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak,
                     "peak_source": f"{peaks['source']} bf16 {'sustained' if timed_s >= 2.0 else 'burst'} (cuBLAS matmul on this pool)",
                     "traffic": (NCU_TRAFFIC_BYTES.get((workload, plan["path"])) if world == 1 else None),
                     "frac_of_nominal_fp16": achieved / NOMINAL_FP16_TFLOPS, "route": plan["path"], "kernel": kernel_of[plan["path"]],
-                    "launch_ms": ms, "kernel_config": ops.kernel_info(lib)["oft_ring" if plan["path"] == "fused_ring" else "oft"], "n_per_gpu": n_loc,
+                    "launch_ms": ms, "kernel_config": ops.kernel_info(lib)[config_of_route.get(plan["path"], "oft")], "n_per_gpu": n_loc,
                     "routes": routes}
         line = {
             "metric": METRIC, "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps, "warmup": warm,

@@ -27,6 +27,7 @@
 #include "oft2_kernel.cuh"
 #include "xr_kernel.cuh"
 #include "oft3_kernel.cuh"
+#include "oft4_kernel.cuh"
 
 namespace {
 
@@ -49,10 +50,10 @@ int fail(int code, const char* fmt, ...) {
 // library choose".  The B200_* environment variables of the same meaning are read ONCE, at the first use
 // of any option in the process, as initial values; after that only b200_set_option changes them, so
 // nothing on the launch path reads the environment.
-enum OptionId { kOptOftRoute, kOptRaster, kOptTileSync, kOptL2Hints, kOptGemmTileSync, kOptGemmL2Hints, kOptGemmSplit, kOptMaps3d, kOptRingBands, kOptPrefetch, kOptCount };
+enum OptionId { kOptOftRoute, kOptRaster, kOptTileSync, kOptL2Hints, kOptGemmTileSync, kOptGemmL2Hints, kOptGemmSplit, kOptMaps3d, kOptRingBands, kOptPrefetch, kOptRotPairs, kOptCount };
 struct OptionDef { const char* name; const char* env; int initial; };
 constexpr OptionDef kOptionDefs[kOptCount] = {
-    {"oft_route", "B200_OFT_PATH", 0},            // 0 choose, 1 X.R in tensor memory per tile, 2 two passes, 3 X.R shared through the L2 ring
+    {"oft_route", "B200_OFT_PATH", 0},            // 0 choose, 1 X.R in tensor memory per tile, 2 two passes, 3 / 4 X.R shared through the L2 ring
     {"raster", "B200_RASTER", -1},                // tile order: 0 z-curve, g > 0 bands of g tile rows
     {"tile_sync", "B200_TILE_SYNC", -1},          // cross-CTA phase lock of the fused kernels
     {"l2_hints", "B200_L2_HINTS", -1},            // 10 * a + b, a / b = 0 normal, 1 evict-first, 2 evict-last for the A / B loads
@@ -62,6 +63,7 @@ constexpr OptionDef kOptionDefs[kOptCount] = {
     {"maps_3d", "B200_MAPS_3D", -1},              // 0: one 2-D copy per 128-byte chunk of an MN-major tile
     {"ring_bands", "B200_RING_BANDS", -1},        // bands of row blocks the X.R ring of route 3 holds (>= 2)
     {"prefetch", "B200_PREFETCH", -1},            // route 3: K steps by which W tiles are asked into L2 ahead of their load (0 off)
+    {"rot_pairs", "B200_ROT_PAIRS", -1},          // route 4: SM pairs that only rotate (>= 1)
 };
 std::atomic<int> g_opt[kOptCount];
 std::once_flag g_opt_once;
@@ -547,12 +549,71 @@ int oft_two_pass(int m, int n, int k, int group_size, const void* A, int ldA, co
   return rc;
 }
 
-// ---- fused OFT with X.R shared through an L2-resident ring (oft3_kernel) ------------------------------------
+// ---- fused OFT with X.R shared through an L2-resident ring (oft3_kernel, oft4_kernel) -----------------------
 // One launch per N-group (each group has its own R, so its own X.R).  Scratch, stream-ordered from the library's
-// pool: the ring of row blocks of X.R (2 bands of 8 row blocks of 256 rows, or all row blocks if fewer) and the
-// zeroed ready / done / round counters of this launch.  The kernel's CTAs wait for one another, so it is only
+// pool: the ring of row blocks of X.R (at least 2 bands of row blocks of 256 rows, or all row blocks if fewer) and
+// the zeroed ready / done / round counters of this launch.  The kernels' CTAs wait for one another, so they are only
 // ever launched cooperatively (all CTAs resident); kNoRing tells the caller to take another route.
 constexpr int kNoRing = -1001;
+
+// Geometry and launch policy shared by the two kernels that keep X.R in the ring.
+//   Tile order and ring size: a band of row blocks sweeps once over all of W.  When W stays in L2 beside the ring
+//   the sweeps cost no DRAM traffic, so bands are short (4 row blocks): the tiles in flight then touch few row
+//   blocks and the rotation can run further ahead in a ring of the same size.  When W streams from DRAM once per
+//   band, bands of 8 halve that traffic.  The ring takes what L2 has left beside W (32 to 64 MB), at least two
+//   bands, in whole bands.  The options raster and ring_bands override both.
+//   Eviction priorities as for the plain pair GEMM (launch_gemm_bn): the band's rows of X.R are what the tiles of
+//   a band share, W streams past them once per band, X is read once.
+//   Phase lock of the tile rounds only when W streams from DRAM: the pairs that share a W tile then fetch it
+//   together (one-pass ncu counters at M 16384, K 8192, N 28672: DRAM reads 19.1 -> 5.8 GB per launch, 6.13 -> 5.53 ms).
+//   With W resident in L2 the ready / done counters keep the pairs close enough and the lock only costs time
+//   (interleaved runs at M 65536, K 8192, N 3584: 17 % slower with it).
+//   Rotation pairs (oft4_kernel only): measured under load, a pair of SMs that only rotates needs about 1.6 times
+//   as long for 64 columns of a row block (256 x 64 of X, 0.7 to 0.8 us: shared-memory bandwidth) as a product pair
+//   for one K step (0.5 us at the sustained clock), and a row block feeds tiles_w tiles; 25 % on top.
+struct RingPlan {
+  int tiles_x, tiles_w, raster, bands, bands_total, slots, tile_sync, rot_pairs;
+  long long ldx;
+  size_t counter_bytes, ring_bytes;
+  unsigned long long hint_x, hint_a, hint_b;
+};
+RingPlan ring_plan(int m, int n, int k, const DeviceState* st) {
+  RingPlan p;
+  p.tiles_x = (m + 255) / 256;
+  p.tiles_w = (n + 255) / 256;
+  const long long w_bytes = static_cast<long long>(n) * k * 2, mib = 1ll << 20;
+  const bool w_resident = w_bytes <= 64 * mib;
+  p.raster = opt(kOptRaster) > 0 ? opt(kOptRaster) : (w_resident ? 4 : 8);
+  p.ldx = (static_cast<long long>(k) + 63) & ~63ll;
+  const long long block_bytes = 256 * p.ldx * 2;
+  long long budget = 64 * mib;
+  if (w_resident) {
+    budget = st->l2_bytes - w_bytes - 16 * mib;
+    budget = budget < 32 * mib ? 32 * mib : (budget > 64 * mib ? 64 * mib : budget);
+  }
+  p.bands = static_cast<int>(budget / (block_bytes * p.raster));
+  if (p.bands < 2) p.bands = 2;
+  if (opt(kOptRingBands) >= 2) p.bands = opt(kOptRingBands);
+  p.bands_total = (p.tiles_x + p.raster - 1) / p.raster;
+  p.slots = p.tiles_x <= p.bands * p.raster ? p.tiles_x : p.bands * p.raster;
+  p.counter_bytes = ((static_cast<size_t>(3) * p.tiles_x + 4) * sizeof(int) + 1023) & ~static_cast<size_t>(1023);
+  p.ring_bytes = static_cast<size_t>(p.slots) * 256 * p.ldx * 2;
+  const long long operand_bytes = (static_cast<long long>(m) + n) * k * 2;
+  const bool big = operand_bytes > 3ll * st->l2_bytes / 2;
+  const bool streams = big && !w_resident;  // W cannot stay in L2 beside the ring: it streams from DRAM once per band
+  p.hint_x = big ? kL2EvictFirst : kL2EvictNormal;
+  p.hint_a = streams ? kL2EvictLast : kL2EvictNormal;
+  p.hint_b = streams ? kL2EvictFirst : kL2EvictNormal;
+  if (const int h = opt(kOptL2Hints); h >= 0) { p.hint_a = hint_word(h / 10); p.hint_b = hint_word(h % 10); }
+  p.tile_sync = opt(kOptTileSync) >= 0 ? opt(kOptTileSync) : (streams ? 1 : 0);
+  const double x = 1.6 / p.tiles_w;
+  p.rot_pairs = static_cast<int>(1.25 * (st->sm_count / 2) * x / (1.0 + x) + 0.999);
+  if (opt(kOptRotPairs) >= 1) p.rot_pairs = opt(kOptRotPairs);
+  if (p.rot_pairs < 1) p.rot_pairs = 1;
+  if (p.rot_pairs > st->sm_count / 4) p.rot_pairs = st->sm_count / 4;
+  if (p.bands_total <= p.bands) p.rot_pairs = 0;  // the ring holds every row block: all pairs rotate, then all multiply
+  return p;
+}
 
 // Further destinations of the result, set by b200_oft_tn_f16_gather for its own call: the shared-X.R kernel stores
 // every tile to each of them from its epilogue (plain stores; the buffers may be another GPU's memory mapped into
@@ -564,113 +625,140 @@ struct MoreDst {
 };
 thread_local MoreDst g_more;
 
+// Scratch of one ring launch, stream-ordered from the library's pool: zeroed counters, then the ring.
+struct RingScratch {
+  unsigned char* base = nullptr;
+  cudaStream_t stream = nullptr;
+  int* counters() const { return reinterpret_cast<int*>(base); }
+  void* ring(const RingPlan& p) const { return base + p.counter_bytes; }
+  ~RingScratch() {
+    if (!base) return;
+    const std::string keep = g_err;
+    cudaFreeAsync(base, stream);
+    g_err = keep;
+  }
+};
+int ring_scratch(RingScratch* sc, const RingPlan& p, cudaStream_t stream, DeviceState* st) {
+  if (cudaError_t e = cudaMallocFromPoolAsync(reinterpret_cast<void**>(&sc->base), p.counter_bytes + p.ring_bytes, st->pool, stream)) {
+    cudaGetLastError();
+    sc->base = nullptr;
+    if (e == cudaErrorMemoryAllocation) return kNoRing;
+    return fail(B200_ECUDA, "cudaMallocFromPoolAsync: %s", cudaGetErrorString(e));
+  }
+  sc->stream = stream;
+  if (cudaError_t e = cudaMemsetAsync(sc->base, 0, p.counter_bytes, stream)) return fail(B200_ECUDA, "cudaMemsetAsync: %s", cudaGetErrorString(e));
+  return B200_OK;
+}
+
+// oft3_kernel: every pair rotates and multiplies.
 template <int kB>
 int launch_oft3(int m, int n, int k, const void* A, int ldA, const void* B, int ldB, const void* Rg, int ldR, void* C, int ldC,
                 cudaStream_t stream, DeviceState* st, long long more_offset) {
   using T = Oft3Traits<kB, 2, 5>;
   if (!st->pool) return kNoRing;
-  const int tiles_m = (m + 2 * T::kBM - 1) / (2 * T::kBM), tiles_n = (n + T::kBN - 1) / T::kBN;
-  // Tile order and ring size.  A band of row blocks sweeps once over all of W.  When W stays in L2 beside the ring
-  // the sweeps cost no DRAM traffic, so bands are short (4 row blocks): the tiles in flight then touch few row
-  // blocks and the rotation can run further ahead in a ring of the same size.  When W streams from DRAM once per
-  // band, bands of 8 halve that traffic.  The ring takes what L2 has left beside W (32 to 64 MB), at least two
-  // bands, in whole bands.  The options raster and ring_bands override both.
-  const long long w_bytes = static_cast<long long>(n) * k * 2, mib = 1ll << 20;
-  const bool w_resident = w_bytes <= 64 * mib;
-  const int raster = opt(kOptRaster) > 0 ? opt(kOptRaster) : (w_resident ? 4 : 8);
-  const long long ldx = (static_cast<long long>(k) + 63) & ~63ll;
-  const long long block_bytes = 2ll * T::kBM * ldx * 2;
-  long long budget = 64 * mib;
-  if (w_resident) {
-    budget = st->l2_bytes - w_bytes - 16 * mib;
-    budget = budget < 32 * mib ? 32 * mib : (budget > 64 * mib ? 64 * mib : budget);
-  }
-  int bands = static_cast<int>(budget / (block_bytes * raster));
-  if (bands < 2) bands = 2;
-  if (opt(kOptRingBands) >= 2) bands = opt(kOptRingBands);
-  const int slots = tiles_m <= bands * raster ? tiles_m : bands * raster;
-  const size_t counter_bytes = ((static_cast<size_t>(3) * tiles_m + 4) * sizeof(int) + 1023) & ~static_cast<size_t>(1023);
-  const size_t ring_bytes = static_cast<size_t>(slots) * 2 * T::kBM * ldx * 2;
-  unsigned char* scratch = nullptr;
-  if (cudaError_t e = cudaMallocFromPoolAsync(reinterpret_cast<void**>(&scratch), counter_bytes + ring_bytes, st->pool, stream)) {
-    cudaGetLastError();
-    if (e == cudaErrorMemoryAllocation) return kNoRing;
-    return fail(B200_ECUDA, "cudaMallocFromPoolAsync: %s", cudaGetErrorString(e));
-  }
-  auto finish = [&](int rc) {
-    const std::string keep = g_err;
-    cudaFreeAsync(scratch, stream);
-    g_err = keep;
-    return rc;
-  };
-  if (cudaError_t e = cudaMemsetAsync(scratch, 0, counter_bytes, stream)) return finish(fail(B200_ECUDA, "cudaMemsetAsync: %s", cudaGetErrorString(e)));
-  int* counters = reinterpret_cast<int*>(scratch);
-  void* ring = scratch + counter_bytes;
+  const RingPlan p = ring_plan(m, n, k, st);
+  RingScratch sc;
+  if (int rc = ring_scratch(&sc, p, stream, st)) return rc;
+  int* counters = sc.counters();
   CUtensorMap mx, mr, mxr, mb;
-  if (int rc = make_map(&mx, A, 2, k, m, ldA, T::kBK, T::kBM, "A")) return finish(rc);
-  if (int rc = make_map(&mr, Rg, 2, k, kB, ldR, T::kBK, kB / 2, "R")) return finish(rc);
-  if (int rc = make_map(&mxr, ring, 2, ldx, static_cast<long long>(slots) * 2 * T::kBM, ldx, T::kBK, T::kBM, "XR ring")) return finish(rc);
-  if (int rc = make_map(&mb, B, 2, k, n, ldB, T::kBK, T::kBNHalf, "B")) return finish(rc);
-  // Eviction priorities as for the plain pair GEMM (launch_gemm_bn): the band's rows of X.R are what the tiles of
-  // a band share, W streams past them once per band, X is read once.
-  const long long operand_bytes = (static_cast<long long>(m) + n) * k * 2;
-  const bool big = operand_bytes > 3ll * st->l2_bytes / 2;
-  const bool streams = big && !w_resident;  // W cannot stay in L2 beside the ring: it streams from DRAM once per band
-  unsigned long long hint_a = streams ? kL2EvictLast : kL2EvictNormal, hint_b = streams ? kL2EvictFirst : kL2EvictNormal;
-  if (const int h = opt(kOptL2Hints); h >= 0) { hint_a = hint_word(h / 10); hint_b = hint_word(h % 10); }
-  // Phase lock of the tile rounds only when W streams from DRAM: the pairs that share a W tile then fetch it
-  // together (one-pass ncu counters at M 16384, K 8192, N 28672: DRAM reads 19.1 -> 5.8 GB per launch, 6.13 -> 5.53 ms).
-  // With W resident in L2 the ready / done counters keep the pairs close enough and the lock only costs time
-  // (interleaved runs at M 65536, K 8192, N 3584: 17 % slower with it).
-  (void)big;
-  int tile_sync = streams ? 1 : 0;
-  if (opt(kOptTileSync) >= 0) tile_sync = opt(kOptTileSync);
+  if (int rc = make_map(&mx, A, 2, k, m, ldA, T::kBK, T::kBM, "A")) return rc;
+  if (int rc = make_map(&mr, Rg, 2, k, kB, ldR, T::kBK, kB / 2, "R")) return rc;
+  if (int rc = make_map(&mxr, sc.ring(p), 2, p.ldx, static_cast<long long>(p.slots) * 2 * T::kBM, p.ldx, T::kBK, T::kBM, "XR ring")) return rc;
+  if (int rc = make_map(&mb, B, 2, k, n, ldB, T::kBK, T::kBNHalf, "B")) return rc;
   // (asking W tiles into L2 a few K steps ahead of their loads was measured too: with the phase lock it added
-  // 1.2 GB of DRAM reads and 5 % of time at the shape above, so it stays off unless the option asks for it)
+  // 1.2 GB of DRAM reads and 5 % of time at M 16384, K 8192, N 28672, so it stays off unless the option asks for it)
   const int prefetch_w = opt(kOptPrefetch) >= 0 ? opt(kOptPrefetch) : 0;
-  Oft3Args args{m, n, k, static_cast<__half*>(C), ldC, st->status, raster, big ? kL2EvictFirst : kL2EvictNormal, hint_a, hint_b,
-                tile_sync, counters + 3 * tiles_m, prefetch_w, slots, counters, counters + 2 * tiles_m, g_more.n, {}};
+  Oft3Args args{m, n, k, static_cast<__half*>(C), ldC, st->status, p.raster, p.hint_x, p.hint_a, p.hint_b,
+                p.tile_sync, counters + 3 * p.tiles_x, prefetch_w, p.slots, counters, counters + 2 * p.tiles_x, g_more.n, {}};
   for (int d = 0; d < g_more.n; ++d) args.C_more[d] = g_more.p[d] + more_offset;
   auto kernel = oft3_kernel<T>;
-  if (int rc = opt_in_smem(kernel, T::kSmemBytes)) return finish(rc);
-  const long long tiles = static_cast<long long>(tiles_m) * tiles_n;
+  if (int rc = opt_in_smem(kernel, T::kSmemBytes)) return rc;
+  const long long tiles = static_cast<long long>(p.tiles_x) * p.tiles_w;
   const int pairs = static_cast<int>(tiles < st->sm_count / 2 ? tiles : st->sm_count / 2);
   if (launch_cooperative(kernel, 2 * pairs, T::kThreads, T::kSmemBytes, stream, mx, mr, mxr, mb, args) != cudaSuccess) {
     cudaGetLastError();
-    return finish(kNoRing);
+    return kNoRing;
   }
-  return finish(B200_OK);
+  return B200_OK;
+}
+
+// oft4_kernel: the last rot_pairs pairs only rotate, the others only multiply (after all of them have rotated the
+// first bands together).
+template <int kB>
+int launch_oft4(int m, int n, int k, const void* A, int ldA, const void* B, int ldB, const void* Rg, int ldR, void* C, int ldC,
+                cudaStream_t stream, DeviceState* st) {
+  using T = Oft4Traits<kB>;
+  if (!st->pool) return kNoRing;
+  const RingPlan p = ring_plan(m, n, k, st);
+  const long long tiles = static_cast<long long>(p.tiles_x) * p.tiles_w;
+  const int all_pairs = st->sm_count / 2;
+  const int prod_pairs = static_cast<int>(tiles < all_pairs - p.rot_pairs ? tiles : all_pairs - p.rot_pairs);
+  // the first phase covers the first wave of tiles and one band more, as far as the ring goes
+  int prologue = (prod_pairs + p.raster * p.tiles_w - 1) / (p.raster * p.tiles_w) + 1;
+  if (prologue > p.bands) prologue = p.bands;
+  if (p.rot_pairs == 0) prologue = p.bands_total;
+  RingScratch sc;
+  if (int rc = ring_scratch(&sc, p, stream, st)) return rc;
+  int* counters = sc.counters();
+  const long long ring_rows = static_cast<long long>(p.slots) * 2 * T::kBM;
+  CUtensorMap mx, mr, mxr, mxs, mw;
+  if (int rc = make_map(&mx, A, 2, k, m, ldA, T::kBK, T::kBM, "A")) return rc;
+  if (int rc = make_map(&mr, Rg, 2, k, kB, ldR, T::kBK, kB / 2, "R")) return rc;
+  if (int rc = make_map(&mxr, sc.ring(p), 2, p.ldx, ring_rows, p.ldx, T::kBK, T::kBM, "XR ring")) return rc;
+  if (int rc = make_map(&mxs, sc.ring(p), 2, p.ldx, ring_rows, p.ldx, T::kBK, 32, "XR ring (stores)")) return rc;
+  if (int rc = make_map(&mw, B, 2, k, n, ldB, T::kBK, T::kBM, "B")) return rc;
+  Oft4Args args{m, n, k, static_cast<__half*>(C), ldC, st->status, p.raster, p.hint_x, p.hint_a, p.hint_b,
+                p.tile_sync, counters + 3 * p.tiles_x, p.slots, counters, counters + 2 * p.tiles_x, p.rot_pairs, prologue};
+  auto kernel = oft4_kernel<T>;
+  if (int rc = opt_in_smem(kernel, T::kSmemBytes)) return rc;
+  if (launch_cooperative(kernel, 2 * (prod_pairs + p.rot_pairs), T::kThreads, T::kSmemBytes, stream, mx, mr, mxr, mxs, mw, args) != cudaSuccess) {
+    cudaGetLastError();
+    return kNoRing;
+  }
+  return B200_OK;
 }
 
 template <int kB>
 int oft_ring(int m, int n, int k, int group_size, const void* A, int ldA, const void* B, int ldB, const void* R, int ldR,
-             void* C, int ldC, cudaStream_t stream, DeviceState* st) {
+             void* C, int ldC, cudaStream_t stream, DeviceState* st, bool split_pairs) {
   int rc = B200_OK;
-  for (int g = 0; rc == B200_OK && g < n / group_size; ++g)  // stream order serialises the groups
-    rc = launch_oft3<kB>(m, group_size, k, A, ldA, static_cast<const __half*>(B) + static_cast<long long>(g) * group_size * ldB, ldB,
-                         static_cast<const __half*>(R) + static_cast<long long>(g) * kB * ldR, ldR,
-                         static_cast<__half*>(C) + static_cast<long long>(g) * group_size, ldC, stream, st, static_cast<long long>(g) * group_size);
-  if (rc == B200_OK) g_more.stored = true;
+  for (int g = 0; rc == B200_OK && g < n / group_size; ++g) {  // stream order serialises the groups
+    const __half* Bg = static_cast<const __half*>(B) + static_cast<long long>(g) * group_size * ldB;
+    const __half* Rg = static_cast<const __half*>(R) + static_cast<long long>(g) * kB * ldR;
+    __half* Cg = static_cast<__half*>(C) + static_cast<long long>(g) * group_size;
+    if (split_pairs) rc = launch_oft4<kB>(m, group_size, k, A, ldA, Bg, ldB, Rg, ldR, Cg, ldC, stream, st);
+    else rc = launch_oft3<kB>(m, group_size, k, A, ldA, Bg, ldB, Rg, ldR, Cg, ldC, stream, st, static_cast<long long>(g) * group_size);
+  }
+  if (rc == B200_OK && !split_pairs) g_more.stored = true;
   return rc;
 }
 
 // Routes of the AR_W product.  1: oft2_kernel, X.R kept in tensor memory and formed again for every N tile (no
 // scratch; the only route for groups narrower than the N tile).  2: rotation pass + plain GEMM.  3: oft3_kernel,
-// one X.R per row block shared by all N tiles of the group through the L2 ring.  0 = choose: the ring kernel when a
-// group spans enough N tiles (its rotation work is 1 / tiles_n of route 1's, and unlike route 2 it neither writes
-// X.R to HBM nor serialises the rotation in front of the product), else route 1.  Crossover measured at M 16384,
-// K 4096 (interleaved runs, route 3 / route 1 time): b 64: 4 tiles 1.13, 6 tiles 1.00, 8 tiles 0.98, 12 tiles 0.92,
+// one X.R per row block shared by all N tiles of the group through the L2 ring, every SM pair rotating and
+// multiplying.  4: oft4_kernel, the same ring with the rotation on a few SM pairs of its own, so that the others
+// run the plain GEMM's loop (two accumulators, six stages).  0 = choose: a ring kernel when a group spans enough N
+// tiles (its rotation work is 1 / tiles_n of route 1's, and unlike route 2 it neither writes X.R to HBM nor
+// serialises the rotation in front of the product), else route 1.  Crossover measured at M 16384, K 4096
+// (interleaved runs, route 3 / route 1 time): b 64: 4 tiles 1.13, 6 tiles 1.00, 8 tiles 0.98, 12 tiles 0.92,
 // 16 tiles 0.95; b 128: 2 tiles 1.43, 4 tiles 0.95, 6 tiles 0.84, 8 tiles 0.82; b 32: 8 tiles 1.00; b 16: 16 tiles 0.89.
+// Route 4 instead of 3 when three rotation pairs or fewer keep up with the product (wide groups: a rotation pair
+// is bound by shared-memory bandwidth, and every pair that rotates is one that does not multiply).  Interleaved
+// sustained runs, M 65536, K 8192, b 128, route 4 / route 3 time: N 28672 (2 pairs) 0.94, N 14336 (3 pairs) 0.93,
+// N 7168 (6 pairs) 0.98 to 1.02, N 3584 (7 pairs) 1.02; M 16384, K = N 4096, b 64 (6 pairs) 1.25.
 // Set by b200_oft_tn_f16_two_pass for its own call and by the option "oft_route".
 thread_local int g_oft_path = 0;
 
-int choose_route(int group_size, int b, const DeviceState* st) {
+int choose_route(int m, int group_size, int k, int b, const DeviceState* st) {
   int path = g_oft_path != 0 ? g_oft_path : opt(kOptOftRoute);
-  const bool can_share = kOftPair && st->pool != nullptr;  // routes 2 and 3 need scratch from the pool
-  if (path == 2 || path == 3) return can_share ? path : 1;
+  const bool can_share = kOftPair && st->pool != nullptr;  // routes 2, 3 and 4 need scratch from the pool
+  if (path == 2 || path == 3 || path == 4) return can_share ? path : 1;
   if (path == 1) return 1;
   const int min_tiles = b >= 128 ? 4 : 8;
-  return (can_share && group_size >= min_tiles * static_cast<int>(CurrCompParams::bN)) ? 3 : 1;
+  if (!can_share || group_size < min_tiles * static_cast<int>(CurrCompParams::bN)) return 1;
+  if (g_more.n > 0) return 3;  // only oft3_kernel stores to further destinations
+  const RingPlan p = ring_plan(m, group_size, k, st);
+  return (p.rot_pairs >= 1 && p.rot_pairs <= 3) ? 4 : 3;
 }
 
 // group_size == n or a multiple of the N tile: one R per tile.  group_size a divisor of the N tile (the
@@ -679,7 +767,7 @@ template <int kB>
 int launch_oft(int m, int n, int k, int group_size, const void* A, int ldA, const void* B, int ldB, const void* R, int ldR,
                void* C, int ldC, cudaStream_t stream, DeviceState* st) {
   constexpr int kBN = CurrCompParams::bN;
-  const int route = choose_route(group_size, kB, st);
+  const int route = choose_route(m, group_size, k, kB, st);
   if (route == 2) {
     const int rc = oft_two_pass<kB>(m, n, k, group_size, A, ldA, B, ldB, R, ldR, C, ldC, stream, st);
     if (rc != kNoScratch) return rc;
@@ -687,8 +775,8 @@ int launch_oft(int m, int n, int k, int group_size, const void* A, int ldA, cons
     // out of memory for X.R: the kernel that keeps X.R in tensor memory needs no scratch
   }
   if constexpr (kOftPair) {
-    if (route == 3 && (group_size == n || group_size % kBN == 0)) {
-      const int rc = oft_ring<kB>(m, n, k, group_size, A, ldA, B, ldB, R, ldR, C, ldC, stream, st);
+    if ((route == 3 || route == 4) && (group_size == n || group_size % kBN == 0)) {
+      const int rc = oft_ring<kB>(m, n, k, group_size, A, ldA, B, ldB, R, ldR, C, ldC, stream, st, route == 4);
       if (rc != kNoRing) return rc;
       // no scratch, or the cooperative launch was refused: fall through to the kernel that needs neither
     }
@@ -1012,10 +1100,10 @@ int b200_oft_plan(int m, int n, int k, int group_size, int reconn_sz, int* path,
     return fail(B200_EINVAL, "bad plan arguments (m=%d n=%d k=%d group_size=%d reconn_sz=%d)", m, n, k, group_size, reconn_sz);
   DeviceState* st;
   if (int rc = device_state(&st)) return rc;
-  const int route = choose_route(group_size, reconn_sz == 8 ? 16 : reconn_sz, st);
+  const int route = choose_route(m, group_size, k, reconn_sz == 8 ? 16 : reconn_sz, st);
   if (path) *path = route;
   const int groups = n / group_size;
-  if (kernel_launches) *kernel_launches = (route == 2 ? 2 * groups : (route == 3 ? groups : 1)) + (reconn_sz == 8 ? 1 : 0);
+  if (kernel_launches) *kernel_launches = (route == 2 ? 2 * groups : ((route == 3 || route == 4) ? groups : 1)) + (reconn_sz == 8 ? 1 : 0);
   return B200_OK;
 }
 
@@ -1408,13 +1496,15 @@ int b200_wait_profile(unsigned long long* out, int n) {
 }
 
 const char* b200_kernel_info(void) {
-  static char buf[1024];
+  static char buf[1536];
   using PH = Params<half, half, MMA_T, MMA_N>;
   using PF = Params<float, float, MMA_N, MMA_T>;
   using O64 = OftT<64, 1>;
   using O128 = OftT<128, 1>;
   using R64 = Oft3Traits<64, 2, 5>;
   using R128 = Oft3Traits<128, 2, 5>;
+  using S64 = Oft4Traits<64>;
+  using S128 = Oft4Traits<128>;
   snprintf(buf, sizeof buf,
            "{\"arch\": \"sm_100a\", \"gemm_half_tn\": {\"bM\": %d, \"bN\": %d, \"bK\": %d, \"bP\": %d}, "
            "\"gemm_float_nt\": {\"bM\": %d, \"bN\": %d, \"bK\": %d, \"bP\": %d}, "
@@ -1422,11 +1512,14 @@ const char* b200_kernel_info(void) {
            "\"b64\": {\"smem\": %d, \"tmem_cols\": %d, \"xr_bufs\": %d}, "
            "\"b128\": {\"smem\": %d, \"tmem_cols\": %d, \"xr_bufs\": %d}}, "
            "\"oft_ring\": {\"ctas\": 2, \"bM\": 128, \"bN\": 256, \"bK\": 64, \"stages_x_r\": %d, \"stages_xr_w\": %d, \"threads\": %d, "
-           "\"accumulators\": 1, \"b64\": {\"smem\": %d, \"rotation_bufs\": %d}, \"b128\": {\"smem\": %d, \"rotation_bufs\": %d}}}",
+           "\"accumulators\": 1, \"b64\": {\"smem\": %d, \"rotation_bufs\": %d}, \"b128\": {\"smem\": %d, \"rotation_bufs\": %d}}, "
+           "\"oft_ring_split\": {\"ctas\": 2, \"bM\": 128, \"bN\": 256, \"bK\": 64, \"stages_xr_w\": %d, \"threads\": %d, \"accumulators\": %d, "
+           "\"rotation_bufs\": %d, \"b64\": {\"smem\": %d, \"stages_x_r\": %d}, \"b128\": {\"smem\": %d, \"stages_x_r\": %d}}}",
            PH::bM, PH::bN, PH::bK, PH::bP, PF::bM, PF::bN, PF::bK, PF::bP, kOftPair ? 2 : 1, (int)CurrCompParams::bM, (int)CurrCompParams::bN,
            (int)CurrCompParams::bK, (int)CurrCompParams::bP1, (int)CurrCompParams::bP2, O64::kThreads, O64::kSmemBytes,
            O64::kTmemUsed, O64::kXrBufs, O128::kSmemBytes, O128::kTmemUsed, O128::kXrBufs, R64::kS1, R64::kS2, R64::kThreads, R64::kSmemBytes,
-           R64::kXrBufs, R128::kSmemBytes, R128::kXrBufs);
+           R64::kXrBufs, R128::kSmemBytes, R128::kXrBufs, S64::kStages, S64::kThreads, S64::kAccBufs, S64::kXrBufs, S64::kSmemBytes, S64::kS1,
+           S128::kSmemBytes, S128::kS1);
   return buf;
 }
 

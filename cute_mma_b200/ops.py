@@ -135,13 +135,14 @@ def rotate(m, k, A, ldA, R, ldR, XR, ldX, stream=None, *, reconn_sz=8, lib=None)
     _check(lib, lib.b200_rotate_f16(m, k, reconn_sz, _ptr(A), ldA, _ptr(R), ldR, _ptr(XR), ldX, _stream(stream)))
 
 
-ROUTES = {1: "fused_tmem", 2: "two_pass", 3: "fused_ring"}
+ROUTES = {1: "fused_tmem", 2: "two_pass", 3: "fused_ring", 4: "fused_ring_split"}
 
 
 def oft_plan(m, n, k, *, group_size=None, reconn_sz=8, lib=None) -> dict:
-    """{'path': 'fused_tmem' | 'two_pass' | 'fused_ring', 'kernel_launches': launches of the library's kernels per
-    oft_tn call}: fused_tmem keeps X.R in tensor memory per N tile, fused_ring shares one X.R per row block
-    among the N tiles of a group through an L2-resident ring, two_pass writes X.R to memory first."""
+    """{'path': 'fused_tmem' | 'two_pass' | 'fused_ring' | 'fused_ring_split', 'kernel_launches': launches of the
+    library's kernels per oft_tn call}: fused_tmem keeps X.R in tensor memory per N tile, fused_ring shares one X.R
+    per row block among the N tiles of a group through an L2-resident ring (fused_ring_split: with the rotation on
+    SM pairs of its own), two_pass writes X.R to memory first."""
     lib = lib or load_library()
     path, launches = ctypes.c_int(0), ctypes.c_int(0)
     _check(lib, lib.b200_oft_plan(m, n, k, n if group_size is None else group_size, reconn_sz, ctypes.byref(path), ctypes.byref(launches)))

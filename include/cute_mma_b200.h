@@ -41,8 +41,10 @@ enum {
  * fewer than 8 N tiles of 256 columns (4 for reconn_sz = 128) keeps X.R in tensor memory and forms it per N tile, as
  * the reference's kernel forms it per thread block (cute_oft_coop_pc.cu:19-186); a wider group forms one X.R per block
  * of 256 rows and shares it among all its N tiles through a ring of row blocks in device scratch that is sized to
- * stay in L2 (32 to 64 MB and a few counters per call in flight, from the same pool, one launch per N-group).  Both
- * give the same numbers; the second also the same bits as b200_oft_tn_f16_two_pass. */
+ * stay in L2 (32 to 64 MB and a few counters per call in flight, from the same pool, one launch per N-group).  In the
+ * ring kernel every SM pair rotates and multiplies; for very wide groups (three rotating pairs or fewer keep up) a
+ * variant gives the rotation to a few SM pairs of its own and runs the plain GEMM's loop on the others.  All give the
+ * same numbers; the ring kernels also the same bits as b200_oft_tn_f16_two_pass. */
 int b200_oft_tn_f16(int m, int n, int k, int group_size, int reconn_sz,
                     const void* A, int ldA, const void* B, int ldB, const void* R, int ldR,
                     void* C, int ldC, void* stream);
@@ -57,9 +59,10 @@ int b200_rotate_f16(int m, int k, int reconn_sz, const void* A, int ldA, const v
 
 /* Which route b200_oft_tn_f16 takes for this problem on the current device and how many of the library's
  * kernels one call launches.  *path: 1 fused kernel that keeps X.R in tensor memory and forms it per N tile
- * (groups of one N tile or less), 2 rotation pass + GEMM (only when asked for), 3 fused kernel in which one
- * X.R per row block serves all N tiles of its group through a ring of row blocks that stays in L2 (groups of
- * two N tiles or more).  No counterpart in the reference. */
+ * (narrow groups), 2 rotation pass + GEMM (only when asked for), 3 fused kernel in which one X.R per row block
+ * serves all N tiles of its group through a ring of row blocks that stays in L2 (groups of 8 N tiles or more, 4 for
+ * reconn_sz = 128), 4 the same ring with the rotation on SM pairs of its own (when at most three such pairs keep
+ * up with the product: groups of about 40 N tiles or more).  No counterpart in the reference. */
 int b200_oft_plan(int m, int n, int k, int group_size, int reconn_sz, int* path, int* kernel_launches);
 
 /* The same product in two passes: X.R (rounded to fp16, as above) is written once to device scratch of
@@ -237,13 +240,16 @@ int b200_wait_profile(unsigned long long* out, int n);
 const char* b200_kernel_info(void);
 
 /* Overrides of the launch heuristics, for experiments and tests (the reference fixes such choices at compile
- * time).  Names: "oft_route" (0 choose, 1 / 2 / 3 as in b200_oft_plan), "raster" (0 z-curve, g > 0 bands of g
+ * time).  Names: "oft_route" (0 choose, 1 / 2 / 3 / 4 as in b200_oft_plan), "raster" (0 z-curve, g > 0 bands of g
  * tile rows), "tile_sync", "gemm_tile_sync" (cross-CTA phase lock off / on), "l2_hints", "gemm_l2_hints"
  * (10 * a + b with 0 normal, 1 evict-first, 2 evict-last for the A / B tile loads), "gemm_split" (0: never
- * split small problems along K), "maps_3d" (0: per-chunk 2-D copies of MN-major tiles).  -1 (0 for the route)
+ * split small problems along K), "maps_3d" (0: per-chunk 2-D copies of MN-major tiles), "ring_bands" (bands of row
+ * blocks the X.R ring of routes 3 and 4 holds, >= 2), "prefetch" (route 3: K steps by which W tiles are asked into
+ * L2 ahead of their load), "rot_pairs" (route 4: SM pairs that only rotate, >= 1).  -1 (0 for the route)
  * hands the choice back to the library.  Process-wide; the B200_* environment variables of the same meaning
  * (B200_OFT_PATH, B200_RASTER, B200_TILE_SYNC, B200_L2_HINTS, B200_GEMM_TILE_SYNC, B200_GEMM_L2_HINTS,
- * B200_GEMM_SPLIT, B200_MAPS_3D) are read once, at the first use of any option, as initial values. */
+ * B200_GEMM_SPLIT, B200_MAPS_3D, B200_RING_BANDS, B200_PREFETCH, B200_ROT_PAIRS) are read once, at the first use of
+ * any option, as initial values. */
 int b200_set_option(const char* name, int value);
 int b200_get_option(const char* name, int* value);
 

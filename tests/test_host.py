@@ -32,6 +32,13 @@ def test_kernel_info_matches_config_headers(lib):
     for b, r_half in ((64, 4096), (128, 8192)):
         assert ring[f"b{b}"]["smem"] == 5 * 32768 + 2 * (16384 + r_half) + 16384 + (2 * 2 + 2 * 5 + 2 * ring[f"b{b}"]["rotation_bufs"] + 2) * 8 + 64 + 1024
         assert ring[f"b{b}"]["smem"] <= 232448 and 256 + ring[f"b{b}"]["rotation_bufs"] * max(b, 64) <= 512
+    split = info["oft_ring_split"]  # product pairs: 6 stages of 32 KB, 2 accumulators; rotation pairs: {X, R} stages + 8 staging buffers of 4 KB
+    assert split["stages_xr_w"] == 6 and split["accumulators"] == 2 and split["threads"] == 192
+    for b, r_half in ((64, 4096), (128, 8192)):
+        s1 = split[f"b{b}"]["stages_x_r"]
+        data = max(6 * 32768, s1 * (16384 + r_half) + 8 * 4096)
+        assert split[f"b{b}"]["smem"] == data + (2 * 6 + 2 * 2 + 2 * s1 + 2 * split["rotation_bufs"]) * 8 + 64 + 1024 <= 232448
+        assert split["rotation_bufs"] * max(b, 64) <= 512 and s1 >= 2 * max(b, 64) // 64
 
 
 def test_argument_validation_without_a_gpu(lib):
@@ -71,7 +78,7 @@ def test_new_entry_points_validate_before_any_cuda_call(lib):
     assert lib.b200_oft_tn_f16_sharded(8, 16, 16, 16, 16, 1, devs, None, 16, ptrs, 16, ptrs, 16, ptrs, 16, None) == ops.EINVAL
     with pytest.raises(ops.Error):
         ops.set_option("no_such_option", 1, lib)
-    for name in ("oft_route", "raster", "tile_sync", "l2_hints", "gemm_tile_sync", "gemm_l2_hints", "gemm_split", "maps_3d", "ring_bands", "prefetch"):
+    for name in ("oft_route", "raster", "tile_sync", "l2_hints", "gemm_tile_sync", "gemm_l2_hints", "gemm_split", "maps_3d", "ring_bands", "prefetch", "rot_pairs"):
         old = ops.get_option(name, lib)
         with ops.option(name, 3, lib):
             assert ops.get_option(name, lib) == 3

@@ -208,6 +208,56 @@ def test_oft_ring_route_reuses_its_slots_and_phase_locks(lib, cuda, pair_build):
     assert oft_ok(got[rows], ref)[0] == 0
 
 
+@pytest.mark.parametrize("m,n,k,b,gs", RING_CASES)
+def test_oft_split_ring_route_small_cases(lib, cuda, pair_build, m, n, k, b, gs):
+    """oft4_kernel (route 4) on problems whose row blocks all fit the ring: every SM pair rotates, then every pair
+    multiplies.  Same bits as the rotation pass + GEMM."""
+    if not pair_build:
+        pytest.skip("the shared-X.R kernels exist in the CTA-pair build only")
+    A, R, B = make_oft_case(m, n, k, b, gs, seed=29, kind="qr")
+    got = run_oft(lib, cuda, A, R, B, m, n, k, b, gs, route=4)
+    with ops.option("gemm_split", 0, lib):
+        two = run_oft(lib, cuda, A, R, B, m, n, k, b, gs, route=2)
+    assert np.array_equal(got.view(np.uint16), two.view(np.uint16))
+
+
+SPLIT_CASES = [
+    # m, n, k, b, raster, ring_bands, rot_pairs: more row blocks than the ring holds, so some pairs only rotate
+    (4096, 2048, 1024, 64, 2, 2, 1),
+    (4096, 2048, 1024, 64, 2, 2, 5),
+    (4096, 1024, 1024, 128, 2, 2, -1),
+    (4096, 2048, 512, 32, 2, 2, 2),
+    (4096, 2048, 512, 16, 2, 2, 3),
+    (4001, 2304, 1088, 64, 2, 2, -1),   # ragged M, 17 blocks of 64
+    (4001, 2304, 1152, 128, 3, 2, 2),   # a ragged last band
+    (256 * 40 + 72, 768, 320, 64, 4, 2, 30),  # far more rotation pairs than needed
+]
+
+
+@pytest.mark.parametrize("m,n,k,b,raster,bands,rot_pairs", SPLIT_CASES)
+def test_oft_split_ring_route_rotation_pairs_and_slot_reuse(lib, cuda, pair_build, m, n, k, b, raster, bands, rot_pairs):
+    """oft4_kernel with rotation pairs at work: the first bands are rotated by all pairs, the rest by the rotation
+    pairs, which rewrite a ring slot only after every tile that read it has finished.  Padded leading dimensions,
+    canaries around C, three launches (the counters are per launch), with and without the phase lock; against the
+    rotation pass + GEMM bit for bit and sampled rows against the oracle."""
+    if not pair_build:
+        pytest.skip("the shared-X.R kernels exist in the CTA-pair build only")
+    A, R, B = make_oft_case(m, n, k, b, seed=33, kind="qr")
+    with ops.option("gemm_split", 0, lib):
+        two = run_oft(lib, cuda, A, R, B, m, n, k, b, route=2)
+    with ops.option("raster", raster, lib), ops.option("ring_bands", bands, lib), ops.option("rot_pairs", rot_pairs, lib):
+        for sync in (0, 1, 1):
+            with ops.option("tile_sync", sync, lib):
+                got = run_oft(lib, cuda, A, R, B, m, n, k, b, ldA=k + 8, ldB=k + 16, ldR=k + 24, ldC=n + 8, route=4)
+            assert np.array_equal(got.view(np.uint16), two.view(np.uint16))
+    rows = np.array([0, 255, 256, 2047, 2048, m - 1])
+    ref = oracle.cpu_oft_tn(A[rows], R, B, len(rows), n, 1, k, b, threads=oracle.num_threads())
+    truth = oracle.oft_f64(A[rows], R, B, len(rows), n, 1, k, b, round_xr=True)
+    bad, worst = oft_ok(got[rows], ref, truth=truth)
+    assert bad == 0, (bad, worst)
+    assert truth_ok(got[rows], truth)[0] == 0
+
+
 def test_oft_two_pass_padded_and_bit_exact_cases(lib, cuda):
     m, n, k, b = 200, 328, 192, 64
     A, R, B = make_oft_case(m, n, k, b, seed=3)
@@ -426,12 +476,12 @@ def test_oft_large_slab_sampled(lib, cuda):
 def test_oft_large_full_size_sampled_and_routes_agree(lib, cuda, pair_build):
     """The large configuration whole on one GPU (M 65536, K 8192, N 28672, b 128, QR blocks): sampled rows
     against the oracle, linearity over the whole output, and the route the library picks here (one X.R per row
-    block shared through the L2 ring) must return the same bits as the rotation pass + GEMM."""
+    block shared through the L2 ring, rotated by SM pairs of their own) must return the same bits as the rotation pass + GEMM."""
     import torch
 
     m, k, n, b = 65536, 8192, 28672, 128
     if pair_build:
-        assert ops.oft_plan(m, n, k, reconn_sz=b, lib=lib)["path"] == "fused_ring"
+        assert ops.oft_plan(m, n, k, reconn_sz=b, lib=lib)["path"] == "fused_ring_split"
         assert ops.oft_plan(16384, 4096, 4096, reconn_sz=64, lib=lib) == {"path": "fused_ring", "kernel_launches": 1}
     assert ops.oft_plan(8192, 8192, 8192, group_size=256, reconn_sz=8, lib=lib) == {"path": "fused_tmem", "kernel_launches": 2}
     _sampled_parity(lib, cuda, m, n, k, b, "qr", 0.02, 8, seed=6)
@@ -525,6 +575,10 @@ def test_route_choice_either_side_of_the_crossover(lib, cuda, pair_build):
     assert plan(768, 128) == "fused_tmem" and plan(1024, 128) == "fused_ring"
     assert plan(4096, 8) == "fused_ring" and plan(1024, 16) == "fused_tmem"
     assert plan(8192, 64, 256) == "fused_tmem" and plan(8192, 64, 2048) == "fused_ring"   # the group's width counts, not N
+    # very wide groups: two or three SM pairs that only rotate keep up, the others run the plain GEMM's loop
+    wide = lambda n: ops.oft_plan(65536, n, 8192, reconn_sz=128, lib=lib)["path"]
+    assert wide(28672) == "fused_ring_split" and wide(14336) == "fused_ring_split" and wide(7168) == "fused_ring" and wide(3584) == "fused_ring"
+    assert ops.oft_plan(1024, 28672, 8192, reconn_sz=128, lib=lib)["path"] == "fused_ring"  # every row block fits the ring
     assert ops.oft_plan(16384, 8192, 4096, group_size=2048, reconn_sz=64, lib=lib)["kernel_launches"] == 4  # one launch per group
     with ops.option("oft_route", 2, lib):
         assert plan(4096, 64) == "two_pass"
