@@ -636,8 +636,9 @@ def test_sharded_entry_point_on_two_devices(lib, cuda):
     assert np.array_equal(got.view(np.uint16), whole.view(np.uint16))
 
 
-def test_oft_ring_route_on_two_streams(lib, cuda, pair_build):
-    """Two launches of the shared-X.R kernel queued on two streams with no synchronisation between them, repeatedly:
+@pytest.mark.parametrize("route", [3, 4])
+def test_oft_ring_route_on_two_streams(lib, cuda, pair_build, route):
+    """Two launches of a shared-X.R kernel (every pair does both jobs; rotation pairs of their own) queued on two streams with no synchronisation between them, repeatedly:
     each has its own ring and counters (stream-ordered from the library's pool) and is launched cooperatively, so
     both finish, no wait runs out, and both return the bits of a launch that ran alone."""
     import torch
@@ -651,7 +652,7 @@ def test_oft_ring_route_on_two_streams(lib, cuda, pair_build):
     from cute_mma_b200 import inputs
     dR = torch.from_numpy(inputs.pack_r(inputs.blocks_qr(1, k // b, b, 78))).to(cuda)
     alone = torch.empty((m, n), dtype=torch.float16, device=cuda)
-    with ops.option("oft_route", 3, lib), ops.option("raster", 4, lib), ops.option("ring_bands", 2, lib):
+    with ops.option("oft_route", route, lib), ops.option("raster", 4, lib), ops.option("ring_bands", 2, lib):
         ops.oft_tn(m, n, k, dA, k, dB, k, dR, k, alone, n, reconn_sz=b, lib=lib)
         torch.cuda.synchronize()
         s1, s2 = torch.cuda.Stream(), torch.cuda.Stream()
