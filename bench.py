@@ -411,6 +411,8 @@ def run_gpu_arm(args, workload):
         if y_chosen is not None:
             routes[rname]["same_bits_as_chosen"] = bool(torch.equal(y_chosen.view(torch.int16), dY.view(torch.int16)))
     del y_chosen
+    # the chosen route once more, after the others: the first timing ran on the coolest GPU of this process
+    routes[plan["path"]]["ms_per_step_after_the_others"] = timed_steps(args.steps, 2)
     for r in routes.values():
         r["frac_of_measured_bf16_burst_per_gpu"] = r["value"] / world / peaks["bf16_burst"]
     # the two passes of the two-pass route on their own (rank 0's GPU)
