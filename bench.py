@@ -533,8 +533,15 @@ def run_gpu_arm(args, workload):
             line["product_with_overlapped_allgather"] = {"ms_per_step": overlapped_ms, "sequential_ms": ms + allgather_ms,
                                                          "matches_nccl_allgather": overlapped_ok,
                                                          "api": "sharded.SlabProductAllGather (row chunks pushed into the peers' symmetric-memory buffers by copy engines)"}
+            # fused product + exchange: the slower of the slab's FLOPs at the measured GEMM peak and the bytes that must
+            # leave this GPU over NVLink ((N - 1) copies of its slab of Y) at the measured 770 GB/s peer-copy rate
+            nvlink_ms = (world - 1) * m * n_loc * 2 / 770e9 * 1e3
+            tensor_ms = flops_launch / (peaks["bf16_burst"] * 1e12) * 1e3
             line["product_with_epilogue_allgather"] = {"ms_per_step": stores_ms, "matches_nccl_allgather": stores_ok,
-                                                       "api": "b200_oft_tn_f16_gather (the kernel's epilogue stores every tile into all GPUs' buffers)"}
+                                                       "api": "b200_oft_tn_f16_gather (the kernel's epilogue stores every tile into all GPUs' buffers)",
+                                                       "roofline": {"bound": "nvlink" if nvlink_ms > tensor_ms else "tensor", "nvlink_ms": nvlink_ms,
+                                                                    "tensor_ms": tensor_ms, "frac": max(nvlink_ms, tensor_ms) / stores_ms,
+                                                                    "nvlink_gbs_per_gpu": (world - 1) * m * n_loc * 2 / (stores_ms * 1e-3) * 1e-9}}
         if world == 1 and workload == DEFAULT_WORKLOAD:
             del hX, hW, hY
             roofline["projection_shape"] = projection_shape_rates(lib, dev, stream, peaks)

@@ -455,19 +455,72 @@ oft3_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ 
       }
       tc_fence_before();
       mbar_arrive_cluster(mapa_shared(acc_empty, 0));
-      if (row < args.m) {
-        for (int d = 0; d <= args.n_more; ++d) {  // the caller's C, then every further destination
-          __half* out_row = (d == 0 ? args.C : args.C_more[d - 1]) + static_cast<long long>(row) * args.ldC;
-          const bool vec = vec_ok && (d == 0 || (reinterpret_cast<uintptr_t>(args.C_more[d - 1]) & 15) == 0);
+      if (row < args.m) {  // the caller's C: a lane owns a row and writes 64 contiguous bytes of it per 32 columns
+        __half* out_row = args.C + static_cast<long long>(row) * args.ldC;
 #pragma unroll
-          for (int c = 0; c < T::kBN / 32; ++c) {
-            const int col0 = tn * T::kBN + c * 32;
-            if (vec && col0 + 32 <= args.n) {
-              uint4* dst = reinterpret_cast<uint4*>(out_row + col0);
+        for (int c = 0; c < T::kBN / 32; ++c) {
+          const int col0 = tn * T::kBN + c * 32;
+          if (vec_ok && col0 + 32 <= args.n) {
+            uint4* dst = reinterpret_cast<uint4*>(out_row + col0);
 #pragma unroll
-              for (int q = 0; q < 4; ++q)
-                dst[q] = make_uint4(p[c * 16 + 4 * q], p[c * 16 + 4 * q + 1], p[c * 16 + 4 * q + 2], p[c * 16 + 4 * q + 3]);
-            } else {
+            for (int q = 0; q < 4; ++q)
+              dst[q] = make_uint4(p[c * 16 + 4 * q], p[c * 16 + 4 * q + 1], p[c * 16 + 4 * q + 2], p[c * 16 + 4 * q + 3]);
+          } else {
+#pragma unroll
+            for (int j = 0; j < 32; ++j)
+              if (col0 + j < args.n) {
+                const uint32_t w = p[c * 16 + j / 2];
+                out_row[col0 + j] = __ushort_as_half(static_cast<unsigned short>((j & 1) ? (w >> 16) : (w & 0xFFFFu)));
+              }
+          }
+        }
+      }
+      if (args.n_more > 0) {
+        // Further destinations (other GPUs' memory): a write of 16 bytes per lane, each to another row, crosses
+        // NVLink as 32 small packets.  The warp's 32 rows x 128 bytes are therefore transposed in registers first
+        // (butterfly of lane exchanges, 32 x 32 words at a time), after which the 32 lanes write the 128 contiguous
+        // bytes of one row with one instruction.  Needs 4-byte aligned rows; else the row-per-lane stores.
+        bool words = (args.ldC & 1) == 0;
+        for (int d = 0; d < args.n_more; ++d) words = words && (reinterpret_cast<uintptr_t>(args.C_more[d]) & 3) == 0;
+        if (words) {
+#pragma unroll
+          for (int blk = 0; blk < T::kBN / 64; ++blk) {
+#pragma unroll
+            for (int sft = 16; sft >= 1; sft >>= 1) {
+              const bool upper = (lane & sft) != 0;
+#pragma unroll
+              for (int j = 0; j < 32; ++j) {
+                if (j & sft) continue;
+                uint32_t& lo = p[blk * 32 + j];
+                uint32_t& hi = p[blk * 32 + j + sft];
+                const uint32_t got = __shfl_xor_sync(0xFFFFFFFFu, upper ? lo : hi, sft);
+                if (upper) lo = got; else hi = got;
+              }
+            }
+          }
+          // now p[blk * 32 + i] of lane L is word (blk * 32 + L) of row i of this warp
+          const int row0 = tm * 2 * T::kBM + rank * T::kBM + quad * 32;
+          for (int d = 0; d < args.n_more; ++d) {
+            __half* base = args.C_more[d] + static_cast<long long>(row0) * args.ldC + tn * T::kBN + 2 * lane;
+#pragma unroll
+            for (int blk = 0; blk < T::kBN / 64; ++blk) {
+              const int col = tn * T::kBN + blk * 64 + 2 * lane;
+#pragma unroll
+              for (int i = 0; i < 32; ++i) {
+                if (row0 + i >= args.m) continue;
+                __half* dst = base + static_cast<long long>(i) * args.ldC + blk * 64;
+                const uint32_t w = p[blk * 32 + i];
+                if (col + 1 < args.n) *reinterpret_cast<uint32_t*>(dst) = w;
+                else if (col < args.n) *dst = __ushort_as_half(static_cast<unsigned short>(w & 0xFFFFu));
+              }
+            }
+          }
+        } else if (row < args.m) {
+          for (int d = 0; d < args.n_more; ++d) {
+            __half* out_row = args.C_more[d] + static_cast<long long>(row) * args.ldC;
+#pragma unroll
+            for (int c = 0; c < T::kBN / 32; ++c) {
+              const int col0 = tn * T::kBN + c * 32;
 #pragma unroll
               for (int j = 0; j < 32; ++j)
                 if (col0 + j < args.n) {

@@ -224,7 +224,8 @@ class SlabProductAllGather:
     its peers' chunks have landed.  At 8 GPUs the exchange (7/8 of Y leaving every GPU) takes longer than the
     product, so the step costs about the exchange instead of product + exchange.
     mode "stores": one launch whose epilogue writes every tile straight into all GPUs' buffers (the direct peer-store
-    epilogue); simpler, but the 16-byte stores of one row per lane use NVLink poorly and the SMs wait for them."""
+    epilogue: each warp transposes its rows in registers and writes whole 128-byte lines).  At 8 GPUs this is the
+    faster of the two (6.2 ms per step against 8.2 ms; the NCCL all-gather alone takes 7.8 ms)."""
 
     def __init__(self, m, n_total, k, n0, n1, *, reconn_sz=8, world=None, rank=None, device=None, lib=None, chunks=4, copy_streams=3,
                  mode="copy_engines"):

@@ -201,7 +201,7 @@ int b200_oft_tn_f16_sharded(int m, int n, int k, int group_size, int reconn_sz, 
  * with ordinary global stores, so a destination may be another GPU's memory mapped into this process (peer access or
  * a shared allocation): with C_dst[d] = column n0 of GPU d's full Y[m][N] and ldC = N, every GPU of a node ends up
  * with all of Y without a separate all-gather (the direct peer-store epilogue; no TMA and no multicast touch peer
- * memory).  Other routes compute into C_dst[0] and copy.  The caller synchronises the GPUs before reading (the
+ * memory; with an even ldC the further destinations are written in whole 128-byte lines).  Other routes compute into C_dst[0] and copy.  The caller synchronises the GPUs before reading (the
  * stores of a peer are complete when that peer's stream is).  No counterpart in the reference, which is single-GPU. */
 int b200_oft_tn_f16_gather(int m, int n, int k, int group_size, int reconn_sz,
                            const void* A, int ldA, const void* B, int ldB, const void* R, int ldR,

@@ -665,16 +665,20 @@ def test_oft_ring_route_on_two_streams(lib, cuda, pair_build, route):
     assert torch.equal(c1, alone) and torch.equal(c2, alone)
 
 
-@pytest.mark.parametrize("m,n,k,b,gs", [(384, 2048, 256, 64, None), (200, 2056, 192, 32, None), (256, 512, 256, 64, None), (256, 2048, 128, 128, 1024)])
-def test_gather_entry_point_stores_every_destination(lib, cuda, pair_build, m, n, k, b, gs):
+@pytest.mark.parametrize("m,n,k,b,gs,pad", [(384, 2048, 256, 64, None, 8), (200, 2056, 192, 32, None, 8), (200, 2055, 192, 32, None, 3),
+                                            (200, 2056, 192, 32, None, 9), (256, 512, 256, 64, None, 8), (256, 2048, 128, 128, 1024, 8),
+                                            (2304, 5120, 256, 64, None, 8)])
+def test_gather_entry_point_stores_every_destination(lib, cuda, pair_build, m, n, k, b, gs, pad):
     """b200_oft_tn_f16_gather with three destinations on this GPU (padded ldC, canaries): each holds the bits of the
-    plain call, whether the shared-X.R kernel stores them from its epilogue (wide groups) or the library copies."""
+    plain call, whether the shared-X.R kernel stores them from its epilogue (wide groups: whole 128-byte lines after
+    a transpose in registers when ldC is even, ragged last column included; one row per lane when it is odd) or the
+    library copies."""
     import torch
 
     A, R, B = make_oft_case(m, n, k, b, gs, seed=81)
     want = run_oft(lib, cuda, A, R, B, m, n, k, b, gs)
     dA, dB, dR = (torch.from_numpy(x).to(cuda) for x in (A, B, R))
-    ldc = n + 8
+    ldc = n + pad
     dsts = [torch.full((m + 1, ldc), -7.0, dtype=torch.float16, device=cuda) for _ in range(3)]
     ops.oft_tn_gather(m, n, k, dA, k, dB, k, dR, k, dsts, ldc, group_size=gs, reconn_sz=b, lib=lib)
     assert ops.device_status(lib)[0] == 0
