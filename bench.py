@@ -441,7 +441,7 @@ def run_gpu_arm(args, workload):
         barrier()
         allgather_ms = max_over_ranks(a0.elapsed_time(a1))
         # the same exchange overlapped with the product (copy engines push finished row chunks to the peers)
-        ag = sharded.SlabProductAllGather(m, n, k, n0, n1, reconn_sz=b, world=world, rank=rank, device=dev, lib=lib)
+        ag = sharded.SlabProductAllGather(m, n, k, n0, n1, reconn_sz=b, world=world, rank=rank, device=dev, lib=lib, mode="copy_engines")
         for _ in range(2):
             y_all = ag(dX, dW, dR)
         overlapped_ok = bool(torch.equal(y_all.view(world * m, n_loc), out.view(world * m, n_loc)))

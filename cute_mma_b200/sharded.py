@@ -217,18 +217,18 @@ class SlabProductAllGather:
     """The rank's slab product with the all-gather of Y overlapped: when the call returns, every rank holds
     all of Y, rank-major [world][m][n_loc] (the layout of all_gather_c).
 
-    mode "copy_engines" (default): the product runs in row chunks on the compute stream; as soon as a chunk of the rank's slab is written, copy
+    mode "copy_engines": the product runs in row chunks on the compute stream; as soon as a chunk of the rank's slab is written, copy
     streams push it into the same place of every peer's buffer over NVLink (contiguous device-to-device copies,
     i.e. copy engines, no SMs and no kernel that waits for another GPU).  The peers' buffers are symmetric memory
     (torch.distributed._symmetric_memory), mapped once at construction.  A host barrier at the end of the call tells a rank that
     its peers' chunks have landed.  At 8 GPUs the exchange (7/8 of Y leaving every GPU) takes longer than the
     product, so the step costs about the exchange instead of product + exchange.
-    mode "stores": one launch whose epilogue writes every tile straight into all GPUs' buffers (the direct peer-store
+    mode "stores" (default): one launch whose epilogue writes every tile straight into all GPUs' buffers (the direct peer-store
     epilogue: each warp transposes its rows in registers and writes whole 128-byte lines).  At 8 GPUs this is the
     faster of the two (6.2 ms per step against 8.2 ms; the NCCL all-gather alone takes 7.8 ms)."""
 
     def __init__(self, m, n_total, k, n0, n1, *, reconn_sz=8, world=None, rank=None, device=None, lib=None, chunks=4, copy_streams=3,
-                 mode="copy_engines"):
+                 mode="stores"):
         import torch
         import torch.distributed as dist
 
