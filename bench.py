@@ -234,9 +234,25 @@ def _device_timer(stream):
     return timed
 
 
+def _interleaved(timed, fns, reps, rounds=4, warm=3):
+    """Median ms per call of each function in `fns`, timed in turn `rounds` times with `reps` calls per timing, so that
+    clock and temperature drift hits all of them alike (a library kernel timed after ours is not on the same GPU state)."""
+    import statistics
+
+    for fn in fns:
+        for _ in range(warm):
+            fn()
+    samples = [[] for _ in fns]
+    for _ in range(rounds):
+        for i, fn in enumerate(fns):
+            samples[i].append(timed(fn, reps, warm=0))
+    return [statistics.median(x) for x in samples]
+
+
 def projection_shape_rates(lib, dev, stream, peaks):
     """Device-timed rates of the single-GPU projection shape (M 16384, K = N 4096, b 64, Cayley blocks) on every
-    route of the library, 50 launches after 5 warm-up launches each; the route the library takes by itself first."""
+    route of the library, beside the plain GEMM of the same size and cuBLAS on it: medians of 5 interleaved timings of
+    10 launches each."""
     import torch
 
     from cute_mma_b200 import inputs, ops
@@ -251,17 +267,29 @@ def projection_shape_rates(lib, dev, stream, peaks):
     timed = _device_timer(stream)
     fl = flops_of(m, k, n, b)
     chosen = ops.oft_plan(m, n, k, reconn_sz=b, lib=lib)["path"]
+    # every route, the plain GEMM of the same size (W . X^T, no rotation: the ceiling of any route) and cuBLAS on it, all
+    # timed in turn (5 rounds of 10 launches each, medians), so that clock drift hits them alike
+    order = sorted(ops.ROUTES.items(), key=lambda kv: kv[1] != chosen)
+
+    def on_route(code):
+        def call():
+            ops.set_option("oft_route", code, lib)
+            ops.oft_tn(m, n, k, dX, k, dW, k, dR, k, dY, n, stream, reconn_sz=b, lib=lib)
+        return call
+
+    fns = [on_route(code) for code, _ in order]
+    fns += [lambda: ops.gemm_tn(n, m, k, dW, k, dX, k, dY, n, stream, lib=lib), lambda: torch.matmul(dX, dW.t())]
+    try:
+        times = _interleaved(timed, fns, 10, rounds=5)
+    finally:
+        ops.set_option("oft_route", 0, lib)
+    assert ops.device_status(lib)[0] == 0
     routes = {}
-    for code, rname in sorted(ops.ROUTES.items(), key=lambda kv: kv[1] != chosen):
-        with ops.option("oft_route", code, lib):
-            ms = timed(lambda: ops.oft_tn(m, n, k, dX, k, dW, k, dR, k, dY, n, stream, reconn_sz=b, lib=lib), 50, warm=5)
-        assert ops.device_status(lib)[0] == 0
+    for (code, rname), ms in zip(order, times):
         tf = fl / (ms * 1e-3) * 1e-12
         routes[rname] = {"ms_per_step": ms, "value": tf, "unit": "TFLOP/s", "steps": 50,
                          "frac_of_measured_bf16_burst": tf / peaks["bf16_burst"], "frac_of_nominal_fp16": tf / NOMINAL_FP16_TFLOPS}
-    # the plain GEMM of the same size (W . X^T, no rotation) and cuBLAS on it, as the ceiling of any route
-    ms_g = timed(lambda: ops.gemm_tn(n, m, k, dW, k, dX, k, dY, n, stream, lib=lib), 50, warm=5)
-    ms_t = timed(lambda: torch.matmul(dX, dW.t()), 50, warm=5)
+    ms_g, ms_t = times[-2], times[-1]
     out = {"workload": name, "M": m, "K": k, "N": n, "b": b, "route": chosen, "routes": routes,
            "value": routes[chosen]["value"], "unit": "TFLOP/s", "ms_per_step": routes[chosen]["ms_per_step"],
            "frac_of_measured_bf16_burst": routes[chosen]["frac_of_measured_bf16_burst"],
@@ -286,8 +314,7 @@ def plain_gemm_rates(lib, dev, stream, peaks):
     B = (torch.rand((m, m), generator=g, device=dev) * 2 - 1).to(torch.float16)
     C = torch.empty((m, m), dtype=torch.float16, device=dev)
     fl = 2.0 * m ** 3
-    ms = timed(lambda: ops.gemm_tn(m, m, m, A, m, B, m, C, m, stream, lib=lib), 20, warm=3)
-    ms_t = timed(lambda: torch.matmul(A, B.t()), 20, warm=3)
+    ms, ms_t = _interleaved(timed, [lambda: ops.gemm_tn(m, m, m, A, m, B, m, C, m, stream, lib=lib), lambda: torch.matmul(A, B.t())], 8)
     tf = fl / (ms * 1e-3) * 1e-12
     out["gemm_half_tn_8192"] = {"ms": ms, "value": tf, "unit": "TFLOP/s", "frac_of_measured_bf16_burst": tf / peaks["bf16_burst"],
                                 "frac_of_nominal_fp16": tf / NOMINAL_FP16_TFLOPS,
@@ -298,11 +325,10 @@ def plain_gemm_rates(lib, dev, stream, peaks):
     B = torch.randn((m, m), generator=g, device=dev)   # [K][N], N contiguous
     C = torch.empty((m, m), dtype=torch.float32, device=dev)
     fl = 2.0 * m ** 3
-    ms = timed(lambda: ops.gemm_nt(m, m, m, A, m, B, m, C, m, stream, dtype="float", lib=lib), 50, warm=5)
     prev = torch.backends.cuda.matmul.allow_tf32
     torch.backends.cuda.matmul.allow_tf32 = True
     try:
-        ms_t = timed(lambda: torch.matmul(A.t(), B), 50, warm=5)
+        ms, ms_t = _interleaved(timed, [lambda: ops.gemm_nt(m, m, m, A, m, B, m, C, m, stream, dtype="float", lib=lib), lambda: torch.matmul(A.t(), B)], 15)
     finally:
         torch.backends.cuda.matmul.allow_tf32 = prev
     tf, tf_t = fl / (ms * 1e-3) * 1e-12, fl / (ms_t * 1e-3) * 1e-12
