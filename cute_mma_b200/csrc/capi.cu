@@ -757,8 +757,14 @@ int choose_route(int m, int group_size, int k, int b, const DeviceState* st) {
   const int min_tiles = b >= 128 ? 4 : 8;
   if (!can_share || group_size < min_tiles * static_cast<int>(CurrCompParams::bN)) return 1;
   if (g_more.n > 0) return 3;  // only oft3_kernel stores to further destinations
+  // Route 4 also wants long tiles: its product pairs write C with the plain GEMM's epilogue (one 2-byte store per
+  // element), which must fit beside a tile's MMAs.  Interleaved runs, route 4 / route 3 time: M 32768, N 28672, K 1024,
+  // b 64: 1.61; M 262144, N 12288, K 2048, b 64 (3 pairs): 1.05; M 65536, N 28672, b 128 (2 pairs), K 2048: 0.86,
+  // K 4096: 0.88.
   const RingPlan p = ring_plan(m, group_size, k, st);
-  return (p.rot_pairs >= 1 && p.rot_pairs <= 3) ? 4 : 3;
+  const int k_steps = (k + 63) / 64;
+  const bool split = p.rot_pairs >= 1 && p.rot_pairs <= 3 && k_steps >= 32 && (p.rot_pairs <= 2 || k_steps >= 64);
+  return split ? 4 : 3;
 }
 
 // group_size == n or a multiple of the N tile: one R per tile.  group_size a divisor of the N tile (the

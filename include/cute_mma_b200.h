@@ -62,7 +62,7 @@ int b200_rotate_f16(int m, int k, int reconn_sz, const void* A, int ldA, const v
  * (narrow groups), 2 rotation pass + GEMM (only when asked for), 3 fused kernel in which one X.R per row block
  * serves all N tiles of its group through a ring of row blocks that stays in L2 (groups of 8 N tiles or more, 4 for
  * reconn_sz = 128), 4 the same ring with the rotation on SM pairs of its own (when at most three such pairs keep
- * up with the product: groups of about 40 N tiles or more).  No counterpart in the reference. */
+ * up with the product: groups of about 40 N tiles or more, K of 2048 or more).  No counterpart in the reference. */
 int b200_oft_plan(int m, int n, int k, int group_size, int reconn_sz, int* path, int* kernel_launches);
 
 /* The same product in two passes: X.R (rounded to fp16, as above) is written once to device scratch of

@@ -579,6 +579,10 @@ def test_route_choice_either_side_of_the_crossover(lib, cuda, pair_build):
     wide = lambda n: ops.oft_plan(65536, n, 8192, reconn_sz=128, lib=lib)["path"]
     assert wide(28672) == "fused_ring_split" and wide(14336) == "fused_ring_split" and wide(7168) == "fused_ring" and wide(3584) == "fused_ring"
     assert ops.oft_plan(1024, 28672, 8192, reconn_sz=128, lib=lib)["path"] == "fused_ring"  # every row block fits the ring
+    # ... and long tiles: K 1024 stays on the kernel in which every pair does both, K 2048 needs two pairs or fewer
+    assert ops.oft_plan(32768, 28672, 1024, reconn_sz=64, lib=lib)["path"] == "fused_ring"
+    assert ops.oft_plan(65536, 28672, 2048, reconn_sz=128, lib=lib)["path"] == "fused_ring_split"
+    assert ops.oft_plan(262144, 12288, 2048, reconn_sz=64, lib=lib)["path"] == "fused_ring"
     assert ops.oft_plan(16384, 8192, 4096, group_size=2048, reconn_sz=64, lib=lib)["kernel_launches"] == 4  # one launch per group
     with ops.option("oft_route", 2, lib):
         assert plan(4096, 64) == "two_pass"
