@@ -81,3 +81,16 @@ def test_gemm_stdout_contract_is_parsed_like_the_reference():
     assert runner.get_flops("CUTE_GEMM:     [1234567.8]GFlop/s  (0.7440)ms") == 1234567.8
     assert runner.get_flops("CUTE_GEMM:     [ 912.5]GFlop/s  (0.1000)ms") == 912.5
     assert math.isnan(runner.get_flops("cute_mma_b200 call failed with status 3"))
+
+
+def test_route_sweep_shape_arguments():
+    import argparse
+
+    import pytest
+
+    from cute_mma_b200.autotune import route_sweep
+
+    assert route_sweep.parse_shape("16384x4096x4096x64") == (16384, 4096, 4096, 64)
+    for bad in ("16384x4096x4096", "0x4096x4096x64", "256x256x100x64"):
+        with pytest.raises(argparse.ArgumentTypeError):
+            route_sweep.parse_shape(bad)

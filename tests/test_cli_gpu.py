@@ -52,3 +52,16 @@ def test_gemm_drivers_correct_and_parsed(bin_dir, exe, trans):
     assert re.search(r"error count: 0, max error: ", out), out
     m = runner.NUMBER.search(out)
     assert m and float(m.group(0)[1:-1]) > 0, out
+
+
+def test_route_sweep_times_every_route(capsys):
+    """The route comparison tool on a small shape: every route runs, the library's choice is named, the table prints."""
+    from cute_mma_b200.autotune import route_sweep
+
+    rows = route_sweep.sweep((2048, 2048, 512, 64), [0, 1, 2, 3, 4], 2, 1.0)
+    assert [r["route"] for r in rows] == [0, 1, 2, 3, 4]
+    assert rows[0]["name"] == "fused_ring" and rows[0]["ratio_to_choice"] == 1.0
+    assert all(r["ms"] > 0 and r["tflops"] > 0 for r in rows)
+    assert route_sweep.main(["256x512x128x32", "--routes", "0,1", "--rounds", "1", "--ms", "0.5"]) == 0
+    out = capsys.readouterr().out
+    assert "route 0 (fused_tmem)" in out and "route 1 fused_tmem" in out
