@@ -235,17 +235,22 @@ def _device_timer(stream):
 
 
 def _interleaved(timed, fns, reps, rounds=4, warm=3):
-    """Median ms per call of each function in `fns`, timed in turn `rounds` times with `reps` calls per timing, so that
-    clock and temperature drift hits all of them alike (a library kernel timed after ours is not on the same GPU state)."""
+    """Median ms per call of each function in `fns`, each timed once per round (`reps` calls per timing) in a freshly
+    shuffled order, so that clock and temperature drift hits all of them alike (on a power-capped GPU the clock a kernel
+    gets depends on what ran just before it)."""
+    import random
     import statistics
 
     for fn in fns:
         for _ in range(warm):
             fn()
     samples = [[] for _ in fns]
+    rng = random.Random(len(fns) * 1000 + reps)
     for _ in range(rounds):
-        for i, fn in enumerate(fns):
-            samples[i].append(timed(fn, reps, warm=0))
+        order = list(range(len(fns)))
+        rng.shuffle(order)  # a fixed order would favour whoever runs behind the coolest neighbour
+        for i in order:
+            samples[i].append(timed(fns[i], reps, warm=0))
     return [statistics.median(x) for x in samples]
 
 
